@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--workload c2|c1|c4|c5|c3] [--impl reference]
+
+Default workload (c2): BASELINE config 2, the 35B-MoE decode attention layer — 16 q / 2 kv heads, head_dim 256,
+partial RoPE (64 dims, theta 1e7), sigmoid gate, 32768-token f16 KV context, one new token — for the model's 10
+attention layers.  A step is one decode token through those 10 layers: RoPE + KV append + split-K decode + combine +
+gate per layer, each layer with its own caches (10 x 67 MB, so no layer's K/V survives in the 126 MB L2 until its
+next use).  Inputs are seeded synthetic tensors (N(0,1) -> f16, 4 outlier channels per head x20); the reference
+measures on chat prompts through real weights, which are not available here.
+
+With N > 1 (torchrun, one process per GPU) the KV sequence is sharded by chunk: every rank holds a 32768-row chunk
+of an N x 32768-token context, streams its chunk, and the ranks merge their (m, l, o) records with one NCCL
+all-gather per layer (weak scaling: per-GPU bytes fixed; at N = 1 this is exactly config 2).
+
+value    algorithmic K/V GB/s with inputs resident in HBM (CUDA events, max over ranks)
+e2e      the same metric through the host-buffer C-ABI call (pinned host q/k/v/gate in, out back, every layer)
+roofline the split-K decode kernel alone: algorithmic bytes per launch / its CUDA-event duration, against the
+         measured copy bandwidth of MEASURED_PEAKS.json
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: nH, nKV, hd, n_rot, theta, ctx, n_cols, n_seqs, layers, gate, outliers
+    "c1": dict(nH=16, nKV=8, hd=128, n_rot=128, theta=1e6, ctx=4096, n_cols=1, n_seqs=1, layers=28, gate=False, outliers=False,
+               desc="config 1: Qwen3-1.7B-shaped decode attention, 16q/8kv hd128 full RoPE, ctx 4096, 28 layers"),
+    "c2": dict(nH=16, nKV=2, hd=256, n_rot=64, theta=1e7, ctx=32768, n_cols=1, n_seqs=1, layers=10, gate=True, outliers=True,
+               desc="config 2: Qwen3.6-35B-MoE-shaped decode attention, 16q/2kv hd256 partial RoPE 64, gate, ctx 32768, 10 attention layers"),
+    "c4": dict(nH=24, nKV=4, hd=256, n_rot=64, theta=1e7, ctx=16384, n_cols=5, n_seqs=1, layers=16, gate=True, outliers=False,
+               desc="config 4: 27B-hybrid-shaped 5-token verify block, 24q/4kv hd256, ctx 16384, 16 attention layers"),
+    "c5": dict(nH=16, nKV=2, hd=256, n_rot=64, theta=1e7, ctx=131072, n_cols=1, n_seqs=8, layers=2, gate=True, outliers=False,
+               desc="config 5: 8 sequences x 131072-token context, 16q/2kv hd256, gate, KV sequence sharded across the GPUs (strong scaling), 2 layers"),
+}
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region (read-only)."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+def run_ours(args, w):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from pooled_b200 import AttnConfig, AttnEngine
+    from pooled_b200.shard import ShardPlan, ShardedDecoder
+
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    nH, nKV, hd, ctx, n_cols, n_seqs, layers = w["nH"], w["nKV"], w["hd"], w["ctx"], w["n_cols"], w["n_seqs"], w["layers"]
+    qd, kvd = nH * hd, nKV * hd
+    strong = args.workload == "c5"
+    # rows each rank holds per sequence, and the global position of the new token
+    chunk = (ctx // world) if strong else ctx
+    total_ctx = ctx if strong else ctx * world
+    pad = 64
+    eng = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=w["n_rot"], rope_theta=w["theta"], max_seq=chunk + pad, n_layers=layers,
+                                n_seqs=n_seqs, act_dtype=torch.float16, max_cols=max(8, n_cols * n_seqs)), device=local)
+    g = torch.Generator(device=dev); g.manual_seed(1234 + rank)
+    for li in range(layers):
+        for name in ("k", "v"):
+            c = eng.cache(li, name)
+            x = torch.randn((n_seqs, chunk + pad, kvd), generator=g, device=dev, dtype=torch.float32)
+            if w["outliers"] and name == "k":
+                x.view(n_seqs, chunk + pad, nKV, hd)[..., :4] *= 20.0
+            c.copy_(x.to(torch.float16).view(torch.int16))
+            del x
+    T = n_cols * n_seqs
+    gh = torch.Generator(); gh.manual_seed(99)
+    mk = lambda n: torch.randn((layers, T, n), generator=gh).to(torch.float16)
+    hq, hk, hv, hg = mk(qd), mk(kvd), mk(kvd), mk(qd)
+    if w["outliers"]:
+        hq.view(layers, T, nH, hd)[..., :4] *= 20.0
+    hq, hk, hv, hg = (t.pin_memory() for t in (hq, hk, hv, hg))
+    hout = torch.empty((layers, T, qd), dtype=torch.float16).pin_memory()
+    dq, dk, dv, dg = (t.to(dev) for t in (hq, hk, hv, hg))
+    dout = torch.empty((layers, T, qd), dtype=torch.float16, device=dev)
+    gate = (lambda t, li: t[li]) if w["gate"] else (lambda t, li: None)
+
+    sharded = world > 1
+    if sharded:
+        plan = ShardPlan(world, chunk)
+        sd = ShardedDecoder(eng, plan, rank, dist)
+        gbuf = torch.empty((world, T * nH * (hd + 2)), dtype=torch.float32, device=dev)
+        new_pos = total_ctx - 1   # the new token is the last row of the last rank's chunk
+        seqs_pos = [(s, new_pos) for s in range(n_seqs)]
+
+        def step():
+            for li in range(layers):
+                sd.step(li, seqs_pos, dq[li], dk[li], dv[li], gate(dg, li), dout[li], gbuf)
+        bytes_per_layer_rank = [2 * min(chunk, max(0, new_pos + 1 - r * chunk)) * kvd * 2 * n_seqs for r in range(world)]
+        bytes_per_step = layers * sum(bytes_per_layer_rank)
+        kernel_bytes = bytes_per_layer_rank[rank]
+    else:
+        pos = ctx   # the cache holds rows [0, ctx); the new tokens land at ctx .. ctx + n_cols - 1
+        if n_seqs == 1:
+            def step():
+                for li in range(layers):
+                    eng.encode_layer(li, pos, dq[li], dk[li], dv[li], gate(dg, li), dout[li], mode="decode")
+        else:
+            items = [(s, pos, 1) for s in range(n_seqs)]
+
+            def step():
+                for li in range(layers):
+                    for s in range(n_seqs):
+                        eng.rope_append(li, s, pos, dq[li, s:s + 1], dk[li, s:s + 1], dv[li, s:s + 1])
+                    eng.decode(li, items, dq[li], gate(dg, li), dout[li])
+        kernel_bytes = 2 * (pos + n_cols) * kvd * 2 * n_seqs
+        bytes_per_step = layers * kernel_bytes
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    clocks = ClockSampler(local); clocks.start()
+    st0 = eng.stats()
+    eng.timing_begin(layers * args.steps + 8)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    core_ms, core_n = eng.timing_end()
+    st1 = eng.stats()
+    eng.sync()
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
+
+    # end to end: host buffers in, host result out, every layer, through the C ABI's host entry point
+    e2e = None
+    if not sharded and n_seqs == 1:
+        for _ in range(3):
+            for li in range(layers):
+                eng.encode_layer_host(li, ctx, hq[li], hk[li], hv[li], gate(hg, li), hout[li], mode="decode")
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            for li in range(layers):
+                eng.encode_layer_host(li, ctx, hq[li], hk[li], hv[li], gate(hg, li), hout[li], mode="decode")
+        e1.record()
+        barrier()
+        ems = e0.elapsed_time(e1)
+        es = 2
+        e2e = {"value": round(bytes_per_step * args.steps / (ems * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ems / args.steps, 4),
+               "h2d_bytes_per_step": layers * T * (qd + 2 * kvd + (qd if w["gate"] else 0)) * es, "d2h_bytes_per_step": layers * T * qd * es}
+    else:
+        # sharded / batched steps: the same step with a pinned-host upload of its inputs and a download of its result
+        def step_host():
+            dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True); dg.copy_(hg, non_blocking=True)
+            step()
+            hout.copy_(dout, non_blocking=True)
+        for _ in range(3):
+            step_host()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step_host()
+        e1.record()
+        barrier()
+        ems = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ems], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ems = float(t.item())
+        e2e = {"value": round(bytes_per_step * args.steps / (ems * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ems / args.steps, 4),
+               "h2d_bytes_per_step": int(hq.numel() + hk.numel() + hv.numel() + hg.numel()) * 2 * world, "d2h_bytes_per_step": int(hout.numel()) * 2 * world}
+    ck = clocks.stop()
+
+    peak, peak_src = peaks()
+    achieved = kernel_bytes / (core_ms / max(core_n, 1) * 1e-3) / 1e9 if core_n else None
+    line = {
+        "metric": "attn decode KV GB/s", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+        "dtype": "f16 cache and activations, f32 accumulate", "data": "synthetic (seeded N(0,1) -> f16, outlier channels x20)" if w["outliers"] else "synthetic (seeded N(0,1) -> f16)",
+        "config": {"workload": w["desc"], "kv_rows_per_gpu": chunk, "total_context": total_ctx, "layers_per_step": layers,
+                   "l2": "each layer has its own caches; a step touches %d MB per GPU, more than the 126 MB L2, before any row is reused" % (layers * kernel_bytes // 1_000_000),
+                   "pct_of_8TBs_nominal": round(100 * value / world / 8000, 1)},
+        "roofline": {"bound": "hbm", "kernel": "pa_decode_kernel", "achieved": round(achieved, 1) if achieved else None, "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4) if achieved else None, "peak_source": peak_src, "launches_timed": int(core_n),
+                     "us_per_launch": round(core_ms / max(core_n, 1) * 1e3, 2), "algorithmic_bytes_per_launch": kernel_bytes, "traffic": args.traffic},
+        "e2e": e2e, "gpu_launches": int(st1["kernel_launches"] - st0["kernel_launches"]), "clocks": ck,
+    }
+    if rank == 0:
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(w, budget_s=args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+
+
+def cpu_baseline(w, budget_s: float = 12.0, threads: int | None = None):
+    """The reference's CPU attention (the oracle's threaded f32 restatement) on one layer call of the workload."""
+    import numpy as np
+    from oracle import po
+    nH, nKV, hd, ctx, n_cols = w["nH"], w["nKV"], w["hd"], w["ctx"], w["n_cols"]
+    rows = ctx + n_cols
+    sample_rows = rows
+    K = po.np_f16_rne(po.normal(1, sample_rows * nKV * hd)).reshape(sample_rows, nKV * hd)
+    V = po.np_f16_rne(po.normal(2, sample_rows * nKV * hd)).reshape(sample_rows, nKV * hd)
+    q = po.normal(3, n_cols * nH * hd).astype(np.float32).reshape(n_cols, nH * hd)
+    g = po.normal(4, n_cols * nH * hd).astype(np.float32).reshape(n_cols, nH * hd) if w["gate"] else None
+    po.attn_f32_fast(q, K, V, nH, nKV, hd, ctx, n_cols, g)   # warm
+    t0 = time.perf_counter(); reps = 0
+    while True:
+        po.attn_f32_fast(q, K, V, nH, nKV, hd, ctx, n_cols, g); reps += 1
+        if time.perf_counter() - t0 > budget_s or reps >= 200:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    nbytes = 2 * rows * nKV * hd * 2 * w["n_seqs"]
+    return {"value": round(nbytes / w["n_seqs"] / dt / 1e9, 3), "unit": "GB/s", "cores": po.threads(), "kind": "port",
+            "sample": f"{reps} repetitions of one layer call of one sequence ({rows} rows x {nKV} kv heads x {hd}), threaded over (column, head); {dt * 1e3:.1f} ms each"}
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb = cpu_baseline(w, budget_s=max(5.0, min(60.0, 4.0 * args.steps)))
+    line = {"impl": "reference", "metric": "attn decode KV GB/s", "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over an f16 cache",
+            "data": "synthetic (seeded N(0,1) -> f16)", "config": {"workload": w["desc"]},
+            "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "pooled's attention runs only as WGSL through WebGPU, which needs a graphics stack (unavailable on this box), and no "
+                    "JavaScript runtime exists here; this arm times the C restatement of its CPU reference attention on the host cores"}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the decode kernel, if known")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

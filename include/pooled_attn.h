@@ -1,0 +1,232 @@
+/*
+ * pooled_attn.h — C ABI of libpooled_attn.so: pooled's GQA attention hot path on B200 (sm_100a).
+ *
+ * The library replaces the WebGPU dispatches that pooled's engines encode for one attention layer:
+ * RoPE, f16 KV-cache append, split-K flash-decode / k-token verify, tiled causal prefill, the LSE
+ * combine and the sigmoid output gate.  Each entry point below names the reference interface it
+ * stands in for (paths inside the pooled repository).
+ *
+ * Conventions
+ *   - plain C: opaque handles, raw device pointers, sizes and strides in ELEMENTS of the tensor's dtype.
+ *   - every call returns PA_OK (0) or a negative pa_status; pa_last_error() gives the message.  There is
+ *     no CPU fallback: an unsupported shape is PA_EUNSUPPORTED (the reference's config functions return
+ *     null there, engine/wgsl/attn_dec.js:41), a missing or faulting GPU is PA_ECUDA.
+ *   - calls enqueue work on the CUDA stream given (0 = the legacy default stream) and return without
+ *     waiting, like WebGPU command encoding followed by queue.submit (engine/qwen35.js:4223); work on one
+ *     stream runs in order.  A context is not thread-safe (the reference host is single-threaded).
+ *   - activations (q, k, v, gate, out) are [column][...] arrays with an explicit column stride, as the
+ *     reference's batched buffers are (FD.s0 / FD.s1, engine/wgsl/attn_dec.js:60).  Column c of a call at
+ *     position pos is the token at position pos + c and attends cache rows [0, pos + c + 1).
+ *   - caches are f16 [n_seqs][max_seq][n_kv_heads * head_dim], K and V separate, pairs little-endian
+ *     (engine/wgsl/qwen35.js:889-906, engine/qwen35.js:1102-1104).
+ */
+#ifndef POOLED_ATTN_H
+#define POOLED_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PA_API __attribute__((visibility("default")))
+
+typedef enum pa_status {
+  PA_OK = 0,
+  PA_EINVAL = -1,       /* bad argument (null pointer, position past max_seq, misaligned stride ...) */
+  PA_EUNSUPPORTED = -2, /* shape outside what the kernels cover */
+  PA_ENOMEM = -3,       /* device allocation failed */
+  PA_ECUDA = -4,        /* CUDA runtime / driver error, or no usable device */
+  PA_ETIMEOUT = -5,     /* a bounded device-side wait ran out (reported by pa_sync / pa_check) */
+  PA_ESTATE = -6        /* context latched after an earlier failure; pa_reset() clears it
+                           (engine/qwen35.js:111-119: every method rejects until reset()) */
+} pa_status;
+
+typedef enum pa_dtype { PA_F32 = 0, PA_F16 = 1 } pa_dtype;
+
+typedef enum pa_rope_mode {
+  PA_ROPE_NONE = 0,  /* q and k arrive already rotated */
+  PA_ROPE_F64 = 1,   /* angle pos * theta^(-2i/n_rot), cos/sin and products in float64, f32 result
+                        (the arithmetic of tests/reference/ref_q38.mjs:67-79; the WGSL rope_part,
+                        engine/wgsl/qwen35.js:386-404, evaluates the same formula in f32) */
+  PA_ROPE_TABLE = 2  /* host-supplied f32 cos/sin table, f32 products rounded one by one
+                        (the Flash engine: engine/qwen4exp.js:549-553, engine/wgsl/qwen4exp.js:545-548) */
+} pa_rope_mode;
+
+enum {
+  PA_FLAG_FAST = 1u /* single-f16 tensor-core operands for q and the softmax weights instead of the
+                        default hi+lo f16 pairs (about 2^-11 relative error on them instead of 2^-22) */
+};
+
+/* Shape and arithmetic of one model's attention layers.  Stands in for the engine's Config / DN uniform
+ * blocks (engine/wgsl/base.js:4-8, engine/qwen35.js:822-832) and the attention options of
+ * Qwen35Engine.create (engine/qwen35.js:266: attnDecodeSplits ...). */
+typedef struct pa_config {
+  uint32_t n_heads;     /* query heads */
+  uint32_t n_kv_heads;  /* K/V heads; n_heads % n_kv_heads == 0 */
+  uint32_t head_dim;    /* 128 or 256 */
+  uint32_t n_rot;       /* rotated dims per head (== head_dim for full RoPE); even, multiple of 2 */
+  double rope_theta;
+  uint32_t rope_mode;   /* pa_rope_mode */
+  uint32_t act_dtype;   /* pa_dtype of q, k, v, gate and out buffers */
+  uint32_t max_cols;    /* most columns one call may carry (decode / verify / prefill chunk) */
+  uint32_t splits;      /* split-K CTAs per (sequence, kv head); 0 = sized to the GPU's SM count */
+  uint32_t flags;       /* PA_FLAG_* */
+  uint32_t reserved[5];
+} pa_config;
+
+typedef struct pa_ctx pa_ctx;     /* one per (device, model shape) */
+typedef struct pa_layer pa_layer; /* one attention layer's K and V caches */
+
+/* One unit of a batched decode: n_cols consecutive tokens of sequence seq, the first at position pos. */
+typedef struct pa_item {
+  uint32_t seq, pos, n_cols, reserved;
+} pa_item;
+
+/* ---- lifetime ------------------------------------------------------------------------------------ */
+
+/* Replaces pipeline creation in Qwen35Engine._initAttnDec / _initAttnTile (engine/qwen35.js:1959-2019). */
+PA_API int pa_create(int device, const pa_config* cfg, pa_ctx** out);
+PA_API int pa_destroy(pa_ctx* ctx);
+/* Replaces the per-layer cache allocation and bind groups (engine/qwen35.js:1102-1145).  Fails with a
+ * readable message when the caches do not fit (engine/qwen35.js:378-383 throws at create as well). */
+PA_API int pa_layer_create(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, pa_layer** out);
+PA_API int pa_layer_destroy(pa_layer* layer);
+/* Declares this layer's caches a shard of longer sequences: cache row 0 holds global position `origin`.  Every
+ * position passed to later calls stays global; appends must fall inside [origin, origin + max_seq), decode
+ * partials cover the rows of [0, pos + c + 1) the shard holds (possibly none).  No counterpart in the reference. */
+PA_API int pa_layer_set_origin(pa_layer* layer, uint32_t origin);
+/* Device pointer of the K (which = 0) or V (1) cache: what _stateParts exports (engine/qwen35.js:129-141). */
+PA_API void* pa_cache_ptr(pa_layer* layer, int which);
+PA_API const char* pa_last_error(pa_ctx* ctx);
+PA_API const char* pa_version(void);
+/* Waits for the stream and reports a device-side failure (onSubmittedWorkDone, engine/qwen35.js:3859). */
+PA_API int pa_sync(pa_ctx* ctx, void* stream);
+PA_API int pa_reset(pa_ctx* ctx); /* engine.reset() after a failed step (engine/qwen35.js:111-119) */
+
+/* Plain device / pinned-host memory for callers without a CUDA binding of their own
+ * (device.createBuffer / queue.writeBuffer / mapAsync in the reference). */
+PA_API int pa_alloc(pa_ctx* ctx, size_t bytes, void** dev_ptr);
+PA_API int pa_free(pa_ctx* ctx, void* dev_ptr);
+PA_API int pa_alloc_host(pa_ctx* ctx, size_t bytes, void** host_ptr);
+PA_API int pa_free_host(pa_ctx* ctx, void* host_ptr);
+PA_API int pa_upload(pa_ctx* ctx, void* dev_dst, const void* host_src, size_t bytes, void* stream);
+PA_API int pa_download(pa_ctx* ctx, void* host_dst, const void* dev_src, size_t bytes, void* stream);
+
+/* ---- host mirrors of the reference's split arithmetic ---------------------------------------------- */
+
+/* attnDecConfig / decSplitLen / decSplits (engine/wgsl/attn_dec.js:40-48): the reference's own split rule,
+ * kept so engine code that sizes buffers from it still works.  pa_dec_config returns the target split
+ * count S, or 0 where the reference returns null. */
+PA_API uint32_t pa_dec_config(uint32_t head_dim, uint32_t G, uint32_t n_kv, uint32_t splits);
+PA_API uint32_t pa_dec_split_len(uint32_t s, uint32_t S);
+PA_API uint32_t pa_dec_splits(uint32_t s, uint32_t S);
+/* tileSplitLen (engine/wgsl/attn_tile.js:53-56). */
+PA_API uint32_t pa_tile_split_len(uint32_t seq_end, uint32_t fa_split, uint32_t fa_splits, uint32_t target);
+/* The split count this library uses for a call whose longest column sees n_rows cache rows. */
+PA_API uint32_t pa_plan_splits(pa_ctx* ctx, uint32_t n_rows, uint32_t n_items);
+
+/* ---- the path, step by step ------------------------------------------------------------------------ */
+
+/* RoPE.  Replaces rope_part / rope_part_mc (engine/wgsl/qwen35.js:386-404, :858-875), the full-head rope
+ * (engine/wgsl/base.js:154-172) and the rotation inside attn_glue (engine/wgsl/qwen35.js:1124-1131).
+ * x: act_dtype [n_cols][col_stride], head h at h * head_stride; y: f32 [n_cols][y_col_stride] with heads
+ * packed [n_heads_x][head_dim].  x == y is allowed when act_dtype is f32 and the layouts coincide.
+ * cs_table (PA_ROPE_TABLE only): f32 [n_cols][n_rot], (cos, sin) per rotated pair. */
+PA_API int pa_rope(pa_ctx* ctx, const void* x, uint64_t col_stride, uint64_t head_stride, uint32_t n_heads_x,
+                   uint32_t pos, uint32_t n_cols, const float* cs_table, float* y, uint64_t y_col_stride,
+                   void* stream);
+
+/* KV append, conversion only: rows pos .. pos+n_cols-1 of sequence seq get the f16 round-to-nearest-even
+ * image of k and v (already rotated).  Replaces kv_store (engine/wgsl/qwen35.js:889-906) and kvStoreRow
+ * (engine/wgsl/qwen4exp.js:494-506).  Bit-exact. */
+PA_API int pa_kv_append(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* k,
+                        const void* v, uint64_t col_stride, int dtype, void* stream);
+
+/* Fused front of the path: rotate q into q_rot (f32 [n_cols][n_heads*head_dim]), rotate k, append k and
+ * v.  Replaces attn_glue_kv minus the head norm (engine/wgsl/layer_fuse.js:87-146).  q_rot may be NULL:
+ * the rotated q then stays in the context's own buffer for the pa_attend call that follows. */
+PA_API int pa_rope_append(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q,
+                          uint64_t q_col_stride, uint64_t q_head_stride, const void* k, const void* v,
+                          uint64_t kv_col_stride, const float* cs_table, float* q_rot, void* stream);
+
+/* Decode / verify core + combine + gate.  Replaces attn_dec + attn_dec_combine(_g) + sigmoid_mul
+ * (engine/wgsl/attn_dec.js:67-287, engine/wgsl/qwen35.js:406-416) as dispatched by _encodeLayerR
+ * (engine/qwen35.js:1619-1640) and the attn_dec branch of _encAttnCore (:2494-2499).
+ * q: rotated queries, dtype q_dtype, [total columns][q_col_stride]; the items' columns follow one another
+ * in q, gate and out.  gate may be NULL; with an interleaved q_full buffer pass gate = q + head_dim and
+ * the same strides (engine/wgsl/attn_dec.js:282-283).  n_cols * (n_heads / n_kv_heads) <= 64 per item. */
+PA_API int pa_decode(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q, int q_dtype,
+                     uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
+                     uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);
+
+/* The same, stopping before normalisation: one (o[head_dim], m, l) f32 record per (column, head) over the
+ * rows this cache holds, for a KV sequence sharded across GPUs.  partial: f32 [rows * head_dim] holding o
+ * (unnormalised), followed by f32 [rows][2] holding (m in natural-log units, l); rows = total columns *
+ * n_heads, so one rank's records are rows * (head_dim + 2) contiguous floats.  No counterpart in the
+ * reference (attention never leaves one device there); the record is the one attn_dec writes per split
+ * (engine/wgsl/attn_dec.js:186-199). */
+PA_API int pa_decode_partial(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q, int q_dtype,
+                             uint64_t q_col_stride, uint64_t q_head_stride, float* partial, void* stream);
+
+/* LSE merge of n_parts partial records per (column, head) + gate: out = sum o_s e^(m_s-M) / sum l_s e^(m_s-M).
+ * parts: n_parts blocks laid out as pa_decode_partial writes them, one after another (what an all-gather
+ * of the ranks' blocks produces).  The arithmetic of attn_dec_combine(_g) (engine/wgsl/attn_dec.js:215-287)
+ * applied to per-GPU records. */
+PA_API int pa_merge(pa_ctx* ctx, const float* parts, uint32_t n_parts, uint32_t n_cols, const void* gate,
+                    uint64_t gate_col_stride, uint64_t gate_head_stride, void* out, uint64_t out_col_stride,
+                    void* stream);
+
+/* Tiled causal prefill of n_cols columns of one sequence starting at pos (their K/V already appended).
+ * Replaces attn_flash_tile + attn_combine_tile + sigmoid_mul_mc (engine/wgsl/attn_tile.js:108-193,
+ * engine/wgsl/qwen35.js:877-887) as dispatched by _encAttnCore (engine/qwen35.js:2489-2493, :2516). */
+PA_API int pa_prefill(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, int q_dtype,
+                      uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
+                      uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);
+
+/* Standalone gate: a[i] *= 1/(1+exp(-g[i])).  Replaces sigmoid_mul(_mc) (engine/wgsl/qwen35.js:406-416). */
+PA_API int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const void* g, uint64_t g_col_stride,
+                          uint64_t g_head_stride, uint32_t n_cols, void* stream);
+
+/* ---- the path in one call --------------------------------------------------------------------------- */
+
+enum { PA_MODE_AUTO = 0, PA_MODE_DECODE = 1, PA_MODE_PREFILL = 2 };
+
+/* One attention layer for n_cols new tokens of one sequence: RoPE on q and k, append k and v, attend
+ * (decode / verify kernel, or the tiled prefill kernel, chosen as _encAttnCore chooses: engine/qwen35.js:
+ * 2485-2503), gate.  This is the attention block of _encodeLayerR / _encodeLayerBatch between the q/k/v
+ * projections and the o projection (engine/qwen35.js:1598-1640, :2473-2517).  Device pointers. */
+PA_API int pa_attn_layer(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q,
+                         uint64_t q_col_stride, uint64_t q_head_stride, const void* k, const void* v,
+                         uint64_t kv_col_stride, const void* gate, uint64_t gate_col_stride,
+                         uint64_t gate_head_stride, const float* cs_table, void* out, uint64_t out_col_stride,
+                         void* stream);
+
+/* The same with HOST buffers (pinned or pageable): inputs are copied to the device, the layer runs, out is
+ * copied back; returns after the stream has drained.  For hosts that hand the library ArrayBuffers. */
+PA_API int pa_attn_layer_host(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode,
+                              const void* q, uint64_t q_col_stride, uint64_t q_head_stride, const void* k,
+                              const void* v, uint64_t kv_col_stride, const void* gate, uint64_t gate_col_stride,
+                              uint64_t gate_head_stride, const float* cs_table, void* out,
+                              uint64_t out_col_stride, void* stream);
+
+/* Counters since creation: what tests/bench_attn_ctx.js collects with timestamp queries. */
+typedef struct pa_stats {
+  uint64_t kernel_launches; /* this library's kernels launched */
+  uint64_t kv_bytes_streamed; /* algorithmic K+V bytes of decode / verify / prefill calls */
+  uint64_t calls;
+} pa_stats;
+PA_API int pa_get_stats(pa_ctx* ctx, pa_stats* out);
+
+/* Device time of the core kernel (the split-K decode kernel, or the tiled prefill kernel) measured with CUDA
+ * events recorded on the call's stream right around that launch: what the per-dispatch timestamp queries of
+ * tests/bench_attn_ctx.js:39-70 give in the reference.  pa_timing_begin arms up to max_events launches;
+ * pa_timing_end waits for them and returns their summed duration and count. */
+PA_API int pa_timing_begin(pa_ctx* ctx, uint32_t max_events);
+PA_API int pa_timing_end(pa_ctx* ctx, double* core_ms, uint64_t* core_launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POOLED_ATTN_H */

@@ -1,0 +1,293 @@
+"""Host side of the attention path: the call surface pooled's engines use, over libpooled_attn.so.
+
+Mirrors, by name and argument meaning:
+  attn_dec_config / dec_split_len / dec_splits / DEC_CQ   engine/wgsl/attn_dec.js:40-51
+  attn_tile_config / tile_split_len                        engine/wgsl/attn_tile.js:43-56
+  AttnEngine.encode_layer                                  the attention block of Qwen35Engine._encodeLayerR
+                                                           (engine/qwen35.js:1598-1640) and _encAttnGlue + _encAttnCore
+                                                           (engine/qwen35.js:2473-2517)
+torch is used for device memory and streams only; every computation is a call into the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import lib as _l
+
+DEC_CQ = 4  # engine/wgsl/attn_dec.js:51
+
+
+def attn_dec_config(hd: int, G: int, nKV: int, splits: int = 0, kvQ8: bool = False, R: int = 1):
+    """attnDecConfig (engine/wgsl/attn_dec.js:40-44): None where the reference's split-K decode refuses the shape."""
+    if kvQ8 or hd != 256 or not (1 <= G <= 8) or not R >= 1:
+        return None
+    S = int(splits) if splits > 0 else max(16, 256 // nKV)
+    return {"HD": hd, "G": G, "S": S, "R": R}
+
+
+def dec_split_len(s: int, S: int) -> int:
+    """decSplitLen (engine/wgsl/attn_dec.js:47)."""
+    return max(64, math.ceil(math.ceil(s / S) / 64) * 64)
+
+
+def dec_splits(s: int, S: int) -> int:
+    """decSplits (engine/wgsl/attn_dec.js:48)."""
+    return math.ceil(s / dec_split_len(s, S))
+
+
+def attn_tile_config(hd: int, G: int, faSplit: int, faSplits: int, wgMem: int = 16384, target: int = 32, tk: int = 0,
+                     kvh: bool = False, pf: bool = False, nr: bool = False):
+    """attnTileConfig (engine/wgsl/attn_tile.js:43-50)."""
+    if not (hd % 16 == 0 and 16 <= hd <= 256 and 1 <= G <= 64):
+        return None
+    if faSplit % 64 != 0 or faSplits < 1:
+        return None
+    nbytes = lambda TK: TK * hd * 4 + TK * 256 * 4
+    TK = tk or next((t for t in (16, 8, 4) if nbytes(t) <= wgMem), 0)
+    if not TK or nbytes(TK) > wgMem:
+        return None
+    return {"HD": hd, "G": G, "CW": 64 // G, "TK": TK, "FASPLIT": faSplit, "FASPLITS": faSplits, "TARGET": max(1, int(target)),
+            "KVH": bool(kvh), "PF": bool(pf), "NR": bool(nr)}
+
+
+def tile_split_len(seqEnd: int, c: dict) -> int:
+    """tileSplitLen (engine/wgsl/attn_tile.js:53-56)."""
+    up64 = lambda x: math.ceil(x / 64) * 64
+    return min(c["FASPLIT"], max(64, up64(math.ceil(seqEnd / c["TARGET"])), up64(math.ceil(seqEnd / c["FASPLITS"]))))
+
+
+@dataclass
+class AttnConfig:
+    """Shape of a model's attention layers (Config / DN of the reference, engine/qwen35.js:822-832)."""
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    n_rot: int
+    rope_theta: float
+    max_seq: int
+    n_layers: int = 1
+    n_seqs: int = 1
+    rope_mode: str = "f64"            # "none" | "f64" | "table"
+    act_dtype: torch.dtype = torch.float16
+    max_cols: int = 8
+    splits: int = 0
+    fast: bool = False
+
+    @property
+    def q_dim(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+
+_ROPE = {"none": _l.PA_ROPE_NONE, "f64": _l.PA_ROPE_F64, "table": _l.PA_ROPE_TABLE}
+_MODE = {"auto": _l.PA_MODE_AUTO, "decode": _l.PA_MODE_DECODE, "prefill": _l.PA_MODE_PREFILL}
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.float16:
+        return _l.PA_F16
+    if t == torch.float32:
+        return _l.PA_F32
+    raise _l.PaError(-1, f"dtype {t} is not supported (float16 or float32)")
+
+
+class _DevArray:
+    """A raw device pointer as something torch can wrap (for cache views)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class AttnEngine:
+    """The attention part of an engine: per-layer f16 K/V caches and the per-layer attention step."""
+
+    def __init__(self, cfg: AttnConfig, device: int = 0):
+        self.cfg, self.device = cfg, device
+        self.L = _l.load()
+        pc = _l.PaConfig(n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, n_rot=cfg.n_rot, rope_theta=cfg.rope_theta,
+                         rope_mode=_ROPE[cfg.rope_mode], act_dtype=_dt(cfg.act_dtype), max_cols=cfg.max_cols, splits=cfg.splits,
+                         flags=_l.PA_FLAG_FAST if cfg.fast else 0)
+        h = C.c_void_p()
+        self.ctx = None
+        self.layers: list[C.c_void_p] = []
+        self.L.check(self.L.pa_create(device, C.byref(pc), C.byref(h)))
+        self.ctx = h
+        try:
+            for _ in range(cfg.n_layers):
+                lh = C.c_void_p()
+                self.L.check(self.L.pa_layer_create(self.ctx, cfg.n_seqs, cfg.max_seq, C.byref(lh)), self.ctx)
+                self.layers.append(lh)
+        except Exception:
+            self.destroy()
+            raise
+
+    @classmethod
+    def create(cls, cfg: AttnConfig, device: int = 0) -> "AttnEngine":
+        return cls(cfg, device)
+
+    # ---- plumbing ----
+    def _st(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _ck(self, rc: int):
+        self.L.check(rc, self.ctx)
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t.data_ptr()) if t is not None else None
+
+    def destroy(self):
+        for lh in self.layers:
+            self.L.pa_layer_destroy(lh)
+        self.layers = []
+        if self.ctx:
+            self.L.pa_destroy(self.ctx)
+            self.ctx = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+    def sync(self):
+        self._ck(self.L.pa_sync(self.ctx, self._st()))
+
+    def reset(self):
+        self._ck(self.L.pa_reset(self.ctx))
+
+    def stats(self) -> dict:
+        s = _l.PaStats()
+        self._ck(self.L.pa_get_stats(self.ctx, C.byref(s)))
+        return {"kernel_launches": s.kernel_launches, "kv_bytes_streamed": s.kv_bytes_streamed, "calls": s.calls}
+
+    def timing_begin(self, max_events: int = 4096):
+        self._ck(self.L.pa_timing_begin(self.ctx, max_events))
+
+    def timing_end(self):
+        """(summed device ms of the core kernel, launches timed) since timing_begin."""
+        ms, n = C.c_double(), C.c_uint64()
+        self._ck(self.L.pa_timing_end(self.ctx, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def plan_splits(self, n_rows: int, n_items: int = 1) -> int:
+        return int(self.L.pa_plan_splits(self.ctx, n_rows, n_items))
+
+    def set_origin(self, li: int, origin: int):
+        """Layer li's caches hold global positions origin .. origin + max_seq - 1 (a KV-sequence shard)."""
+        self._ck(self.L.pa_layer_set_origin(self.layers[li], origin))
+
+    def cache(self, li: int, which: str) -> torch.Tensor:
+        """The K ("k") or V ("v") cache of layer li as a uint16 tensor [n_seqs, max_seq, kv_dim] (no copy)."""
+        ptr = self.L.pa_cache_ptr(self.layers[li], 0 if which == "k" else 1)
+        arr = _DevArray(ptr, (self.cfg.n_seqs, self.cfg.max_seq, self.cfg.kv_dim), "<i2")
+        return torch.as_tensor(arr, device=f"cuda:{self.device}")
+
+    # ---- the path, step by step ----
+    def rope(self, x: torch.Tensor, n_heads: int, pos: int, head_stride: int | None = None, cs_table: torch.Tensor | None = None) -> torch.Tensor:
+        """RoPE of x [n_cols, stride] -> float32 [n_cols, n_heads * head_dim]."""
+        n_cols = x.shape[0]
+        y = torch.empty((n_cols, n_heads * self.cfg.head_dim), dtype=torch.float32, device=x.device)
+        self._ck(self.L.pa_rope(self.ctx, self._p(x), x.stride(0), head_stride or self.cfg.head_dim, n_heads, pos, n_cols, self._p(cs_table),
+                                self._p(y), y.stride(0), self._st()))
+        return y
+
+    def kv_append(self, li: int, seq: int, pos: int, k: torch.Tensor, v: torch.Tensor):
+        assert k.dtype == v.dtype and k.stride(0) == v.stride(0)
+        self._ck(self.L.pa_kv_append(self.layers[li], seq, pos, k.shape[0], self._p(k), self._p(v), k.stride(0), _dt(k.dtype), self._st()))
+
+    def rope_append(self, li: int, seq: int, pos: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_head_stride: int | None = None,
+                    cs_table: torch.Tensor | None = None) -> torch.Tensor:
+        n_cols = q.shape[0]
+        q_rot = torch.empty((n_cols, self.cfg.q_dim), dtype=torch.float32, device=q.device)
+        self._ck(self.L.pa_rope_append(self.layers[li], seq, pos, n_cols, self._p(q), q.stride(0), q_head_stride or self.cfg.head_dim, self._p(k),
+                                       self._p(v), k.stride(0), self._p(cs_table), self._p(q_rot), self._st()))
+        return q_rot
+
+    def _items(self, items):
+        arr = (_l.PaItem * len(items))()
+        for i, (seq, pos, n_cols) in enumerate(items):
+            arr[i].seq, arr[i].pos, arr[i].n_cols = seq, pos, n_cols
+        return arr
+
+    def _gate(self, gate, gate_head_stride):
+        if gate is None:
+            return None, 0, 0
+        return self._p(gate), gate.stride(0), gate_head_stride or self.cfg.head_dim
+
+    def decode(self, li: int, items, q: torch.Tensor, gate: torch.Tensor | None = None, out: torch.Tensor | None = None,
+               q_head_stride: int | None = None, gate_head_stride: int | None = None) -> torch.Tensor:
+        """Decode / verify: items = [(seq, pos, n_cols)], q rotated, [total columns, stride]."""
+        total = sum(it[2] for it in items)
+        if out is None:
+            out = torch.empty((total, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_decode(self.layers[li], self._items(items), len(items), self._p(q), _dt(q.dtype), q.stride(0),
+                                  q_head_stride or self.cfg.head_dim, gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
+        return out
+
+    def decode_partial(self, li: int, items, q: torch.Tensor, q_head_stride: int | None = None) -> torch.Tensor:
+        """Per-(column, head) records over this cache's rows: float32 [rows*head_dim (o) + rows*2 (m, l)]."""
+        total = sum(it[2] for it in items)
+        rows = total * self.cfg.n_heads
+        part = torch.empty(rows * (self.cfg.head_dim + 2), dtype=torch.float32, device=q.device)
+        self._ck(self.L.pa_decode_partial(self.layers[li], self._items(items), len(items), self._p(q), _dt(q.dtype), q.stride(0),
+                                          q_head_stride or self.cfg.head_dim, self._p(part), self._st()))
+        return part
+
+    def merge(self, parts: torch.Tensor, n_cols: int, gate: torch.Tensor | None = None, out: torch.Tensor | None = None,
+              gate_head_stride: int | None = None) -> torch.Tensor:
+        """LSE merge of parts [n_parts, rows*(head_dim+2)] + gate."""
+        if out is None:
+            out = torch.empty((n_cols, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=parts.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_merge(self.ctx, self._p(parts), parts.shape[0], n_cols, gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
+        return out
+
+    def prefill(self, li: int, seq: int, pos: int, q: torch.Tensor, gate: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                q_head_stride: int | None = None, gate_head_stride: int | None = None) -> torch.Tensor:
+        n_cols = q.shape[0]
+        if out is None:
+            out = torch.empty((n_cols, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_prefill(self.layers[li], seq, pos, n_cols, self._p(q), _dt(q.dtype), q.stride(0), q_head_stride or self.cfg.head_dim,
+                                   gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
+        return out
+
+    def sigmoid_mul(self, a: torch.Tensor, g: torch.Tensor, g_head_stride: int | None = None):
+        self._ck(self.L.pa_sigmoid_mul(self.ctx, self._p(a), a.stride(0), self._p(g), g.stride(0), g_head_stride or self.cfg.head_dim,
+                                       a.shape[0], self._st()))
+
+    # ---- the path in one call ----
+    def encode_layer(self, li: int, pos: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None, seq: int = 0, mode: str = "auto", q_head_stride: int | None = None,
+                     gate_head_stride: int | None = None, cs_table: torch.Tensor | None = None) -> torch.Tensor:
+        """RoPE + append + attend + gate for q.shape[0] new tokens at positions pos.. (device tensors).
+
+        One token is the attention block of _encodeLayerR (engine/qwen35.js:1598-1640); several are _encAttnGlue +
+        _encAttnCore (engine/qwen35.js:2473-2517): all columns' K/V are appended before any column attends."""
+        n_cols = q.shape[0]
+        if out is None:
+            out = torch.empty((n_cols, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_attn_layer(self.layers[li], seq, pos, n_cols, _MODE[mode], self._p(q), q.stride(0), q_head_stride or self.cfg.head_dim,
+                                      self._p(k), self._p(v), k.stride(0), gp, gcs, ghs, self._p(cs_table), self._p(out), out.stride(0), self._st()))
+        return out
+
+    def encode_layer_host(self, li: int, pos: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor,
+                          seq: int = 0, mode: str = "auto", q_head_stride: int | None = None, gate_head_stride: int | None = None,
+                          cs_table: torch.Tensor | None = None) -> torch.Tensor:
+        """The same with HOST tensors (pinned or pageable): copies in, runs, copies out, returns when done."""
+        assert not q.is_cuda and not out.is_cuda
+        n_cols = q.shape[0]
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_attn_layer_host(self.layers[li], seq, pos, n_cols, _MODE[mode], self._p(q), q.stride(0), q_head_stride or self.cfg.head_dim,
+                                           self._p(k), self._p(v), k.stride(0), gp, gcs, ghs, self._p(cs_table), self._p(out), out.stride(0), self._st()))
+        return out

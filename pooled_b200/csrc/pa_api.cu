@@ -1,0 +1,607 @@
+// C ABI of libpooled_attn.so: contexts, layer caches, tensor maps and the entry points declared in
+// include/pooled_attn.h.  No exceptions cross the boundary; every failure is a status code plus a message.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "pa_common.cuh"
+
+#include "pa_params.cuh"
+
+namespace pa {
+cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, int nt, cudaStream_t st);
+cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, cudaStream_t st);
+cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st);
+cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
+int prefill_supported(const pa_ctx* ctx);
+cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, cudaStream_t st);
+}  // namespace pa
+
+using namespace pa;
+
+static thread_local std::string g_err;  // for failures before a context exists
+
+static int fail(pa_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf; else g_err = buf;
+  return code;
+}
+#define CU_TRY(ctx, expr)                                                                         \
+  do {                                                                                            \
+    cudaError_t e_ = (expr);                                                                      \
+    if (e_ != cudaSuccess) {                                                                      \
+      (ctx)->failed = true;                                                                       \
+      return fail((ctx), PA_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));               \
+    }                                                                                             \
+  } while (0)
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn get_encode() {
+  static encode_tiled_fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<encode_tiled_fn>(p);
+  }
+  return fn;
+}
+
+// View of an f16 cache [rows][kv_dim] as {64 elements, rows, kv_dim/64 chunks}; a box of {64, box_rows,
+// head_dim/64} lands in shared memory as [chunk][row][128 bytes] with the 128-byte swizzle.
+static int make_cache_map(pa_ctx* ctx, CUtensorMap* tm, void* base, uint64_t rows, uint32_t kv_dim, uint32_t hd, uint32_t box_rows) {
+  encode_tiled_fn enc = get_encode();
+  if (!enc) return fail(ctx, PA_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {64, rows, kv_dim / 64};
+  cuuint64_t strides[2] = {(cuuint64_t)kv_dim * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, hd / 64};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ctx, PA_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return PA_OK;
+}
+
+static uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+// ------------------------------------------------------------------------------ host mirrors --
+
+extern "C" uint32_t pa_dec_config(uint32_t head_dim, uint32_t G, uint32_t n_kv, uint32_t splits) {
+  if (head_dim != 256 || G < 1 || G > 8 || n_kv < 1) return 0;
+  if (splits > 0) return splits;
+  uint32_t s = 256 / n_kv;
+  return s > 16 ? s : 16;
+}
+extern "C" uint32_t pa_dec_split_len(uint32_t s, uint32_t S) {
+  uint32_t l = ceil_div(ceil_div(s, S), 64) * 64;
+  return l > 64 ? l : 64;
+}
+extern "C" uint32_t pa_dec_splits(uint32_t s, uint32_t S) { return ceil_div(s, pa_dec_split_len(s, S)); }
+extern "C" uint32_t pa_tile_split_len(uint32_t seq_end, uint32_t fa_split, uint32_t fa_splits, uint32_t target) {
+  auto up64 = [](uint32_t x) { return ceil_div(x, 64) * 64; };
+  if (target < 1) target = 1;
+  uint32_t m = 64;
+  uint32_t a = up64(ceil_div(seq_end, target)), b = up64(ceil_div(seq_end, fa_splits));
+  if (a > m) m = a;
+  if (b > m) m = b;
+  return m < fa_split ? m : fa_split;
+}
+
+// Splits per (item, kv head): enough CTAs to give every SM one, never more than one wave, at least two
+// 64-row tiles each.  Depends on the call's longest column and item count only.
+static uint32_t plan_splits(const pa_ctx* ctx, uint32_t n_rows, uint32_t n_items, uint32_t total_cols = 0) {
+  const uint32_t tiles = ceil_div(n_rows, 64);
+  if (!total_cols) total_cols = n_items;
+  uint32_t want = ctx->cfg.splits ? ctx->cfg.splits : (uint32_t)ctx->sm_count / (ctx->cfg.n_kv_heads * n_items);
+  if (want < 1) want = 1;
+  uint32_t cap = tiles / 2;
+  if (cap < 1) cap = 1;
+  if (want > cap) want = cap;
+  if (want > ctx->max_splits) want = ctx->max_splits;
+  const uint32_t fit = (uint32_t)(ctx->part_slots / ((size_t)total_cols * ctx->cfg.n_heads));
+  if (want > fit) want = fit;
+  return want;
+}
+extern "C" uint32_t pa_plan_splits(pa_ctx* ctx, uint32_t n_rows, uint32_t n_items) {
+  if (!ctx || n_items < 1) return 0;
+  return plan_splits(ctx, n_rows, n_items);
+}
+
+// ------------------------------------------------------------------------------ lifetime --
+
+extern "C" const char* pa_version(void) { return "pooled_attn 0.1 (sm_100a)"; }
+extern "C" const char* pa_last_error(pa_ctx* ctx) { return ctx ? ctx->err.c_str() : g_err.c_str(); }
+
+extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
+  if (!cfg || !out) return fail(nullptr, PA_EINVAL, "pa_create: null argument");
+  *out = nullptr;
+  if (cfg->n_heads < 1 || cfg->n_kv_heads < 1 || cfg->n_heads % cfg->n_kv_heads)
+    return fail(nullptr, PA_EINVAL, "pa_create: n_heads %u must be a multiple of n_kv_heads %u", cfg->n_heads, cfg->n_kv_heads);
+  if (cfg->head_dim != 128 && cfg->head_dim != 256)
+    return fail(nullptr, PA_EUNSUPPORTED, "pa_create: head_dim %u is not supported (128 or 256)", cfg->head_dim);
+  if (cfg->n_rot > cfg->head_dim || (cfg->n_rot & 1) || (cfg->rope_mode != PA_ROPE_NONE && cfg->n_rot < 2))
+    return fail(nullptr, PA_EINVAL, "pa_create: n_rot %u must be even and at most head_dim", cfg->n_rot);
+  if (cfg->rope_mode > PA_ROPE_TABLE || cfg->act_dtype > PA_F16) return fail(nullptr, PA_EINVAL, "pa_create: bad rope_mode or act_dtype");
+  if (cfg->max_cols < 1) return fail(nullptr, PA_EINVAL, "pa_create: max_cols must be at least 1");
+  int n_dev = 0;
+  if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev)
+    return fail(nullptr, PA_ECUDA, "pa_create: CUDA device %d is not available (%d visible); there is no CPU fallback", device, n_dev);
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return fail(nullptr, PA_ECUDA, "pa_create: cannot query device %d", device);
+  if (prop.major != 10)
+    return fail(nullptr, PA_EUNSUPPORTED, "pa_create: device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+  pa_ctx* ctx = new (std::nothrow) pa_ctx();
+  if (!ctx) return fail(nullptr, PA_ENOMEM, "pa_create: out of host memory");
+  ctx->device = device;
+  ctx->cfg = *cfg;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->smem_optin = (int)prop.sharedMemPerBlockOptin;
+  ctx->G = cfg->n_heads / cfg->n_kv_heads;
+  ctx->q_dim = cfg->n_heads * cfg->head_dim;
+  ctx->kv_dim = cfg->n_kv_heads * cfg->head_dim;
+  ctx->max_splits = 256;
+  auto bail = [&](int code, const char* what, cudaError_t e) {
+    std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
+    pa_destroy(ctx);
+    return fail(nullptr, code, "%s", msg.c_str());
+  };
+  cudaError_t e;
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return bail(PA_ECUDA, "cudaSetDevice", e);
+  const uint32_t half = cfg->n_rot / 2;
+  if (half) {
+    double host[128];
+    for (uint32_t i = 0; i < half; ++i) host[i] = pow(cfg->rope_theta, -(2.0 * (double)i) / (double)cfg->n_rot);
+    if ((e = cudaMalloc(&ctx->inv_freq, half * sizeof(double))) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(inv_freq)", e);
+    if ((e = cudaMemcpy(ctx->inv_freq, host, half * sizeof(double), cudaMemcpyHostToDevice)) != cudaSuccess) return bail(PA_ECUDA, "cudaMemcpy(inv_freq)", e);
+  }
+  if ((e = cudaMalloc(&ctx->q_rot, (size_t)cfg->max_cols * cfg->n_heads * cfg->head_dim * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(q_rot)", e);
+  // split partials: one (o, m, l) record per (query row, split).  A call uses rows * splits of them, about
+  // 64 rows x one CTA per SM; the split planner keeps every call inside this capacity.
+  ctx->part_slots = 16384;
+  if ((e = cudaMalloc(&ctx->part_o, ctx->part_slots * cfg->head_dim * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(part_o)", e);
+  if ((e = cudaMalloc(&ctx->part_ml, ctx->part_slots * 2 * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(part_ml)", e);
+  if ((e = cudaMalloc(&ctx->dev_err, 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(err)", e);
+  if ((e = cudaMemset(ctx->dev_err, 0, 4)) != cudaSuccess) return bail(PA_ECUDA, "cudaMemset(err)", e);
+  if ((e = cudaMallocHost(&ctx->host_err, 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMallocHost(err)", e);
+  *ctx->host_err = 0;
+  *out = ctx;
+  return PA_OK;
+}
+
+extern "C" int pa_destroy(pa_ctx* ctx) {
+  if (!ctx) return PA_OK;
+  cudaSetDevice(ctx->device);
+  cudaFree(ctx->inv_freq); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err);
+  cudaFree(ctx->stage_dev);
+  for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
+  if (ctx->host_err) cudaFreeHost(ctx->host_err);
+  if (ctx->stage_host) cudaFreeHost(ctx->stage_host);
+  delete ctx;
+  return PA_OK;
+}
+
+extern "C" int pa_layer_create(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, pa_layer** out) {
+  if (!ctx || !out) return fail(ctx, PA_EINVAL, "pa_layer_create: null argument");
+  *out = nullptr;
+  if (n_seqs < 1 || max_seq < 1) return fail(ctx, PA_EINVAL, "pa_layer_create: n_seqs and max_seq must be positive");
+  const uint64_t rows = (uint64_t)n_seqs * max_seq;
+  if (rows >= (1ull << 31)) return fail(ctx, PA_EUNSUPPORTED, "pa_layer_create: %llu cache rows exceed the 2^31 row limit of one layer", (unsigned long long)rows);
+  pa_layer* L = new (std::nothrow) pa_layer();
+  if (!L) return fail(ctx, PA_ENOMEM, "pa_layer_create: out of host memory");
+  L->ctx = ctx; L->n_seqs = n_seqs; L->max_seq = max_seq;
+  cudaSetDevice(ctx->device);
+  const size_t bytes = rows * ctx->kv_dim * 2;
+  size_t free_b = 0, total_b = 0;
+  cudaMemGetInfo(&free_b, &total_b);
+  if (cudaMalloc(&L->k, bytes) != cudaSuccess || cudaMalloc(&L->v, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(L->k);
+    delete L;
+    return fail(ctx, PA_ENOMEM, "context %u x %u sequences needs two %.0f MiB KV buffers for this layer; the device has %.0f MiB free (ask for a shorter context or fewer sequences)",
+                max_seq, n_seqs, bytes / 1048576.0, free_b / 1048576.0);
+  }
+  int rc = make_cache_map(ctx, &L->tm_k64, L->k, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
+  if (!rc) rc = make_cache_map(ctx, &L->tm_v64, L->v, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
+  if (!rc) rc = make_cache_map(ctx, &L->tm_k128, L->k, rows, ctx->kv_dim, ctx->cfg.head_dim, 128);
+  if (!rc) rc = make_cache_map(ctx, &L->tm_v128, L->v, rows, ctx->kv_dim, ctx->cfg.head_dim, 128);
+  if (rc) { cudaFree(L->k); cudaFree(L->v); delete L; return rc; }
+  *out = L;
+  return PA_OK;
+}
+
+extern "C" int pa_layer_destroy(pa_layer* L) {
+  if (!L) return PA_OK;
+  cudaSetDevice(L->ctx->device);
+  cudaFree(L->k); cudaFree(L->v);
+  delete L;
+  return PA_OK;
+}
+
+extern "C" int pa_layer_set_origin(pa_layer* L, uint32_t origin) {
+  if (!L) return PA_EINVAL;
+  L->origin = origin;
+  return PA_OK;
+}
+
+extern "C" void* pa_cache_ptr(pa_layer* L, int which) { return L ? (which ? (void*)L->v : (void*)L->k) : nullptr; }
+
+extern "C" int pa_sync(pa_ctx* ctx, void* stream) {
+  if (!ctx) return PA_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_TRY(ctx, cudaMemcpyAsync(ctx->host_err, ctx->dev_err, 4, cudaMemcpyDeviceToHost, st));
+  CU_TRY(ctx, cudaStreamSynchronize(st));
+  if (*ctx->host_err) {
+    ctx->failed = true;
+    return fail(ctx, PA_ETIMEOUT, "a device-side wait ran out (code %u); call pa_reset() before the next step", *ctx->host_err);
+  }
+  return PA_OK;
+}
+
+extern "C" int pa_reset(pa_ctx* ctx) {
+  if (!ctx) return PA_EINVAL;
+  cudaGetLastError();
+  if (cudaMemset(ctx->dev_err, 0, 4) != cudaSuccess) return fail(ctx, PA_ECUDA, "pa_reset: the device does not answer");
+  *ctx->host_err = 0;
+  ctx->failed = false;
+  ctx->err.clear();
+  return PA_OK;
+}
+
+extern "C" int pa_get_stats(pa_ctx* ctx, pa_stats* out) {
+  if (!ctx || !out) return PA_EINVAL;
+  *out = ctx->stats;
+  return PA_OK;
+}
+
+extern "C" int pa_timing_begin(pa_ctx* ctx, uint32_t max_events) {
+  if (!ctx || max_events < 1) return PA_EINVAL;
+  cudaSetDevice(ctx->device);
+  while (ctx->ev.size() < 2 * (size_t)max_events) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return fail(ctx, PA_ECUDA, "pa_timing_begin: cudaEventCreate failed");
+    ctx->ev.push_back(e);
+  }
+  ctx->ev_used = 0;
+  ctx->timing = true;
+  return PA_OK;
+}
+extern "C" int pa_timing_end(pa_ctx* ctx, double* core_ms, uint64_t* core_launches) {
+  if (!ctx || !core_ms || !core_launches) return PA_EINVAL;
+  ctx->timing = false;
+  double total = 0;
+  for (size_t i = 0; i + 1 < ctx->ev_used; i += 2) {
+    CU_TRY(ctx, cudaEventSynchronize(ctx->ev[i + 1]));
+    float ms = 0;
+    CU_TRY(ctx, cudaEventElapsedTime(&ms, ctx->ev[i], ctx->ev[i + 1]));
+    total += ms;
+  }
+  *core_ms = total;
+  *core_launches = ctx->ev_used / 2;
+  ctx->ev_used = 0;
+  return PA_OK;
+}
+static inline void timing_mark(pa_ctx* ctx, cudaStream_t st, int end) {
+  if (!ctx->timing) return;
+  if (!end && ctx->ev_used + 2 > ctx->ev.size()) { ctx->timing = false; return; }
+  cudaEventRecord(ctx->ev[ctx->ev_used++], st);
+}
+
+extern "C" int pa_alloc(pa_ctx* ctx, size_t bytes, void** p) {
+  if (!ctx || !p) return PA_EINVAL;
+  if (cudaMalloc(p, bytes) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_alloc: %zu bytes do not fit on the device", bytes); }
+  return PA_OK;
+}
+extern "C" int pa_free(pa_ctx* ctx, void* p) { (void)ctx; cudaFree(p); return PA_OK; }
+extern "C" int pa_alloc_host(pa_ctx* ctx, size_t bytes, void** p) {
+  if (!ctx || !p) return PA_EINVAL;
+  if (cudaMallocHost(p, bytes) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_alloc_host: cannot pin %zu bytes", bytes); }
+  return PA_OK;
+}
+extern "C" int pa_free_host(pa_ctx* ctx, void* p) { (void)ctx; cudaFreeHost(p); return PA_OK; }
+extern "C" int pa_upload(pa_ctx* ctx, void* d, const void* h, size_t n, void* stream) {
+  if (!ctx) return PA_EINVAL;
+  CU_TRY(ctx, cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return PA_OK;
+}
+extern "C" int pa_download(pa_ctx* ctx, void* h, const void* d, size_t n, void* stream) {
+  if (!ctx) return PA_EINVAL;
+  CU_TRY(ctx, cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+// ------------------------------------------------------------------------------ the path --
+
+#define GUARD(ctx)                                                                                       \
+  do {                                                                                                   \
+    if (!(ctx)) return PA_EINVAL;                                                                        \
+    if ((ctx)->failed) return fail((ctx), PA_ESTATE, "an earlier step failed (%s); call pa_reset() first", (ctx)->err.c_str()); \
+  } while (0)
+
+// own_rows: the call writes or reads rows pos .. pos+n_cols-1 themselves, which must lie inside this layer's cache
+// (for a shard: inside [origin, origin + max_seq)); otherwise any position at or past the origin's sequence is fine
+static int check_cols(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const char* who, bool own_rows = true) {
+  pa_ctx* ctx = L->ctx;
+  if (seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "%s: sequence %u of %u", who, seq, L->n_seqs);
+  if (n_cols < 1 || n_cols > ctx->cfg.max_cols) return fail(ctx, PA_EINVAL, "%s: %u columns, the context was created for at most %u", who, n_cols, ctx->cfg.max_cols);
+  if ((uint64_t)pos + n_cols >= (1ull << 31)) return fail(ctx, PA_EINVAL, "%s: position %u is out of range", who, pos);
+  if (own_rows && (pos < L->origin || (uint64_t)pos + n_cols > (uint64_t)L->origin + L->max_seq))
+    return fail(ctx, PA_EINVAL, "%s: positions %u..%u pass the layer's max_seq %u (rows %u..%u)", who, pos, pos + n_cols - 1, L->max_seq,
+                L->origin, L->origin + L->max_seq - 1);
+  return PA_OK;
+}
+
+static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
+                            uint32_t q_heads, float* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
+                            uint32_t mode, int in_f16, cudaStream_t st) {
+  RopeParams p{};
+  p.q = q; p.q_col_stride = qcs; p.q_head_stride = qhs; p.q_heads = q_heads; p.q_out = q_out; p.q_out_col_stride = q_out_cs;
+  p.k = k; p.v = v; p.kv_col_stride = kvcs; p.kv_heads = ctx->cfg.n_kv_heads;
+  if (L) { p.k_cache = L->k; p.v_cache = L->v; p.cache_row0 = (uint64_t)seq * L->max_seq + (pos - L->origin); }
+  p.hd = ctx->cfg.head_dim; p.n_rot = ctx->cfg.n_rot; p.pos = pos; p.mode = mode; p.in_f16 = in_f16;
+  p.inv_freq = ctx->inv_freq; p.cs_table = cs_table;
+  if (mode == PA_ROPE_TABLE && !cs_table) return fail(ctx, PA_EINVAL, "rope: PA_ROPE_TABLE needs a cos/sin table");
+  CU_TRY(ctx, launch_rope_append(p, n_cols, st));
+  ctx->stats.kernel_launches++;
+  return PA_OK;
+}
+
+extern "C" int pa_rope(pa_ctx* ctx, const void* x, uint64_t col_stride, uint64_t head_stride, uint32_t n_heads_x, uint32_t pos, uint32_t n_cols,
+                       const float* cs_table, float* y, uint64_t y_col_stride, void* stream) {
+  GUARD(ctx);
+  if (!x || !y || n_cols < 1 || n_heads_x < 1) return fail(ctx, PA_EINVAL, "pa_rope: null or empty argument");
+  cudaSetDevice(ctx->device);
+  return rope_append_impl(nullptr, ctx, 0, pos, n_cols, x, col_stride, head_stride, n_heads_x, y, y_col_stride, nullptr, nullptr, 0, cs_table,
+                          ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, (cudaStream_t)stream);
+}
+
+extern "C" int pa_kv_append(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* k, const void* v, uint64_t col_stride, int dtype,
+                            void* stream) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (!k || !v) return fail(ctx, PA_EINVAL, "pa_kv_append: null k or v");
+  if (int rc = check_cols(L, seq, pos, n_cols, "pa_kv_append")) return rc;
+  cudaSetDevice(ctx->device);
+  return rope_append_impl(L, ctx, seq, pos, n_cols, nullptr, 0, 0, 0, nullptr, 0, k, v, col_stride, nullptr, PA_ROPE_NONE, dtype == PA_F16,
+                          (cudaStream_t)stream);
+}
+
+extern "C" int pa_rope_append(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t q_col_stride, uint64_t q_head_stride,
+                              const void* k, const void* v, uint64_t kv_col_stride, const float* cs_table, float* q_rot, void* stream) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (!q || !k || !v) return fail(ctx, PA_EINVAL, "pa_rope_append: null q, k or v");
+  if (int rc = check_cols(L, seq, pos, n_cols, "pa_rope_append")) return rc;
+  cudaSetDevice(ctx->device);
+  return rope_append_impl(L, ctx, seq, pos, n_cols, q, q_col_stride, q_head_stride, ctx->cfg.n_heads, q_rot ? q_rot : ctx->q_rot, ctx->q_dim, k, v,
+                          kv_col_stride, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, (cudaStream_t)stream);
+}
+
+static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, ItemList* il, uint32_t* total_cols, uint32_t* max_rows, uint32_t* max_cols,
+                       uint64_t* kv_bytes, const char* who, bool sharded_ok) {
+  pa_ctx* ctx = L->ctx;
+  if (!items || n_items < 1 || n_items > (uint32_t)kMaxItems) return fail(ctx, PA_EINVAL, "%s: between 1 and %d items per call", who, kMaxItems);
+  uint32_t cols = 0, mr = 0, mc = 0;
+  uint64_t bytes = 0;
+  for (uint32_t i = 0; i < n_items; ++i) {
+    if (int rc = check_cols(L, items[i].seq, items[i].pos, items[i].n_cols, who, sharded_ok ? false : true)) return rc;
+    if (items[i].n_cols * ctx->G > (uint32_t)kMaxRows)
+      return fail(ctx, PA_EUNSUPPORTED, "%s: %u columns x %u heads per kv head exceed the %d query rows one pass carries; use pa_prefill", who,
+                  items[i].n_cols, ctx->G, kMaxRows);
+    const int64_t end = (int64_t)items[i].pos + items[i].n_cols - (int64_t)L->origin;
+    const uint32_t rows = (uint32_t)(end < 0 ? 0 : end > (int64_t)L->max_seq ? L->max_seq : end);
+    il->seq[i] = items[i].seq; il->n_cols[i] = items[i].n_cols; il->col0[i] = cols;
+    il->lim0[i] = (int32_t)((int64_t)items[i].pos + 1 - (int64_t)L->origin); il->n_rows[i] = rows;
+    cols += items[i].n_cols;
+    if (rows > mr) mr = rows;
+    if (items[i].n_cols > mc) mc = items[i].n_cols;
+    bytes += 2ull * rows * ctx->kv_dim * 2;
+  }
+  if (cols > ctx->cfg.max_cols || (size_t)cols * ctx->cfg.n_heads > ctx->part_slots)
+    return fail(ctx, PA_EINVAL, "%s: %u columns in one call exceed the context's max_cols %u", who, cols, ctx->cfg.max_cols);
+  *total_cols = cols; *max_rows = mr; *max_cols = mc; *kv_bytes = bytes;
+  return PA_OK;
+}
+
+static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
+                       uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who) {
+  pa_ctx* ctx = L->ctx;
+  if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
+  if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
+  DecodeParams p{};
+  uint32_t total_cols, max_rows, max_cols; uint64_t kv_bytes;
+  // partial records may come from a shard that holds only part (or none) of the rows the columns see
+  if (int rc = build_items(L, items, n_items, &p.items, &total_cols, &max_rows, &max_cols, &kv_bytes, who, partial != nullptr)) return rc;
+  cudaSetDevice(ctx->device);
+  const uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols);
+  p.q = q; p.q_f16 = q_dtype == PA_F16; p.q_col_stride = qcs; p.q_head_stride = qhs;
+  p.part_o = ctx->part_o; p.part_ml = ctx->part_ml; p.n_splits = ns;
+  p.n_heads = ctx->cfg.n_heads; p.G = ctx->G; p.max_seq = L->max_seq;
+  p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)ctx->cfg.head_dim));
+  p.err = ctx->dev_err;
+  const int nt = (int)ceil_div(max_cols * ctx->G, 8);
+  timing_mark(ctx, st, 0);
+  if (max_rows > 0) CU_TRY(ctx, launch_decode(L, p, dim3(ns, ctx->cfg.n_kv_heads, n_items), nt, st));
+  timing_mark(ctx, st, 1);
+  CombineParams c{};
+  c.o = ctx->part_o; c.ml = ctx->part_ml;
+  c.o_row_stride = (uint64_t)ns * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
+  c.ml_row_stride = (uint64_t)ns * 2; c.ml_part_stride = 2;
+  c.n_heads = ctx->cfg.n_heads; c.fixed_parts = 0; c.n_splits = ns;
+  c.gate = gate; c.gate_col_stride = gcs; c.gate_head_stride = ghs; c.out = out; c.out_col_stride = ocs;
+  c.act_f16 = ctx->cfg.act_dtype == PA_F16;
+  c.partial_out = partial; c.partial_rows = (uint64_t)total_cols * ctx->cfg.n_heads;
+  c.items = p.items; c.n_items = n_items;
+  CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
+  ctx->stats.kernel_launches += 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
+  return PA_OK;
+}
+
+extern "C" int pa_decode(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t q_col_stride, uint64_t q_head_stride,
+                         const void* gate, uint64_t gate_col_stride, uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  if (!out) return fail(L->ctx, PA_EINVAL, "pa_decode: null out");
+  return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
+                     (cudaStream_t)stream, "pa_decode");
+}
+
+extern "C" int pa_decode_partial(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t q_col_stride,
+                                 uint64_t q_head_stride, float* partial, void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  if (!partial) return fail(L->ctx, PA_EINVAL, "pa_decode_partial: null partial");
+  return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, nullptr, 0, 0, nullptr, 0, partial, (cudaStream_t)stream,
+                     "pa_decode_partial");
+}
+
+extern "C" int pa_merge(pa_ctx* ctx, const float* parts, uint32_t n_parts, uint32_t n_cols, const void* gate, uint64_t gate_col_stride,
+                        uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream) {
+  GUARD(ctx);
+  if (!parts || !out || n_parts < 1 || n_parts > 512 || n_cols < 1) return fail(ctx, PA_EINVAL, "pa_merge: null argument, or n_parts outside 1..512");
+  cudaSetDevice(ctx->device);
+  const uint64_t rows = (uint64_t)n_cols * ctx->cfg.n_heads, hd = ctx->cfg.head_dim;
+  CombineParams c{};
+  c.o = parts; c.ml = parts + rows * hd;
+  c.o_row_stride = hd; c.o_part_stride = rows * (hd + 2);
+  c.ml_row_stride = 2; c.ml_part_stride = rows * (hd + 2);
+  c.n_heads = ctx->cfg.n_heads; c.fixed_parts = n_parts; c.n_splits = 1;
+  c.gate = gate; c.gate_col_stride = gate_col_stride; c.gate_head_stride = gate_head_stride; c.out = out; c.out_col_stride = out_col_stride;
+  c.act_f16 = ctx->cfg.act_dtype == PA_F16;
+  CU_TRY(ctx, launch_combine((int)hd, c, (uint32_t)rows, (cudaStream_t)stream));
+  ctx->stats.kernel_launches++;
+  return PA_OK;
+}
+
+static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
+                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, cudaStream_t st) {
+  pa_ctx* ctx = L->ctx;
+  if (!q || !out) return fail(ctx, PA_EINVAL, "pa_prefill: null q or out");
+  if (int rc = check_cols(L, seq, pos, n_cols, "pa_prefill")) return rc;
+  if (!prefill_supported(ctx)) return fail(ctx, PA_EUNSUPPORTED, "pa_prefill: head_dim %u is outside the tiled prefill kernel's shapes", ctx->cfg.head_dim);
+  if ((qcs & 3) || (qhs & 3) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "pa_prefill: q strides must be multiples of 4 elements and q 16-byte aligned");
+  cudaSetDevice(ctx->device);
+  PrefillParams p{};
+  p.q = q; p.q_f16 = q_dtype == PA_F16; p.q_col_stride = qcs; p.q_head_stride = qhs;
+  p.gate = gate; p.gate_col_stride = gcs; p.gate_head_stride = ghs; p.out = out; p.out_col_stride = ocs;
+  p.act_f16 = ctx->cfg.act_dtype == PA_F16;
+  p.seq = seq; p.pos = pos - L->origin; p.n_cols = n_cols; p.n_heads = ctx->cfg.n_heads; p.G = ctx->G; p.max_seq = L->max_seq;
+  p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)ctx->cfg.head_dim));
+  p.err = ctx->dev_err;
+  timing_mark(ctx, st, 0);
+  CU_TRY(ctx, launch_prefill(L, p, st));
+  timing_mark(ctx, st, 1);
+  ctx->stats.kernel_launches++; ctx->stats.calls++;
+  ctx->stats.kv_bytes_streamed += 2ull * (pos + n_cols) * ctx->kv_dim * 2;
+  return PA_OK;
+}
+
+extern "C" int pa_prefill(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, int q_dtype, uint64_t q_col_stride,
+                          uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride, uint64_t gate_head_stride, void* out, uint64_t out_col_stride,
+                          void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  return prefill_impl(L, seq, pos, n_cols, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride,
+                      (cudaStream_t)stream);
+}
+
+extern "C" int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const void* g, uint64_t g_col_stride, uint64_t g_head_stride, uint32_t n_cols,
+                              void* stream) {
+  GUARD(ctx);
+  if (!a || !g || n_cols < 1) return fail(ctx, PA_EINVAL, "pa_sigmoid_mul: null or empty argument");
+  cudaSetDevice(ctx->device);
+  SigmoidParams p{};
+  p.a = a; p.a_col_stride = a_col_stride; p.g = g; p.g_col_stride = g_col_stride; p.g_head_stride = g_head_stride;
+  p.n_heads = ctx->cfg.n_heads; p.hd = ctx->cfg.head_dim; p.f16 = ctx->cfg.act_dtype == PA_F16;
+  CU_TRY(ctx, launch_sigmoid_mul(p, n_cols, (cudaStream_t)stream));
+  ctx->stats.kernel_launches++;
+  return PA_OK;
+}
+
+// ------------------------------------------------------------------------------ one call --
+
+static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t qcs, uint64_t qhs, const void* k,
+                      const void* v, uint64_t kvcs, const void* gate, uint64_t gcs, uint64_t ghs, const float* cs_table, void* out, uint64_t ocs,
+                      cudaStream_t st) {
+  pa_ctx* ctx = L->ctx;
+  if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer: null q, k, v or out");
+  if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer")) return rc;
+  cudaSetDevice(ctx->device);
+  if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
+                                ctx->cfg.act_dtype == PA_F16, st))
+    return rc;
+  // the decode / verify kernel carries at most 64 query rows per kv head; wider passes are prefill chunks
+  // (the reference takes the tiled kernel on full-width non-verify passes, engine/qwen35.js:2489)
+  bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
+  if (prefill)
+    return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
+  pa_item it{seq, pos, n_cols, 0};
+  return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer");
+}
+
+extern "C" int pa_attn_layer(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t q_col_stride,
+                             uint64_t q_head_stride, const void* k, const void* v, uint64_t kv_col_stride, const void* gate, uint64_t gate_col_stride,
+                             uint64_t gate_head_stride, const float* cs_table, void* out, uint64_t out_col_stride, void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  return layer_impl(L, seq, pos, n_cols, mode, q, q_col_stride, q_head_stride, k, v, kv_col_stride, gate, gate_col_stride, gate_head_stride, cs_table, out,
+                    out_col_stride, (cudaStream_t)stream);
+}
+
+extern "C" int pa_attn_layer_host(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t qcs, uint64_t qhs,
+                                  const void* k, const void* v, uint64_t kvcs, const void* gate, uint64_t gcs, uint64_t ghs, const float* cs_table,
+                                  void* out, uint64_t ocs, void* stream) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer_host: null q, k, v or out");
+  if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer_host")) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaSetDevice(ctx->device);
+  const size_t es = ctx->cfg.act_dtype == PA_F16 ? 2 : 4;
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  // bytes of each host array as the strides describe it (last column only up to its last element)
+  const size_t q_last = (size_t)(ctx->cfg.n_heads - 1) * qhs + ctx->cfg.head_dim;
+  const size_t qb = up(((size_t)(n_cols - 1) * qcs + q_last) * es), kb = up(((size_t)(n_cols - 1) * kvcs + ctx->kv_dim) * es);
+  const size_t g_last = (size_t)(ctx->cfg.n_heads - 1) * ghs + ctx->cfg.head_dim;
+  const size_t gb = gate ? up(((size_t)(n_cols - 1) * gcs + g_last) * es) : 0;
+  const size_t ob = up(((size_t)(n_cols - 1) * ocs + ctx->q_dim) * es);
+  const size_t tb = cs_table ? up((size_t)n_cols * ctx->cfg.n_rot * 4) : 0;
+  // a gate that lives inside the q buffer (interleaved q_full) is not copied twice
+  const uint8_t* qh = (const uint8_t*)q; const uint8_t* gh = (const uint8_t*)gate;
+  const bool gate_in_q = gate && gh >= qh && gh < qh + qb;
+  const size_t need = qb + 2 * kb + (gate_in_q ? 0 : gb) + ob + tb;
+  if (need > ctx->stage_bytes) {
+    CU_TRY(ctx, cudaStreamSynchronize(st));
+    cudaFree(ctx->stage_dev); ctx->stage_dev = nullptr; ctx->stage_bytes = 0;
+    if (cudaMalloc(&ctx->stage_dev, need) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_attn_layer_host: %zu staging bytes do not fit on the device", need); }
+    ctx->stage_bytes = need;
+  }
+  uint8_t* d = (uint8_t*)ctx->stage_dev;
+  uint8_t *dq = d, *dk = dq + qb, *dv = dk + kb, *dg = dv + kb, *dout = dg + (gate_in_q ? 0 : gb), *dt = dout + ob;
+  CU_TRY(ctx, cudaMemcpyAsync(dq, q, ((size_t)(n_cols - 1) * qcs + q_last) * es, cudaMemcpyHostToDevice, st));
+  CU_TRY(ctx, cudaMemcpyAsync(dk, k, ((size_t)(n_cols - 1) * kvcs + ctx->kv_dim) * es, cudaMemcpyHostToDevice, st));
+  CU_TRY(ctx, cudaMemcpyAsync(dv, v, ((size_t)(n_cols - 1) * kvcs + ctx->kv_dim) * es, cudaMemcpyHostToDevice, st));
+  const void* dgate = nullptr;
+  if (gate_in_q) dgate = dq + (gh - qh);
+  else if (gate) { CU_TRY(ctx, cudaMemcpyAsync(dg, gate, ((size_t)(n_cols - 1) * gcs + g_last) * es, cudaMemcpyHostToDevice, st)); dgate = dg; }
+  if (cs_table) CU_TRY(ctx, cudaMemcpyAsync(dt, cs_table, (size_t)n_cols * ctx->cfg.n_rot * 4, cudaMemcpyHostToDevice, st));
+  if (int rc = layer_impl(L, seq, pos, n_cols, mode, dq, qcs, qhs, dk, dv, kvcs, dgate, gcs, ghs, cs_table ? (const float*)dt : nullptr, dout, ocs, st)) return rc;
+  if (ocs == ctx->q_dim) {
+    CU_TRY(ctx, cudaMemcpyAsync(out, dout, (size_t)n_cols * ctx->q_dim * es, cudaMemcpyDeviceToHost, st));
+  } else {
+    CU_TRY(ctx, cudaMemcpy2DAsync(out, ocs * es, dout, ocs * es, ctx->q_dim * es, n_cols, cudaMemcpyDeviceToHost, st));
+  }
+  return pa_sync(ctx, stream);
+}

@@ -1,0 +1,157 @@
+// Shared device helpers for the sm_100a attention kernels: PTX wrappers for mbarrier, TMA, ldmatrix and
+// mma.sync, the bounded-wait rule, and the internal context layout.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/pooled_attn.h"
+
+namespace pa {
+
+// Every device-side wait is bounded: after this many polls the waiter records PA_WAIT_* in the context's
+// error word and carries on as if the wait had succeeded, so control flow stays uniform, every thread
+// reaches the end of the kernel and the host reports PA_ETIMEOUT instead of a hung GPU.
+constexpr uint32_t kWaitPolls = 1u << 24;  // with 32..64 ns back-off: well under a second
+
+enum : uint32_t { WAIT_KFULL = 1, WAIT_VFULL = 2, WAIT_EMPTY = 3, WAIT_MMA = 4, WAIT_TMEM = 5, WAIT_QFULL = 6 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  err_smem: a shared word that any thread sets once a wait ran out; later waits return at once.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* err_smem, uint32_t code) {
+  if (mbar_test(bar, parity)) return;
+  for (uint32_t i = 0; i < kWaitPolls; ++i) {
+    if (*err_smem) return;
+    if (mbar_test(bar, parity)) return;
+    if (i > 64) __nanosleep(32);
+  }
+  *err_smem = code;
+}
+
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+
+// 3-D tiled TMA load (no multicast) completing on an mbarrier of this CTA.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, int x, int y, int z, int w, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_t(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+// D (16x8, f32) += A (16x16 f16, row) * B (16x8 f16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// hi + lo f16 pair of an f32: x ~= hi + lo with about 22 significant bits
+__device__ __forceinline__ void split_h(float x, __half& hi, __half& lo) {
+  hi = __float2half_rn(x);
+  lo = __float2half_rn(x - __half2float(hi));
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+constexpr int kMaxItems = 32;     // items of one batched decode call
+constexpr int kMaxRows = 64;      // query rows (columns x heads of one kv head) one decode CTA carries
+
+struct ItemList {
+  uint32_t seq[kMaxItems];
+  int32_t lim0[kMaxItems];     // cache rows column 0 sees, before clamping: pos + 1 - layer origin (may be <= 0)
+  uint32_t n_rows[kMaxItems];  // cache rows the last column sees: clamp(pos + n_cols - origin, 0, max_seq)
+  uint32_t n_cols[kMaxItems];
+  uint32_t col0[kMaxItems];    // first column of the item in q / gate / out
+};
+
+}  // namespace pa
+
+struct pa_ctx {
+  int device = 0;
+  int sm_count = 148;
+  int smem_optin = 0;
+  pa_config cfg{};
+  uint32_t G = 1, q_dim = 0, kv_dim = 0;
+  double* inv_freq = nullptr;  // device: theta^(-2i/n_rot), i < n_rot/2, evaluated on the host in float64
+  float* q_rot = nullptr;      // device: rotated q of the current call, f32 [max_cols][q_dim]
+  float* part_o = nullptr;     // device: split partials, f32 [rows][splits][head_dim] of the current call
+  float* part_ml = nullptr;    // device: f32 [rows][splits][2]
+  uint32_t max_splits = 0;
+  size_t part_slots = 0;       // (query row, split) records the partial buffers hold
+  uint32_t* dev_err = nullptr;   // device error word (bounded waits)
+  uint32_t* host_err = nullptr;  // pinned mirror
+  void* stage_dev = nullptr;     // device staging of the host-buffer entry point
+  void* stage_host = nullptr;    // pinned staging
+  size_t stage_bytes = 0;
+  std::vector<cudaEvent_t> ev;   // timing: event pairs around core-kernel launches
+  size_t ev_used = 0;
+  bool timing = false;
+  bool failed = false;
+  std::string err;
+  pa_stats stats{};
+};
+
+struct pa_layer {
+  pa_ctx* ctx = nullptr;
+  uint32_t n_seqs = 0, max_seq = 0;
+  uint32_t origin = 0;           // global position of cache row 0 (a shard of a longer sequence)
+  __half* k = nullptr;
+  __half* v = nullptr;
+  CUtensorMap tm_k64, tm_v64;    // 64-row boxes for the decode kernel
+  CUtensorMap tm_k128, tm_v128;  // 128-row boxes for the prefill kernel
+};

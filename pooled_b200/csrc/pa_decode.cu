@@ -1,0 +1,479 @@
+// Split-K flash-decode / k-token verify for an f16 KV cache, and the LSE combine that follows it.
+//
+// One CTA per (split of the KV sequence, kv head, item).  All query rows that share the kv head — the G
+// heads of the GQA group times the item's columns, at most 64 — ride in the same CTA, so every K and V
+// byte is fetched from HBM once.  A producer thread streams 64-position K and V tiles with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of shared-memory slots guarded by
+// mbarriers; four consumer warps take the tiles apart with ldmatrix and multiply on the tensor cores
+// (mma.sync m16n8k16, f32 accumulate):
+//     S^T[pos, row] = K[pos, :] . Q[row, :]        warp w owns positions 16w .. 16w+15 of the tile
+//     O^T[dim, row] += V^T[dim, pos] . P^T[pos, row]   warp w owns a quarter of the head dims
+// with an online softmax in between (running maximum and sum per row, exchanged between the warps through
+// shared memory).  q, and the softmax weights P, enter the tensor cores as hi + lo f16 pairs unless the
+// context asks for PA_FLAG_FAST, so the result carries about 22 significant bits of both.
+// The kernel is HBM-bound: 2 * rows * head_dim * 2 bytes per kv head; the math needs a fraction of the
+// time a tile takes to arrive.
+//
+// Each CTA writes an unnormalised partial (o, m, l) per query row; pa_combine_kernel merges the splits
+// (out = sum o_s e^(m_s-M) / sum l_s e^(m_s-M)), applies the sigmoid gate and stores f32 or f16.
+//
+// Stands in for attn_dec / attn_dec_combine / attn_dec_combine_g of pooled (engine/wgsl/attn_dec.js:67-287).
+#include "pa_params.cuh"
+
+namespace pa {
+
+constexpr int kT = 64;             // positions per tile
+constexpr int kConsumers = 128;    // 4 consumer warps
+constexpr int kDecThreads = 160;   // + 1 producer warp
+constexpr int kMaxStages = 8;
+
+template <int HD, int NT, bool PRECISE>
+struct DecSmem {
+  static constexpr int ROWS = NT * 8;
+  static constexpr int SLOT = kT * HD * 2;           // bytes of one K or V tile
+  static constexpr int QP = HD * 2 + 16;             // q row pitch (bytes): 16-byte skew against bank conflicts
+  static constexpr int PP = ROWS * 2;                // P^T row pitch (bytes)
+  static constexpr int Q_BYTES = ROWS * QP * (PRECISE ? 2 : 1);
+  static constexpr int P_BYTES = kT * PP * (PRECISE ? 2 : 1);
+  static constexpr int MISC = 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64;
+  static constexpr int fixed_bytes() { return Q_BYTES + P_BYTES + MISC; }
+  static int stages_for(int smem_limit) {
+    int s = (smem_limit - 1024 - fixed_bytes()) / (2 * SLOT);
+    return s > kMaxStages ? kMaxStages : s;
+  }
+  static int total_bytes(int stages) { return 1024 + stages * 2 * SLOT + fixed_bytes(); }
+};
+
+template <int HD, int NT, bool PRECISE>
+__global__ void __launch_bounds__(kDecThreads, 1)
+pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
+  using L = DecSmem<HD, NT, PRECISE>;
+  constexpr int ROWS = L::ROWS, SLOT = L::SLOT, QP = L::QP, PP = L::PP;
+  constexpr int MT = HD / 64;        // 16-dim output tiles per consumer warp
+  constexpr int CH = HD / 64;        // 128-byte chunks per cache row of one kv head
+
+  const uint32_t split = blockIdx.x, g = blockIdx.y, item = blockIdx.z;
+  const uint32_t n_cols = p.items.n_cols[item];
+  const uint32_t n_rows = p.items.n_rows[item];                // cache rows the last column sees
+  const uint32_t tiles = (n_rows + kT - 1) / kT;
+  const uint32_t tps = (tiles + p.n_splits - 1) / p.n_splits;  // tiles per split
+  const uint32_t tile0 = split * tps;
+  if (tile0 >= tiles) return;
+  const uint32_t tile1 = min(tiles, tile0 + tps);
+  const uint32_t n_tiles = tile1 - tile0;
+  const uint32_t NS = p.n_stages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_slots = base;
+  uint8_t* v_slots = base + NS * SLOT;
+  uint8_t* q_hi = v_slots + NS * SLOT;
+  uint8_t* q_lo = q_hi + ROWS * QP;
+  uint8_t* p_hi = q_hi + L::Q_BYTES;
+  uint8_t* p_lo = p_hi + kT * PP;
+  float* s_max = reinterpret_cast<float*>(p_hi + L::P_BYTES);   // [4][ROWS]
+  float* s_l = s_max + 4 * ROWS;                                // [4][ROWS]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_l + 4 * ROWS); // kfull, kempty, vfull, vempty [kMaxStages] each
+  volatile uint32_t* s_err = reinterpret_cast<volatile uint32_t*>(bars + 4 * kMaxStages);
+
+  const uint32_t kfull = smem_u32(bars), kempty = kfull + kMaxStages * 8, vfull = kempty + kMaxStages * 8,
+                 vempty = vfull + kMaxStages * 8;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    *s_err = 0;
+    for (uint32_t s = 0; s < NS; ++s) {
+      mbar_init(kfull + 8 * s, 1);
+      mbar_init(vfull + 8 * s, 1);
+      mbar_init(kempty + 8 * s, 4);
+      mbar_init(vempty + 8 * s, 4);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- producer ----
+    if (lane == 0) {
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+      const int y0 = (int)(p.items.seq[item] * p.max_seq + tile0 * kT);
+      const int z = (int)(g * CH);
+      for (uint32_t i = 0; i < n_tiles; ++i) {
+        const uint32_t s = i % NS, ph = (i / NS) & 1;
+        mbar_wait(kempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
+        mbar_expect_tx(kfull + 8 * s, SLOT);
+        tma_load_3d(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s);
+        mbar_wait(vempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
+        mbar_expect_tx(vfull + 8 * s, SLOT);
+        tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
+      }
+      if (*s_err) {
+        // a wait ran out somewhere: let the copies still in flight land (bounded) before the CTA exits
+        const uint32_t first = n_tiles > NS ? n_tiles - NS : 0;
+        for (uint32_t i = first; i < n_tiles; ++i) {
+          const uint32_t s = i % NS, ph = (i / NS) & 1;
+          for (uint32_t k = 0; k < (1u << 16) && !mbar_test(kfull + 8 * s, ph); ++k) __nanosleep(64);
+          for (uint32_t k = 0; k < (1u << 16) && !mbar_test(vfull + 8 * s, ph); ++k) __nanosleep(64);
+        }
+        atomicMax(p.err, *s_err);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers ----
+  const int w = warp, r = lane >> 2, j = lane & 3;
+  const uint32_t G = p.G, live_rows = n_cols * G;
+
+  // q rows of this kv head -> shared memory as f16 hi (+ lo); rows past live_rows are zero
+  for (int idx = tid; idx < ROWS * (HD / 2); idx += kConsumers) {
+    const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+    float x0 = 0.f, x1 = 0.f;
+    if ((uint32_t)row < live_rows) {
+      const uint32_t c = row / G, hh = row % G;
+      const uint64_t off = (uint64_t)(p.items.col0[item] + c) * p.q_col_stride + (uint64_t)(g * G + hh) * p.q_head_stride + d;
+      if (p.q_f16) {
+        const __half2 h2 = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(p.q) + off);
+        x0 = __low2float(h2); x1 = __high2float(h2);
+      } else {
+        const float2 f2 = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.q) + off);
+        x0 = f2.x; x1 = f2.y;
+      }
+    }
+    __half h0, l0, h1, l1;
+    split_h(x0, h0, l0); split_h(x1, h1, l1);
+    *reinterpret_cast<__half2*>(q_hi + row * QP + d * 2) = __halves2half2(h0, h1);
+    if (PRECISE) *reinterpret_cast<__half2*>(q_lo + row * QP + d * 2) = __halves2half2(l0, l1);
+  }
+
+  // causal limit of the two rows this thread owns in every 8-row group
+  uint32_t lim[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      uint32_t row = nt * 8 + 2 * j + e;
+      const int32_t c = (int32_t)min(row / G, n_cols - 1);
+      lim[nt][e] = (uint32_t)min(max(p.items.lim0[item] + c, 0), (int32_t)n_rows);
+    }
+
+  float m_run[NT][2], l_run[NT][2];
+  float oacc[MT][NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    m_run[nt][0] = m_run[nt][1] = -3.0e38f;
+    l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oacc[mt][nt][e] = 0.f;
+  }
+  named_bar_sync(1, kConsumers);   // q visible
+
+  const uint32_t q_hi_s = smem_u32(q_hi), q_lo_s = smem_u32(q_lo), p_hi_s = smem_u32(p_hi), p_lo_s = smem_u32(p_lo);
+
+  for (uint32_t i = 0; i < n_tiles; ++i) {
+    const uint32_t s = i % NS, ph = (i / NS) & 1;
+    const uint32_t tile_pos = (tile0 + i) * kT;
+    const uint32_t ks_base = smem_u32(k_slots + s * SLOT), vs_base = smem_u32(v_slots + s * SLOT);
+
+    // ---- S^T = K . Q^T for positions 16w .. 16w+15 ----
+    float sacc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+    mbar_wait(kfull + 8 * s, ph, s_err, WAIT_KFULL);
+    {
+      const uint32_t krow = 16 * w + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll 4
+      for (int k2 = 0; k2 < HD / 32; ++k2) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t c16g = (2 * k2 + e) * 2 + (lane >> 4);
+          const uint32_t addr = ks_base + (c16g >> 3) * (kT * 128) + krow * 128 + (((c16g & 7) ^ (krow & 7)) << 4);
+          ldsm_x4(addr, a[e][0], a[e][1], a[e][2], a[e][3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t qoff = (nt * 8 + (lane & 7)) * QP + (4 * k2 + (lane >> 3)) * 16;
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(q_hi_s + qoff, b0, b1, b2, b3);
+          mma_16816(sacc[nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
+          mma_16816(sacc[nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
+          if (PRECISE) {
+            ldsm_x4(q_lo_s + qoff, b0, b1, b2, b3);
+            mma_16816(sacc[nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
+            mma_16816(sacc[nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(kempty + 8 * s);
+
+    // ---- scale, causal mask, tile maximum per row ----
+    const uint32_t pos_a = tile_pos + 16 * w + r, pos_b = pos_a + 8;
+    float tmax[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float sa = sacc[nt][e] * p.scale_log2, sb = sacc[nt][2 + e] * p.scale_log2;
+        sa = pos_a < lim[nt][e] ? sa : -INFINITY;
+        sb = pos_b < lim[nt][e] ? sb : -INFINITY;
+        sacc[nt][e] = sa; sacc[nt][2 + e] = sb;
+        float mx = fmaxf(sa, sb);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        tmax[nt][e] = mx;
+      }
+      if (r == 0) { s_max[w * ROWS + nt * 8 + 2 * j] = tmax[nt][0]; s_max[w * ROWS + nt * 8 + 2 * j + 1] = tmax[nt][1]; }
+    }
+    named_bar_sync(1, kConsumers);
+
+    // ---- new running maximum, weights P = 2^(s - m), rescale factor ----
+    float alpha[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int row = nt * 8 + 2 * j + e;
+        float mn = m_run[nt][e];
+        mn = fmaxf(mn, fmaxf(fmaxf(s_max[row], s_max[ROWS + row]), fmaxf(s_max[2 * ROWS + row], s_max[3 * ROWS + row])));
+        alpha[nt][e] = exp2f(m_run[nt][e] - mn);
+        m_run[nt][e] = mn;
+        const float pa = exp2f(sacc[nt][e] - mn), pb = exp2f(sacc[nt][2 + e] - mn);
+        sacc[nt][e] = pa; sacc[nt][2 + e] = pb;
+        l_run[nt][e] = l_run[nt][e] * alpha[nt][e] + (pa + pb);
+      }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      // P^T[pos][row]: this thread holds rows 2j, 2j+1 of group nt at positions 16w+r and 16w+r+8
+      const uint32_t o_a = (16 * w + r) * PP + (nt * 8 + 2 * j) * 2, o_b = o_a + 8 * PP;
+      __half ha0, la0, ha1, la1, hb0, lb0, hb1, lb1;
+      split_h(sacc[nt][0], ha0, la0); split_h(sacc[nt][1], ha1, la1);
+      split_h(sacc[nt][2], hb0, lb0); split_h(sacc[nt][3], hb1, lb1);
+      *reinterpret_cast<__half2*>(p_hi + o_a) = __halves2half2(ha0, ha1);
+      *reinterpret_cast<__half2*>(p_hi + o_b) = __halves2half2(hb0, hb1);
+      if (PRECISE) {
+        *reinterpret_cast<__half2*>(p_lo + o_a) = __halves2half2(la0, la1);
+        *reinterpret_cast<__half2*>(p_lo + o_b) = __halves2half2(lb0, lb1);
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        oacc[mt][nt][0] *= alpha[nt][0]; oacc[mt][nt][1] *= alpha[nt][1];
+        oacc[mt][nt][2] *= alpha[nt][0]; oacc[mt][nt][3] *= alpha[nt][1];
+      }
+
+    mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
+    if (tile_pos + kT > n_rows) {
+      // rows of the tile past the sequence end hold whatever the cache holds there (possibly NaN):
+      // their weights are zero, but 0 * NaN is NaN, so clear them
+      const uint32_t nv = n_rows - tile_pos;
+      for (uint32_t idx = tid; idx < (kT - nv) * (HD / 8); idx += kConsumers) {
+        const uint32_t row = nv + idx / (HD / 8), c16g = idx % (HD / 8);
+        *reinterpret_cast<uint4*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + row * 128 + (((c16g & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    named_bar_sync(1, kConsumers);   // P (and the cleared rows) visible to every warp
+
+    // ---- O^T += V^T . P^T, dims (w*MT + mt)*16 .. +15 ----
+#pragma unroll
+    for (int ks = 0; ks < kT / 16; ++ks) {
+      uint32_t bh[NT][2], bl[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint32_t poff = (ks * 16 + (lane & 15)) * PP + nt * 16;
+        ldsm_x2_t(p_hi_s + poff, bh[nt][0], bh[nt][1]);
+        if (PRECISE) ldsm_x2_t(p_lo_s + poff, bl[nt][0], bl[nt][1]);
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const uint32_t qd = lane >> 3;
+        const uint32_t vrow = ks * 16 + (lane & 7) + (qd >> 1) * 8;
+        const uint32_t c16g = (w * MT + mt) * 2 + (qd & 1);
+        const uint32_t addr = vs_base + (c16g >> 3) * (kT * 128) + vrow * 128 + (((c16g & 7) ^ (vrow & 7)) << 4);
+        uint32_t a0, a1, a2, a3;
+        ldsm_x4_t(addr, a0, a1, a2, a3);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_16816(oacc[mt][nt], a0, a1, a2, a3, bh[nt][0], bh[nt][1]);
+          if (PRECISE) mma_16816(oacc[mt][nt], a0, a1, a2, a3, bl[nt][0], bl[nt][1]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(vempty + 8 * s);
+  }
+
+  // ---- partial (o, m, l) per row ----
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float l = l_run[nt][e];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      if (r == 0) s_l[w * ROWS + nt * 8 + 2 * j + e] = l;
+    }
+  named_bar_sync(1, kConsumers);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const uint32_t row = nt * 8 + 2 * j + e;
+      if (row >= live_rows) continue;
+      const uint32_t c = row / G, hh = row % G;
+      const uint64_t prow = (uint64_t)(p.items.col0[item] + c) * p.n_heads + g * G + hh;
+      const uint64_t slot = prow * p.n_splits + split;
+      float* po = p.part_o + slot * HD;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int d = (w * MT + mt) * 16 + r;
+        po[d] = oacc[mt][nt][e];
+        po[d + 8] = oacc[mt][nt][2 + e];
+      }
+      if (w == 0 && r == 0) {
+        const float l = (s_l[row] + s_l[ROWS + row]) + (s_l[2 * ROWS + row] + s_l[3 * ROWS + row]);
+        p.part_ml[slot * 2] = m_run[nt][e] * 0.6931471805599453f;
+        p.part_ml[slot * 2 + 1] = l;
+      }
+    }
+  if (*s_err && tid == 0) atomicMax(p.err, *s_err);
+}
+
+// ------------------------------------------------------------------------------ combine --
+
+template <int HD>
+__global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) {
+  __shared__ float s_w[512];
+  __shared__ float s_red[8];
+  __shared__ float s_acc[8][HD];
+  const uint32_t prow = blockIdx.x, col = prow / p.n_heads, h = prow % p.n_heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t ns = p.fixed_parts;
+  if (ns == 0) {
+    uint32_t it = 0;
+    for (uint32_t i = 0; i < p.n_items; ++i) if (col >= p.items.col0[i]) it = i;
+    const uint32_t n_rows = p.items.n_rows[it];
+    const uint32_t tiles = (n_rows + kT - 1) / kT, tps = (tiles + p.n_splits - 1) / p.n_splits;
+    ns = tiles ? (tiles + tps - 1) / tps : 0;   // a shard that holds no row of the item: an empty record
+  }
+  const float* ml = p.ml + prow * p.ml_row_stride;
+  float M = -3.0e38f;
+  for (uint32_t s = tid; s < ns; s += 256) M = fmaxf(M, ml[s * p.ml_part_stride]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  if (lane == 0) s_red[warp] = M;
+  __syncthreads();
+  M = s_red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) M = fmaxf(M, s_red[i]);
+  __syncthreads();
+  float Lp = 0.f;
+  for (uint32_t s = tid; s < ns; s += 256) {
+    const float wgt = __expf(ml[s * p.ml_part_stride] - M);
+    s_w[s] = wgt;
+    Lp += ml[s * p.ml_part_stride + 1] * wgt;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) Lp += __shfl_xor_sync(0xffffffffu, Lp, o);
+  if (lane == 0) s_red[warp] = Lp;
+  __syncthreads();
+  float Lsum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) Lsum += s_red[i];
+
+  constexpr int V4 = HD / 128;   // float4s per lane
+  float4 acc[V4];
+#pragma unroll
+  for (int v = 0; v < V4; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* ob = p.o + prow * p.o_row_stride;
+  for (uint32_t s = warp; s < ns; s += 8) {
+    const float wgt = s_w[s];
+    const float4* src = reinterpret_cast<const float4*>(ob + s * p.o_part_stride);
+#pragma unroll
+    for (int v = 0; v < V4; ++v) {
+      const float4 x = src[v * 32 + lane];
+      acc[v].x += x.x * wgt; acc[v].y += x.y * wgt; acc[v].z += x.z * wgt; acc[v].w += x.w * wgt;
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < V4; ++v) *reinterpret_cast<float4*>(&s_acc[warp][(v * 32 + lane) * 4]) = acc[v];
+  __syncthreads();
+  for (int d = tid; d < HD; d += 256) {
+    float t = s_acc[0][d];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) t += s_acc[i][d];
+    if (p.partial_out) {
+      p.partial_out[(uint64_t)prow * HD + d] = t;
+      if (d == 0) {
+        float* mlo = p.partial_out + p.partial_rows * HD + (uint64_t)prow * 2;
+        mlo[0] = M; mlo[1] = Lsum;
+      }
+      continue;
+    }
+    float rv = t / Lsum;
+    if (p.gate) {
+      const uint64_t go = (uint64_t)col * p.gate_col_stride + (uint64_t)h * p.gate_head_stride + d;
+      const float gv = p.act_f16 ? __half2float(reinterpret_cast<const __half*>(p.gate)[go]) : reinterpret_cast<const float*>(p.gate)[go];
+      rv *= 1.0f / (1.0f + __expf(-gv));
+    }
+    const uint64_t oo = (uint64_t)col * p.out_col_stride + (uint64_t)h * HD + d;
+    if (p.act_f16) reinterpret_cast<__half*>(p.out)[oo] = __float2half_rn(rv);
+    else reinterpret_cast<float*>(p.out)[oo] = rv;
+  }
+}
+
+// ------------------------------------------------------------------------------ launchers --
+
+template <int HD, int NT, bool PRECISE>
+static cudaError_t launch_decode_t(const pa_layer* L, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  using S = DecSmem<HD, NT, PRECISE>;
+  DecodeParams pp = p;
+  int stages = S::stages_for(L->ctx->smem_optin);
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  pp.n_stages = (uint32_t)stages;
+  const int bytes = S::total_bytes(stages);
+  static bool attr_set = false;
+  auto kern = pa_decode_kernel<HD, NT, PRECISE>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  kern<<<grid, kDecThreads, bytes, st>>>(L->tm_k64, L->tm_v64, pp);
+  return cudaGetLastError();
+}
+
+template <int HD, bool PRECISE>
+static cudaError_t launch_decode_nt(const pa_layer* L, const DecodeParams& p, dim3 grid, int nt, cudaStream_t st) {
+  switch (nt) {
+    case 1: return launch_decode_t<HD, 1, PRECISE>(L, p, grid, st);
+    case 2: return launch_decode_t<HD, 2, PRECISE>(L, p, grid, st);
+    case 3: case 4: return launch_decode_t<HD, 4, PRECISE>(L, p, grid, st);
+    default: return launch_decode_t<HD, 8, PRECISE>(L, p, grid, st);
+  }
+}
+
+cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, int nt, cudaStream_t st) {
+  const bool precise = !(L->ctx->cfg.flags & PA_FLAG_FAST);
+  if (L->ctx->cfg.head_dim == 256) return precise ? launch_decode_nt<256, true>(L, p, grid, nt, st) : launch_decode_nt<256, false>(L, p, grid, nt, st);
+  if (L->ctx->cfg.head_dim == 128) return precise ? launch_decode_nt<128, true>(L, p, grid, nt, st) : launch_decode_nt<128, false>(L, p, grid, nt, st);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, cudaStream_t st) {
+  if (head_dim == 256) pa_combine_kernel<256><<<rows, 256, 0, st>>>(p);
+  else if (head_dim == 128) pa_combine_kernel<128><<<rows, 256, 0, st>>>(p);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+}  // namespace pa

@@ -1,0 +1,59 @@
+// Kernel parameter blocks shared by the kernels and the C-ABI front.
+#pragma once
+#include "pa_common.cuh"
+
+namespace pa {
+
+struct DecodeParams {
+  const void* q;            // rotated queries
+  int q_f16;                // dtype of q
+  uint64_t q_col_stride, q_head_stride;
+  float* part_o;            // [rows][n_splits][HD]
+  float* part_ml;           // [rows][n_splits][2]   (m in natural-log units, l)
+  uint32_t n_splits;
+  uint32_t n_heads, G, max_seq, n_stages;
+  float scale_log2;         // log2(e) / sqrt(head_dim)
+  uint32_t* err;
+  ItemList items;
+};
+
+struct CombineParams {
+  const float* o;        // record s of row prow: o + prow * o_row_stride + s * o_part_stride, HD floats
+  const float* ml;       // (m, l) of it:        ml + prow * ml_row_stride + s * ml_part_stride
+  uint64_t o_row_stride, o_part_stride, ml_row_stride, ml_part_stride;
+  uint32_t n_heads, fixed_parts;  // fixed_parts != 0: that many records per row; else from the item's split plan
+  uint32_t n_splits;
+  const void* gate; uint64_t gate_col_stride, gate_head_stride;
+  void* out; uint64_t out_col_stride;
+  int act_f16;
+  float* partial_out;    // != nullptr: write the merged record (o unnormalised, m, l) instead of out
+  uint64_t partial_rows; // rows in partial_out (o block first, then the (m, l) block)
+  ItemList items; uint32_t n_items;
+};
+
+struct RopeParams {
+  const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
+  float* q_out; uint64_t q_out_col_stride;                                  // f32, heads packed [q_heads][hd]
+  const void* k; const void* v; uint64_t kv_col_stride; uint32_t kv_heads;  // k == nullptr: skip
+  __half* k_cache; __half* v_cache; uint64_t cache_row0;                    // row of column 0
+  uint32_t hd, n_rot, pos, mode;
+  int in_f16;
+  const double* inv_freq;
+  const float* cs_table;   // [n_cols][n_rot] (cos, sin) per pair
+};
+
+struct SigmoidParams {
+  void* a; uint64_t a_col_stride; const void* g; uint64_t g_col_stride, g_head_stride;
+  uint32_t n_heads, hd; int f16;
+};
+
+struct PrefillParams {
+  const void* q; int q_f16; uint64_t q_col_stride, q_head_stride;
+  const void* gate; uint64_t gate_col_stride, gate_head_stride;
+  void* out; uint64_t out_col_stride; int act_f16;
+  uint32_t seq, pos, n_cols, n_heads, G, max_seq;
+  float scale_log2;
+  uint32_t* err;
+};
+
+}  // namespace pa

@@ -1,0 +1,69 @@
+"""KV-sequence-sharded decode across the GPUs of one box (one process per GPU, torch.distributed).
+
+Each rank keeps a contiguous chunk of every sequence's K/V rows in its own layer caches: rank r of P holds global
+rows [r * chunk, (r + 1) * chunk).  A decode step runs the ordinary split-K kernel on the rank's rows, which leaves
+one (o, m, l) record per (sequence, head); the ranks all-gather their record blocks (NCCL over NVLink; about
+head_dim + 2 floats per row, so the exchange is latency-, not bandwidth-bound) and every rank merges them with the
+same LSE combine the single-GPU path uses, gate included.  The new token's K/V row is appended by the rank that owns
+its position.  pooled itself never shards attention (it is pipeline-parallel over layers); the merge is the
+arithmetic of its attn_dec_combine (engine/wgsl/attn_dec.js:215-287) applied across GPUs instead of across splits.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class ShardPlan:
+    """Contiguous chunks of `chunk` rows per rank."""
+    world: int
+    chunk: int
+
+    def owner(self, pos: int) -> int:
+        r = pos // self.chunk
+        if r >= self.world:
+            raise ValueError(f"position {pos} is past the {self.world} x {self.chunk} rows the ranks hold")
+        return r
+
+    def local_rows(self, rank: int, n_rows: int) -> int:
+        """How many of the global rows [0, n_rows) rank holds."""
+        return max(0, min(self.chunk, n_rows - rank * self.chunk))
+
+    def local_pos(self, rank: int, pos: int) -> int:
+        return pos - rank * self.chunk
+
+
+class ShardedDecoder:
+    """One decode step of a sharded layer.  `engine` needs set_origin(), rope(), rope_append(), decode_partial() and
+    merge() with AttnEngine's signatures; `dist` is torch.distributed (or a stand-in with all_gather_into_tensor).
+    Every position stays global: the engine's layers are told which global row their cache starts at."""
+
+    def __init__(self, engine, plan: ShardPlan, rank: int, dist, group=None):
+        self.eng, self.plan, self.rank, self.dist, self.group = engine, plan, rank, dist, group
+        for li in range(engine.cfg.n_layers):
+            engine.set_origin(li, rank * plan.chunk)
+
+    def step(self, li: int, seqs_pos, q, k, v, gate, out=None, gather_buf=None):
+        """seqs_pos: [(seq, global position of the new token)], one token per sequence; q/k/v/gate: [n_seqs, ...]
+        on every rank (the projections are replicated).  Returns out [n_seqs, q_dim] on every rank."""
+        eng, plan = self.eng, self.plan
+        n = len(seqs_pos)
+        q_rot = []
+        for i, (seq, pos) in enumerate(seqs_pos):
+            if plan.owner(pos) == self.rank:   # this rank owns the new row: rotate q and k, append k and v
+                q_rot.append(eng.rope_append(li, seq, pos, q[i:i + 1], k[i:i + 1], v[i:i + 1]))
+            else:
+                q_rot.append(eng.rope(q[i:i + 1], eng.cfg.n_heads, pos))
+        q_rot = q_rot[0] if n == 1 else _cat(q_rot)
+        part = eng.decode_partial(li, [(seq, pos, 1) for seq, pos in seqs_pos], q_rot)
+        if plan.world == 1:
+            return eng.merge(part[None], n, gate, out)
+        if gather_buf is None:
+            gather_buf = part.new_empty((plan.world, part.numel()))
+        self.dist.all_gather_into_tensor(gather_buf.view(-1), part, group=self.group)
+        return eng.merge(gather_buf, n, gate, out)
+
+
+def _cat(parts):
+    import torch
+    return torch.cat(parts, dim=0)

@@ -1,0 +1,255 @@
+"""Split-K decode / verify, combine and gate on the GPU against the float64 oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from oracle import po
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(nH, nKV, hd, max_seq, act="f32", n_seqs=1, max_cols=8, n_rot=64, theta=1e7, rope_mode="f64", **kw):
+    import torch
+    from pooled_b200 import AttnConfig, AttnEngine
+    return AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=n_rot, rope_theta=theta, max_seq=max_seq, n_seqs=n_seqs,
+                                 rope_mode=rope_mode, act_dtype=torch.float32 if act == "f32" else torch.float16, max_cols=max_cols, **kw))
+
+
+# ---- the reference's own kernel test, retargeted: tests/test_attn_dec.js ------------------------------
+
+REF_RUNS = [  # (nH, nKV, maxSeq, cases) as in tests/test_attn_dec.js:106-107 (QUICK sizes first in CI there)
+    (16, 2, 70000, [1, 2, 5, 63, 64, 65, 127, 128, 129, 300, 1000, 4096, 8192, 8193, 16385, 33000, 69999]),
+    (24, 4, 40000, [1, 3, 64, 129, 257, 1000, 4097, 16384, 32769, 39999]),
+]
+
+
+@pytest.fixture(scope="module")
+def ref_inputs():
+    """The LCG stream of tests/test_attn_dec.js: the seed carries over from the first run to the second."""
+    seed = 12345
+    out = []
+    for nH, nKV, max_seq, cases in REF_RUNS:
+        K, V, q, seed = po.gen_attn_dec(seed, max_seq, nKV * 256, nH * 256)
+        out.append((nH, nKV, max_seq, cases, K, V, q))
+    return out
+
+
+@pytest.mark.parametrize("run", [0, 1])
+def test_attn_dec_js_cases(ref_inputs, run):
+    import torch
+    nH, nKV, max_seq, cases, K, V, q = ref_inputs[run]
+    eng = _engine(nH, nKV, 256, max_seq, act="f32", max_cols=4, rope_mode="none")
+    util.load_cache(eng, 0, 0, K, V)
+    qd = util.torch_dev(q)
+    worst = 0.0
+    for seq_len in cases:
+        pos = seq_len - 1
+        one = eng.decode(0, [(0, pos, 1)], qd[0:1]).cpu().numpy()
+        ref = po.attn_f64(q[0:1], K, V, nH, nKV, 256, pos, 1)
+        ma, rel = util.errs(one, ref)
+        worst = max(worst, rel)
+        assert np.all(np.isfinite(one)) and rel < util.REF_REL, f"seqLen {seq_len}: relDiff vs f64 {rel:.2e}"
+        if seq_len >= 4:
+            # verify vs decode: a 4-column pass ending here against one-column passes at each position.  The reference
+            # makes these bitwise equal by deriving split boundaries from each column's own position; here the
+            # columns of a pass share one K/V stream, so the bound is the same 2e-5 against float64 instead.
+            multi = eng.decode(0, [(0, pos - 3, 4)], qd[0:4]).cpu().numpy()
+            refm = po.attn_f64(q[0:4], K, V, nH, nKV, 256, pos - 3, 4)
+            assert util.errs(multi, refm)[1] < util.REF_REL
+            for c in range(4):
+                single = eng.decode(0, [(0, pos - 3 + c, 1)], qd[c:c + 1]).cpu().numpy()
+                assert util.errs(single[0], multi[c])[1] < util.REF_REL
+    eng.sync()
+    print(f"run {run}: worst relDiff vs f64 {worst:.2e}")
+
+
+# ---- BASELINE configurations -------------------------------------------------------------------------
+
+def _config_inputs(cfg_id, nH, nKV, hd, rows, n_cols, outliers=False):
+    K = util.normal_f16(0xB0B + cfg_id, (rows, nKV * hd)); V = util.normal_f16(0xC0DE + cfg_id, (rows, nKV * hd))
+    q = util.normal_f16(0xA11CE + cfg_id, (n_cols, nH * hd)); g = util.normal_f16(0x6A7E + cfg_id, (n_cols, nH * hd))
+    if outliers:
+        K = util.with_outliers(K, nKV, hd)
+        # q heads of one kv head share that head's outlier channels
+        G = nH // nKV
+        qq = q.reshape(n_cols, nH, hd).copy()
+        for h in range(nH):
+            for c in po.outlier_channels(h // G, hd):
+                qq[:, h, c] *= 20.0
+        q = po.np_h2f(po.np_f16_rne(qq)).reshape(n_cols, nH * hd)
+    return q, K, V, g
+
+
+def _layer_step_vs_oracle(eng, cfgid, nH, nKV, hd, n_rot, theta, ctx, n_cols, gate, outliers, act):
+    """Cache rows [0, ctx) pre-rotated; the new tokens' q, k, v go through RoPE + append + attend + gate."""
+    import torch
+    td = torch.float16 if act == "f16" else torch.float32
+    q, K, V, g = _config_inputs(cfgid, nH, nKV, hd, ctx + n_cols, n_cols, outliers)
+    Kc, Vc = po.np_f16_rne(K[:ctx]), po.np_f16_rne(V[:ctx])
+    util.load_cache(eng, 0, 0, Kc, Vc)
+    k_new, v_new = K[ctx:], V[ctx:]
+    out = eng.encode_layer(0, ctx, util.torch_dev(q, td), util.torch_dev(k_new, td), util.torch_dev(v_new, td),
+                           util.torch_dev(g, td) if gate else None, mode="decode").float().cpu().numpy()
+    eng.sync()
+    # oracle: the same steps on the CPU
+    Kf = np.concatenate([Kc, np.stack([po.f16_rne(po.rope_neox_f64(k_new[c], nKV, hd, n_rot, ctx + c, theta)) for c in range(n_cols)])])
+    Vf = np.concatenate([Vc, po.f16_rne(v_new)])
+    gk, gv = util.read_cache(eng, 0, 0, ctx, n_cols)
+    assert np.array_equal(gk, Kf[ctx:]) and np.array_equal(gv, Vf[ctx:]), "KV append is not bit-exact"
+    q_rot = np.stack([po.rope_neox_f64(q[c], nH, hd, n_rot, ctx + c, theta) for c in range(n_cols)])
+    ref = po.attn_f64(q_rot, Kf, Vf, nH, nKV, hd, ctx, n_cols, g if gate else None)
+    return out, ref, (q_rot, Kf, Vf, g)
+
+
+def test_config1_qwen3_17b_decode():
+    # 16 q / 8 kv heads, head_dim 128, full RoPE theta 1e6 at position 4096, context 4096
+    eng = _engine(16, 8, 128, 4200, act="f16", n_rot=128, theta=1e6)
+    out, ref, _ = _layer_step_vs_oracle(eng, 1, 16, 8, 128, 128, 1e6, 4096, 1, False, False, "f16")
+    ma, mr = util.assert_close(out, ref, "config 1")
+    print(f"config 1: max-abs {ma:.2e} max-rel {mr:.2e}")
+
+
+def test_config2_moe_decode_with_outliers_and_gate():
+    # 16 q / 2 kv heads, head_dim 256, partial RoPE 64 dims theta 1e7, context 32768, outlier channels x20, sigmoid gate
+    eng = _engine(16, 2, 256, 32768 + 8, act="f16")
+    out, ref, _ = _layer_step_vs_oracle(eng, 2, 16, 2, 256, 64, 1e7, 32768, 1, True, True, "f16")
+    ma, mr = util.assert_close(out, ref, "config 2")
+    print(f"config 2: max-abs {ma:.2e} max-rel {mr:.2e}")
+
+
+def test_config4_verify_block_equals_sequential_decodes():
+    # 24 q / 4 kv heads, 5-token block against a 16384-token cache: equal to 5 sequential decodes within tolerance
+    import torch
+    eng = _engine(24, 4, 256, 16384 + 8, act="f16")
+    out, ref, (q_rot, Kf, Vf, g) = _layer_step_vs_oracle(eng, 4, 24, 4, 256, 64, 1e7, 16384, 5, False, False, "f16")
+    ma, mr = util.assert_close(out, ref, "config 4 block")
+    qd = util.torch_dev(q_rot)
+    for c in range(5):
+        single = eng.decode(0, [(0, 16384 + c, 1)], qd[c:c + 1]).float().cpu().numpy()
+        util.assert_close(single[0], ref[c], f"config 4 sequential decode {c}")
+        util.assert_close(single[0], out[c], f"config 4 block column {c} vs decode")
+    print(f"config 4: max-abs {ma:.2e} max-rel {mr:.2e}")
+
+
+def test_config5_batched_long_context_reduced():
+    # config 5's shape (8 sequences, gate) at 1/16 of its context so the float64 oracle finishes in seconds
+    import torch
+    n_seqs, ctx, nH, nKV, hd = 8, 8192 + 37, 16, 2, 256
+    eng = _engine(nH, nKV, hd, ctx + 4, act="f16", n_seqs=n_seqs, max_cols=8)
+    qs, gs, refs = [], [], []
+    for s in range(n_seqs):
+        q, K, V, g = _config_inputs(50 + s, nH, nKV, hd, ctx - s * 100, 1)
+        Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+        util.load_cache(eng, 0, s, Kc, Vc)
+        refs.append(po.attn_f64(q, Kc, Vc, nH, nKV, hd, ctx - s * 100 - 1, 1, g)[0]); qs.append(q[0]); gs.append(g[0])
+    items = [(s, ctx - s * 100 - 1, 1) for s in range(n_seqs)]
+    out = eng.decode(0, items, util.torch_dev(np.stack(qs), torch.float16), util.torch_dev(np.stack(gs), torch.float16)).float().cpu().numpy()
+    eng.sync()
+    util.assert_close(out, np.stack(refs), "config 5 (reduced)")
+
+
+# ---- edges ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("nH,nKV,hd", [(16, 2, 256), (24, 4, 256), (16, 8, 128), (8, 8, 128), (32, 2, 256)])
+@pytest.mark.parametrize("seq_len", [1, 2, 63, 64, 65, 127, 128, 129, 1000, 4097])
+def test_short_and_ragged_contexts(nH, nKV, hd, seq_len):
+    eng = _engine(nH, nKV, hd, 4200, act="f32", rope_mode="none")
+    q, K, V, g = _config_inputs(7, nH, nKV, hd, seq_len, 1)
+    Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+    util.load_cache(eng, 0, 0, Kc, Vc)
+    out = eng.decode(0, [(0, seq_len - 1, 1)], util.torch_dev(q), util.torch_dev(g)).cpu().numpy()
+    ref = po.attn_f64(q, Kc, Vc, nH, nKV, hd, seq_len - 1, 1, g)
+    assert util.errs(out, ref)[1] < util.REF_REL
+
+
+def test_rows_past_a_columns_position_never_count_even_when_nan():
+    # tests/unit/attn_tile_test.js:43-49: rows at or past the pass's end hold NaN and must not be used
+    import torch
+    nH, nKV, hd, base, nc = 16, 2, 256, 301, 8
+    eng = _engine(nH, nKV, hd, 4096, act="f32", rope_mode="none")
+    kc = eng.cache(0, "k"); vc = eng.cache(0, "v")
+    kc.fill_(0x7e00); vc.fill_(0x7e00)
+    q, K, V, _ = _config_inputs(9, nH, nKV, hd, base + nc, nc)
+    Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+    util.load_cache(eng, 0, 0, Kc, Vc)
+    out = eng.decode(0, [(0, base, nc)], util.torch_dev(q)).cpu().numpy()
+    ref = po.attn_f64(q, Kc, Vc, nH, nKV, hd, base, nc)
+    assert np.all(np.isfinite(out)) and util.errs(out, ref)[1] < util.REF_REL
+    # column 0 must not see the later columns' rows either: poison them too and decode it alone
+    kc[0, base + 1:] = 0x7e00; vc[0, base + 1:] = 0x7e00
+    one = eng.decode(0, [(0, base, 1)], util.torch_dev(q[0:1])).cpu().numpy()
+    assert util.errs(one[0], ref[0])[1] < util.REF_REL
+
+
+def test_padded_strides_and_interleaved_gate():
+    # column strides padded as in tests/unit/attn_tile_test.js:51 (nH*hd + 12 / + 20); q and gate interleaved per head as
+    # q_full [nH][2*hd] (engine/wgsl/attn_dec.js:282-283)
+    import torch
+    nH, nKV, hd, ctx, nc = 16, 2, 256, 700, 3
+    eng = _engine(nH, nKV, hd, 1024, act="f32", rope_mode="none")
+    q, K, V, g = _config_inputs(3, nH, nKV, hd, ctx + nc, nc)
+    Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+    util.load_cache(eng, 0, 0, Kc, Vc)
+    ref = po.attn_f64(q, Kc, Vc, nH, nKV, hd, ctx, nc, g)
+    s0, s1 = 2 * nH * hd + 12, nH * hd + 20
+    qfull = torch.full((nc, s0), float("nan"), device="cuda")
+    qfull[:, :2 * nH * hd] = torch.from_numpy(np.stack([q.reshape(nc, nH, hd), g.reshape(nc, nH, hd)], axis=2).reshape(nc, -1)).cuda()
+    out = torch.full((nc, s1), float("nan"), device="cuda")
+    eng.decode(0, [(0, ctx, nc)], qfull, gate=qfull[:, hd:], out=out, q_head_stride=2 * hd, gate_head_stride=2 * hd)
+    o = out.cpu().numpy()
+    assert util.errs(o[:, :nH * hd], ref)[1] < util.REF_REL
+    assert np.all(np.isnan(o[:, nH * hd:])), "wrote into the padding between columns"
+
+
+def test_fast_mode_stays_inside_the_baseline_tolerance():
+    eng = _engine(16, 2, 256, 8300, act="f16", fast=True)
+    out, ref, _ = _layer_step_vs_oracle(eng, 2, 16, 2, 256, 64, 1e7, 8192, 1, True, False, "f16")
+    util.assert_close(out, ref, "fast mode")
+
+
+def test_sharded_partials_merge_to_the_full_result():
+    # the KV sequence cut into 4 contiguous shards, one layer per "rank"; merged records equal the unsharded decode
+    import torch
+    nH, nKV, hd, ctx, P = 16, 2, 256, 8192 + 11, 4
+    q, K, V, g = _config_inputs(5, nH, nKV, hd, ctx, 2)
+    Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+    ref = po.attn_f64(q[:1], Kc, Vc, nH, nKV, hd, ctx - 1, 1, g[:1])
+    eng = _engine(nH, nKV, hd, ctx, act="f16", rope_mode="none", n_seqs=1)
+    from pooled_b200 import AttnConfig, AttnEngine
+    shard = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=64, rope_theta=1e7, max_seq=ctx, n_layers=P,
+                                  rope_mode="none", act_dtype=torch.float16))
+    bounds = [(r * ctx) // P for r in range(P + 1)]
+    parts = []
+    qd = util.torch_dev(q[:1], torch.float16)
+    for r in range(P):
+        a, b = bounds[r], bounds[r + 1]
+        util.load_cache(shard, r, 0, Kc[a:b], Vc[a:b])
+        parts.append(shard.decode_partial(r, [(0, b - a - 1, 1)], qd))
+    merged = shard.merge(torch.stack(parts), 1, util.torch_dev(g[:1], torch.float16)).float().cpu().numpy()
+    util.assert_close(merged, ref, "sharded merge")
+    # merging one record is the identity (normalise + gate)
+    util.load_cache(eng, 0, 0, Kc, Vc)
+    full = eng.decode(0, [(0, ctx - 1, 1)], qd, util.torch_dev(g[:1], torch.float16)).float().cpu().numpy()
+    one = eng.merge(eng.decode_partial(0, [(0, ctx - 1, 1)], qd)[None], 1, util.torch_dev(g[:1], torch.float16)).float().cpu().numpy()
+    assert np.array_equal(full, one)
+    util.assert_close(full, merged, "sharded vs unsharded")
+
+
+def test_determinism_same_bits_twice():
+    eng = _engine(16, 2, 256, 9000, act="f32", rope_mode="none")
+    q, K, V, g = _config_inputs(8, 16, 2, 256, 8193, 1)
+    util.load_cache(eng, 0, 0, po.np_f16_rne(K), po.np_f16_rne(V))
+    a = eng.decode(0, [(0, 8192, 1)], util.torch_dev(q)).cpu().numpy()
+    b = eng.decode(0, [(0, 8192, 1)], util.torch_dev(q)).cpu().numpy()
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_unsupported_shapes_are_refused_with_a_message():
+    import torch
+    from pooled_b200 import PaError
+    eng = _engine(16, 2, 256, 1024, act="f32", max_cols=16, rope_mode="none")
+    q = torch.zeros((9, 4096), device="cuda")
+    with pytest.raises(PaError) as e:
+        eng.decode(0, [(0, 100, 9)], q)     # 9 columns x 8 heads = 72 query rows per kv head
+    assert e.value.code == -2 and "pa_prefill" in str(e.value)
+    assert eng.stats()["calls"] == 0
