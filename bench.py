@@ -172,19 +172,60 @@ def run_ours(args, w):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # launch mode of the timed region: the 10-layer step captured once into a CUDA graph and replayed (what pooled does
+    # with its pre-encoded per-token command buffers, engine/qwen35.js:4004-4009), or eager C-ABI calls (--no-graph)
+    launches_per_step = None
+    run_step = step
+    graph = None
+    if args.graph and not sharded:
+        s0 = eng.stats()
+        cs = torch.cuda.Stream(device=dev)
+        cs.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(cs):
+            step()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=cs):
+                s1 = eng.stats()
+                step()
+                launches_per_step = eng.stats()["kernel_launches"] - s1["kernel_launches"]
+        torch.cuda.current_stream(dev).wait_stream(cs)
+        run_step = graph.replay
+        for _ in range(3):
+            run_step()
+    barrier()
     clocks = ClockSampler(local); clocks.start()
     st0 = eng.stats()
-    eng.timing_begin(layers * args.steps + 8)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for _ in range(args.steps):
-        step()
+        run_step()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    core_ms, core_n = eng.timing_end()
     st1 = eng.stats()
+    n_launch = launches_per_step * args.steps if launches_per_step is not None else st1["kernel_launches"] - st0["kernel_launches"]
+    # The dominant kernel alone.  Single-sequence steps: the same K steps with only the core kernel of every layer
+    # launched, back to back, between one CUDA-event pair (a pair around each 10-20 us launch would time the launch
+    # gap as well).  Batched / sharded steps: an event pair around every core launch.
+    if not sharded and n_seqs == 1:
+        eng.set_core_only(True)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        core_ms, core_n = e0.elapsed_time(e1), layers * args.steps
+        eng.set_core_only(False)
+        step()
+    else:
+        eng.timing_begin(layers * args.steps + 8)
+        for _ in range(args.steps):
+            step()
+        core_ms, core_n = eng.timing_end()
     eng.sync()
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -238,11 +279,12 @@ def run_ours(args, w):
         "dtype": "f16 cache and activations, f32 accumulate", "data": "synthetic (seeded N(0,1) -> f16, outlier channels x20)" if w["outliers"] else "synthetic (seeded N(0,1) -> f16)",
         "config": {"workload": w["desc"], "kv_rows_per_gpu": chunk, "total_context": total_ctx, "layers_per_step": layers,
                    "l2": "each layer has its own caches; a step touches %d MB per GPU, more than the 126 MB L2, before any row is reused" % (layers * kernel_bytes // 1_000_000),
+                   "launch": "CUDA graph replay of the step" if graph is not None else "eager C-ABI calls",
                    "pct_of_8TBs_nominal": round(100 * value / world / 8000, 1)},
         "roofline": {"bound": "hbm", "kernel": "pa_decode_kernel", "achieved": round(achieved, 1) if achieved else None, "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4) if achieved else None, "peak_source": peak_src, "launches_timed": int(core_n),
                      "us_per_launch": round(core_ms / max(core_n, 1) * 1e3, 2), "algorithmic_bytes_per_launch": kernel_bytes, "traffic": args.traffic},
-        "e2e": e2e, "gpu_launches": int(st1["kernel_launches"] - st0["kernel_launches"]), "clocks": ck,
+        "e2e": e2e, "gpu_launches": int(n_launch), "clocks": ck,
     }
     if rank == 0:
         if world == 1:
@@ -297,9 +339,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager C-ABI calls instead of a CUDA-graph replay of the step")
+    ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling captures)")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the decode kernel, if known")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.layers > 0:
+        w["layers"] = args.layers
     if args.impl == "reference":
         run_reference(args, w)
     else:

@@ -224,6 +224,10 @@ PA_API int pa_get_stats(pa_ctx* ctx, pa_stats* out);
  * tests/bench_attn_ctx.js:39-70 give in the reference.  pa_timing_begin arms up to max_events launches;
  * pa_timing_end waits for them and returns their summed duration and count. */
 PA_API int pa_timing_begin(pa_ctx* ctx, uint32_t max_events);
+/* Profiling aid: while on, pa_attn_layer / pa_decode launch their core kernel only (no RoPE/append, no combine), so
+ * that successive calls put core launches back to back, as tests/bench/attn_tile_bench.js times one kernel alone.
+ * Outputs are not produced while it is on. */
+PA_API int pa_set_core_only(pa_ctx* ctx, int on);
 PA_API int pa_timing_end(pa_ctx* ctx, double* core_ms, uint64_t* core_launches);
 
 #ifdef __cplusplus

@@ -168,6 +168,10 @@ class AttnEngine:
         self._ck(self.L.pa_get_stats(self.ctx, C.byref(s)))
         return {"kernel_launches": s.kernel_launches, "kv_bytes_streamed": s.kv_bytes_streamed, "calls": s.calls}
 
+    def set_core_only(self, on: bool):
+        """Profiling aid: layer / decode calls launch their core kernel only (outputs are not produced)."""
+        self._ck(self.L.pa_set_core_only(self.ctx, 1 if on else 0))
+
     def timing_begin(self, max_events: int = 4096):
         self._ck(self.L.pa_timing_begin(self.ctx, max_events))
 

@@ -3,6 +3,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -263,6 +264,11 @@ extern "C" int pa_get_stats(pa_ctx* ctx, pa_stats* out) {
   return PA_OK;
 }
 
+extern "C" int pa_set_core_only(pa_ctx* ctx, int on) {
+  if (!ctx) return PA_EINVAL;
+  ctx->core_only = on != 0;
+  return PA_OK;
+}
 extern "C" int pa_timing_begin(pa_ctx* ctx, uint32_t max_events) {
   if (!ctx || max_events < 1) return PA_EINVAL;
   cudaSetDevice(ctx->device);
@@ -415,7 +421,7 @@ static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, Item
 }
 
 static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
-                       uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who) {
+                       uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false) {
   pa_ctx* ctx = L->ctx;
   if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
   if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
@@ -430,6 +436,18 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   p.n_heads = ctx->cfg.n_heads; p.G = ctx->G; p.max_seq = L->max_seq;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)ctx->cfg.head_dim));
   p.err = ctx->dev_err;
+  // after this library's own RoPE/append kernel the only rows in flux are the call's new ones: older rows may be
+  // fetched while that kernel still runs
+  p.prefetch_old_rows = after_own_append ? 1u : 0u;
+#ifdef PA_TRACE
+  {
+    static unsigned long long* tr = nullptr;
+    if (!tr) cudaMalloc(&tr, 1024 * 256 * 8);
+    cudaMemsetAsync(tr, 0, 1024 * 256 * 8, st);
+    p.trace = tr;
+    if (getenv("PA_TRACE_PTR")) { FILE* f = fopen(getenv("PA_TRACE_PTR"), "w"); fprintf(f, "%llu\n", (unsigned long long)(uintptr_t)tr); fclose(f); }
+  }
+#endif
   const int nt = (int)ceil_div(max_cols * ctx->G, 8);
   timing_mark(ctx, st, 0);
   if (max_rows > 0) CU_TRY(ctx, launch_decode(L, p, dim3(ns, ctx->cfg.n_kv_heads, n_items), nt, st));
@@ -443,8 +461,8 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   c.act_f16 = ctx->cfg.act_dtype == PA_F16;
   c.partial_out = partial; c.partial_rows = (uint64_t)total_cols * ctx->cfg.n_heads;
   c.items = p.items; c.n_items = n_items;
-  CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
-  ctx->stats.kernel_launches += 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
+  if (!ctx->core_only) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
+  ctx->stats.kernel_launches += ctx->core_only ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
   return PA_OK;
 }
 
@@ -538,16 +556,17 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer: null q, k, v or out");
   if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer")) return rc;
   cudaSetDevice(ctx->device);
-  if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
-                                ctx->cfg.act_dtype == PA_F16, st))
-    return rc;
+  if (!ctx->core_only)
+    if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
+                                  ctx->cfg.act_dtype == PA_F16, st))
+      return rc;
   // the decode / verify kernel carries at most 64 query rows per kv head; wider passes are prefill chunks
   // (the reference takes the tiled kernel on full-width non-verify passes, engine/qwen35.js:2489)
   bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
   if (prefill)
     return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
   pa_item it{seq, pos, n_cols, 0};
-  return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer");
+  return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", !ctx->core_only);
 }
 
 extern "C" int pa_attn_layer(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t q_col_stride,

@@ -106,10 +106,33 @@ __device__ __forceinline__ void split_h(float x, __half& hi, __half& lo) {
   lo = __float2half_rn(x - __half2float(hi));
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may begin before its predecessor in the
+// stream has finished, once every CTA of the predecessor has called pdl_trigger() or exited; pdl_wait() returns
+// when the predecessor has completed and its writes are visible.  Rule used by this library: every kernel calls
+// pdl_wait() before its first global write and before reading anything an earlier kernel of the stream wrote, and
+// only the RoPE/append kernel triggers before its own wait, so whatever runs ahead of its predecessor's end
+// overlaps nothing but that one kernel.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 
 constexpr int kMaxItems = 32;     // items of one batched decode call
 constexpr int kMaxRows = 64;      // query rows (columns x heads of one kv head) one decode CTA carries
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 struct ItemList {
   uint32_t seq[kMaxItems];
@@ -141,6 +164,7 @@ struct pa_ctx {
   std::vector<cudaEvent_t> ev;   // timing: event pairs around core-kernel launches
   size_t ev_used = 0;
   bool timing = false;
+  bool core_only = false;        // profiling aid: calls launch their core kernel only
   bool failed = false;
   std::string err;
   pa_stats stats{};

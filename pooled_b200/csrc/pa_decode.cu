@@ -22,6 +22,13 @@
 
 namespace pa {
 
+#ifdef PA_TRACE
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TR(slot) do { if (p.trace && lane == 0 && (warp == 0 || warp == 4)) p.trace[(((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 256 + (slot)] = gtime(); } while (0)
+#else
+#define TR(slot) do {} while (0)
+#endif
+
 constexpr int kT = 64;             // positions per tile
 constexpr int kConsumers = 128;    // 4 consumer warps
 constexpr int kDecThreads = 160;   // + 1 producer warp
@@ -80,17 +87,66 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                  vempty = vfull + kMaxStages * 8;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (tid == 0) {
-    *s_err = 0;
-    for (uint32_t s = 0; s < NS; ++s) {
-      mbar_init(kfull + 8 * s, 1);
-      mbar_init(vfull + 8 * s, 1);
-      mbar_init(kempty + 8 * s, 4);
-      mbar_init(vempty + 8 * s, 4);
+  TR(0);
+  // The consumers put their q loads in flight before the producer may start: a q load issued behind the
+  // first 190 KB of K/V tiles of every SM would wait for all of them at the memory controllers.
+  // With few query rows the values wait in registers across the barrier; with many they are staged into shared
+  // memory first (the producer then starts about one memory round trip later).
+  constexpr int QLD = ROWS * (HD / 2) / kConsumers;
+  constexpr bool Q_IN_REGS = QLD <= 16;
+  float2 qreg[Q_IN_REGS ? QLD : 1];
+  const uint32_t G = p.G, live_rows = n_cols * G;
+  auto q_load = [&](int idx) {
+    const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+    float2 x = make_float2(0.f, 0.f);
+    if ((uint32_t)row < live_rows) {
+      const uint32_t c = row / G, hh = row % G;
+      const uint64_t off = (uint64_t)(p.items.col0[item] + c) * p.q_col_stride + (uint64_t)(g * G + hh) * p.q_head_stride + d;
+      if (p.q_f16) x = __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(p.q) + off));
+      else x = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.q) + off);
     }
-    fence_barrier_init();
+    return x;
+  };
+  auto q_store = [&](int idx, float2 x) {
+    const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+    __half h0, l0, h1, l1;
+    split_h(x.x, h0, l0); split_h(x.y, h1, l1);
+    *reinterpret_cast<__half2*>(q_hi + row * QP + d * 2) = __halves2half2(h0, h1);
+    if (PRECISE) *reinterpret_cast<__half2*>(q_lo + row * QP + d * 2) = __halves2half2(l0, l1);
+  };
+  if (warp < 4) {
+    pdl_wait();      // q (and the partial buffers written at the end) belong to earlier kernels until here
+    pdl_trigger();
+    if (Q_IN_REGS) {
+#pragma unroll
+      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = q_load(tid + it * kConsumers);
+    } else {
+#pragma unroll 8
+      for (int it = 0; it < QLD; ++it) q_store(tid + it * kConsumers, q_load(tid + it * kConsumers));
+    }
   }
-  __syncthreads();
+  // The producer warp sets up the barriers and goes; the consumers meet it at named barrier 2.  When the call may
+  // not fetch ahead of its predecessor, the producer also waits (named barrier 3) until the q loads are in flight:
+  // a q load issued behind the first 190 KB of K/V tiles of every SM would queue behind all of them.
+  if (warp == 4) {
+    if (lane == 0) {
+      *s_err = 0;
+      for (uint32_t s = 0; s < NS; ++s) {
+        mbar_init(kfull + 8 * s, 1);
+        mbar_init(vfull + 8 * s, 1);
+        mbar_init(kempty + 8 * s, 4);
+        mbar_init(vempty + 8 * s, 4);
+      }
+      fence_barrier_init();
+    }
+    __syncwarp();
+    named_bar_arrive(2, kDecThreads);
+    if (!p.prefetch_old_rows) named_bar_sync(3, kDecThreads);
+  } else {
+    if (!p.prefetch_old_rows) named_bar_arrive(3, kDecThreads);
+    named_bar_sync(2, kDecThreads);
+  }
+  TR(warp == 4 ? 128 : 1);
 
   if (warp == 4) {
     // ---------------------------------------------------------------- producer ----
@@ -99,12 +155,18 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       prefetch_tmap(&tm_v);
       const int y0 = (int)(p.items.seq[item] * p.max_seq + tile0 * kT);
       const int z = (int)(g * CH);
+      const uint32_t old_rows = n_rows - min(n_rows, n_cols);   // rows below the ones this call's columns added
+      bool waited = !p.prefetch_old_rows;
+      if (waited) pdl_wait();
       for (uint32_t i = 0; i < n_tiles; ++i) {
         const uint32_t s = i % NS, ph = (i / NS) & 1;
+        if (!waited && (tile0 + i + 1) * kT > old_rows) { pdl_wait(); waited = true; }
         mbar_wait(kempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
+        if (i < 30) TR(130 + 2 * i);
         mbar_expect_tx(kfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s);
         mbar_wait(vempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
+        if (i < 30) TR(131 + 2 * i);
         mbar_expect_tx(vfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
       }
@@ -124,27 +186,10 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
   // ------------------------------------------------------------------ consumers ----
   const int w = warp, r = lane >> 2, j = lane & 3;
-  const uint32_t G = p.G, live_rows = n_cols * G;
 
-  // q rows of this kv head -> shared memory as f16 hi (+ lo); rows past live_rows are zero
-  for (int idx = tid; idx < ROWS * (HD / 2); idx += kConsumers) {
-    const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
-    float x0 = 0.f, x1 = 0.f;
-    if ((uint32_t)row < live_rows) {
-      const uint32_t c = row / G, hh = row % G;
-      const uint64_t off = (uint64_t)(p.items.col0[item] + c) * p.q_col_stride + (uint64_t)(g * G + hh) * p.q_head_stride + d;
-      if (p.q_f16) {
-        const __half2 h2 = *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(p.q) + off);
-        x0 = __low2float(h2); x1 = __high2float(h2);
-      } else {
-        const float2 f2 = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.q) + off);
-        x0 = f2.x; x1 = f2.y;
-      }
-    }
-    __half h0, l0, h1, l1;
-    split_h(x0, h0, l0); split_h(x1, h1, l1);
-    *reinterpret_cast<__half2*>(q_hi + row * QP + d * 2) = __halves2half2(h0, h1);
-    if (PRECISE) *reinterpret_cast<__half2*>(q_lo + row * QP + d * 2) = __halves2half2(l0, l1);
+  if (Q_IN_REGS) {
+#pragma unroll
+    for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) q_store(tid + it * kConsumers, qreg[it]);
   }
 
   // causal limit of the two rows this thread owns in every 8-row group
@@ -170,6 +215,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       for (int e = 0; e < 4; ++e) oacc[mt][nt][e] = 0.f;
   }
   named_bar_sync(1, kConsumers);   // q visible
+  TR(2);
 
   const uint32_t q_hi_s = smem_u32(q_hi), q_lo_s = smem_u32(q_lo), p_hi_s = smem_u32(p_hi), p_lo_s = smem_u32(p_lo);
 
@@ -179,10 +225,18 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const uint32_t ks_base = smem_u32(k_slots + s * SLOT), vs_base = smem_u32(v_slots + s * SLOT);
 
     // ---- S^T = K . Q^T for positions 16w .. 16w+15 ----
-    float sacc[NT][4];
+    // NA independent accumulator sets per row group: with one, the 2 * HD/16 MMAs of a group form a single
+    // dependency chain and the tensor pipe idles between them
+    constexpr int NA = NT >= 4 ? 1 : 4 / NT;
+    float sacc[NT][4], sacc_x[NT][NA > 1 ? NA - 1 : 1][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+      for (int a = 0; a < NA - 1; ++a) sacc_x[nt][a][0] = sacc_x[nt][a][1] = sacc_x[nt][a][2] = sacc_x[nt][a][3] = 0.f;
+    }
     mbar_wait(kfull + 8 * s, ph, s_err, WAIT_KFULL);
+    if (i < 15) TR(8 + 8 * i);
     {
       const uint32_t krow = 16 * w + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll 4
@@ -200,17 +254,24 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           uint32_t b0, b1, b2, b3;
           ldsm_x4(q_hi_s + qoff, b0, b1, b2, b3);
           mma_16816(sacc[nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
-          mma_16816(sacc[nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
+          mma_16816(NA >= 2 ? sacc_x[nt][0] : sacc[nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
           if (PRECISE) {
             ldsm_x4(q_lo_s + qoff, b0, b1, b2, b3);
-            mma_16816(sacc[nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
-            mma_16816(sacc[nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
+            mma_16816(NA >= 4 ? sacc_x[nt][1] : sacc[nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
+            mma_16816(NA >= 4 ? sacc_x[nt][2] : (NA >= 2 ? sacc_x[nt][0] : sacc[nt]), a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
           }
         }
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(kempty + 8 * s);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int a = 0; a < NA - 1; ++a)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[nt][e] += sacc_x[nt][a][e];
+    if (i < 15) TR(9 + 8 * i);
 
     // ---- scale, causal mask, tile maximum per row ----
     const uint32_t pos_a = tile_pos + 16 * w + r, pos_b = pos_a + 8;
@@ -232,6 +293,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       if (r == 0) { s_max[w * ROWS + nt * 8 + 2 * j] = tmax[nt][0]; s_max[w * ROWS + nt * 8 + 2 * j + 1] = tmax[nt][1]; }
     }
     named_bar_sync(1, kConsumers);
+    if (i < 15) TR(10 + 8 * i);
 
     // ---- new running maximum, weights P = 2^(s - m), rescale factor ----
     float alpha[NT][2];
@@ -270,7 +332,9 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         oacc[mt][nt][2] *= alpha[nt][0]; oacc[mt][nt][3] *= alpha[nt][1];
       }
 
+    if (i < 15) TR(11 + 8 * i);
     mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
+    if (i < 15) TR(12 + 8 * i);
     if (tile_pos + kT > n_rows) {
       // rows of the tile past the sequence end hold whatever the cache holds there (possibly NaN):
       // their weights are zero, but 0 * NaN is NaN, so clear them
@@ -281,6 +345,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       }
     }
     named_bar_sync(1, kConsumers);   // P (and the cleared rows) visible to every warp
+    if (i < 15) TR(13 + 8 * i);
 
     // ---- O^T += V^T . P^T, dims (w*MT + mt)*16 .. +15 ----
 #pragma unroll
@@ -309,6 +374,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(vempty + 8 * s);
+    if (i < 15) TR(14 + 8 * i);
   }
 
   // ---- partial (o, m, l) per row ----
@@ -346,6 +412,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       }
     }
   if (*s_err && tid == 0) atomicMax(p.err, *s_err);
+  TR(3);
 }
 
 // ------------------------------------------------------------------------------ combine --
@@ -357,6 +424,8 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   __shared__ float s_acc[8][HD];
   const uint32_t prow = blockIdx.x, col = prow / p.n_heads, h = prow % p.n_heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_wait();      // the partial records belong to the kernel before this one
+  pdl_trigger();
   uint32_t ns = p.fixed_parts;
   if (ns == 0) {
     uint32_t it = 0;
@@ -441,15 +510,15 @@ static cudaError_t launch_decode_t(const pa_layer* L, const DecodeParams& p, dim
   if (stages < 2) return cudaErrorInvalidConfiguration;
   pp.n_stages = (uint32_t)stages;
   const int bytes = S::total_bytes(stages);
-  static bool attr_set = false;
+  static bool attr_set[64] = {};
   auto kern = pa_decode_kernel<HD, NT, PRECISE>;
-  if (!attr_set) {
+  const int dev = L->ctx->device & 63;
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    attr_set[dev] = true;
   }
-  kern<<<grid, kDecThreads, bytes, st>>>(L->tm_k64, L->tm_v64, pp);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, dim3(kDecThreads), (size_t)bytes, st, L->tm_k64, L->tm_v64, pp);
 }
 
 template <int HD, bool PRECISE>
@@ -470,10 +539,9 @@ cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, i
 }
 
 cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, cudaStream_t st) {
-  if (head_dim == 256) pa_combine_kernel<256><<<rows, 256, 0, st>>>(p);
-  else if (head_dim == 128) pa_combine_kernel<128><<<rows, 256, 0, st>>>(p);
-  else return cudaErrorInvalidValue;
-  return cudaGetLastError();
+  if (head_dim == 256) return launch_pdl(pa_combine_kernel<256>, dim3(rows), dim3(256), 0, st, p);
+  if (head_dim == 128) return launch_pdl(pa_combine_kernel<128>, dim3(rows), dim3(256), 0, st, p);
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace pa

@@ -12,8 +12,10 @@ struct DecodeParams {
   float* part_ml;           // [rows][n_splits][2]   (m in natural-log units, l)
   uint32_t n_splits;
   uint32_t n_heads, G, max_seq, n_stages;
+  uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends
   float scale_log2;         // log2(e) / sqrt(head_dim)
   uint32_t* err;
+  unsigned long long* trace;   // development builds only (PA_TRACE): per-CTA timestamps; nullptr otherwise
   ItemList items;
 };
 

@@ -30,6 +30,10 @@ __global__ void __launch_bounds__(256) pa_rope_append_kernel(const RopeParams p)
   __shared__ double s_c[128], s_s[128];
   __shared__ float s_cf[128], s_sf[128];
   const uint32_t col = blockIdx.x, half = p.n_rot / 2;
+  // The kernel after this one may start fetching old cache rows while this one runs (it never touches the rows or
+  // the rotated q written here before its own wait); this kernel itself writes nothing before its predecessor ends.
+  pdl_trigger();
+  pdl_wait();
   if (p.mode == PA_ROPE_F64) {
     for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
       const double ang = __dmul_rn((double)(p.pos + col), p.inv_freq[i]);
@@ -101,8 +105,7 @@ __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams
 }
 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
-  pa_rope_append_kernel<<<n_cols, 256, 0, st>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(pa_rope_append_kernel, dim3(n_cols), dim3(256), 0, st, p);
 }
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st) {
   pa_sigmoid_mul_kernel<<<n_cols, 256, 0, st>>>(p);

@@ -70,6 +70,7 @@ SYMBOLS = {
     "pa_attn_layer_host": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
     "pa_get_stats": (_i, [_vp, C.POINTER(PaStats)]),
     "pa_timing_begin": (_i, [_vp, _u32]),
+    "pa_set_core_only": (_i, [_vp, _i]),
     "pa_timing_end": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(_u64)]),
 }
 
