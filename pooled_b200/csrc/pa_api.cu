@@ -18,7 +18,7 @@ cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
-cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, cudaStream_t st);
+cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
 }  // namespace pa
 
 using namespace pa;
@@ -213,8 +213,6 @@ extern "C" int pa_layer_create(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, p
   }
   int rc = make_cache_map(ctx, &L->tm_k64, L->k, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
   if (!rc) rc = make_cache_map(ctx, &L->tm_v64, L->v, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
-  if (!rc) rc = make_cache_map(ctx, &L->tm_k128, L->k, rows, ctx->kv_dim, ctx->cfg.head_dim, 128);
-  if (!rc) rc = make_cache_map(ctx, &L->tm_v128, L->v, rows, ctx->kv_dim, ctx->cfg.head_dim, 128);
   if (rc) { cudaFree(L->k); cudaFree(L->v); delete L; return rc; }
   *out = L;
   return PA_OK;
@@ -508,7 +506,9 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   if (!q || !out) return fail(ctx, PA_EINVAL, "pa_prefill: null q or out");
   if (int rc = check_cols(L, seq, pos, n_cols, "pa_prefill")) return rc;
   if (!prefill_supported(ctx)) return fail(ctx, PA_EUNSUPPORTED, "pa_prefill: head_dim %u is outside the tiled prefill kernel's shapes", ctx->cfg.head_dim);
-  if ((qcs & 3) || (qhs & 3) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "pa_prefill: q strides must be multiples of 4 elements and q 16-byte aligned");
+  const uint64_t qm = q_dtype == PA_F16 ? 7 : 3, om = ctx->cfg.act_dtype == PA_F16 ? 7 : 3;   // 16-byte vector accesses
+  if ((qcs & qm) || (qhs & qm) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "pa_prefill: q strides must be multiples of 16 bytes and q 16-byte aligned");
+  if ((ocs & om) || ((uintptr_t)out & 15)) return fail(ctx, PA_EINVAL, "pa_prefill: the out column stride must be a multiple of 16 bytes and out 16-byte aligned");
   cudaSetDevice(ctx->device);
   PrefillParams p{};
   p.q = q; p.q_f16 = q_dtype == PA_F16; p.q_col_stride = qcs; p.q_head_stride = qhs;
@@ -517,8 +517,14 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   p.seq = seq; p.pos = pos - L->origin; p.n_cols = n_cols; p.n_heads = ctx->cfg.n_heads; p.G = ctx->G; p.max_seq = L->max_seq;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)ctx->cfg.head_dim));
   p.err = ctx->dev_err;
+  // Tensor maps of this call: the sequence's rows [0, pos + n_cols) only, so that a K/V tile reaching past the last
+  // appended row is zero-filled by TMA instead of carrying whatever the cache holds there (0 * NaN is NaN).
+  CUtensorMap tm_k, tm_v;
+  const uint64_t seq_off = (uint64_t)seq * L->max_seq * ctx->kv_dim;
+  if (int rc = make_cache_map(ctx, &tm_k, L->k + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
+  if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
   timing_mark(ctx, st, 0);
-  CU_TRY(ctx, launch_prefill(L, p, st));
+  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, st));
   timing_mark(ctx, st, 1);
   ctx->stats.kernel_launches++; ctx->stats.calls++;
   ctx->stats.kv_bytes_streamed += 2ull * (pos + n_cols) * ctx->kv_dim * 2;

@@ -176,6 +176,5 @@ struct pa_layer {
   uint32_t origin = 0;           // global position of cache row 0 (a shard of a longer sequence)
   __half* k = nullptr;
   __half* v = nullptr;
-  CUtensorMap tm_k64, tm_v64;    // 64-row boxes for the decode kernel
-  CUtensorMap tm_k128, tm_v128;  // 128-row boxes for the prefill kernel
+  CUtensorMap tm_k64, tm_v64;    // 64-row boxes over all sequences' rows, for the decode kernel
 };

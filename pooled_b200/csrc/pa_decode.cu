@@ -417,12 +417,15 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
 // ------------------------------------------------------------------------------ combine --
 
+// grid (query rows, HD / 64): one CTA per (column, head, 64-dim slice).  Two memory round trips in all: every
+// thread fetches the (m, l) of up to two splits at once, then 16 groups of 16 lanes (a float4 each) walk the splits
+// 16 apart with four loads in flight per lane.  Every sum has a fixed order.
 template <int HD>
 __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) {
   __shared__ float s_w[512];
-  __shared__ float s_red[8];
-  __shared__ float s_acc[8][HD];
-  const uint32_t prow = blockIdx.x, col = prow / p.n_heads, h = prow % p.n_heads;
+  __shared__ float s_red[8], s_red2[8];
+  __shared__ float4 s_acc[16][16];
+  const uint32_t prow = blockIdx.x, slice = blockIdx.y, col = prow / p.n_heads, h = prow % p.n_heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_wait();      // the partial records belong to the kernel before this one
   pdl_trigger();
@@ -435,8 +438,10 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     ns = tiles ? (tiles + tps - 1) / tps : 0;   // a shard that holds no row of the item: an empty record
   }
   const float* ml = p.ml + prow * p.ml_row_stride;
-  float M = -3.0e38f;
-  for (uint32_t s = tid; s < ns; s += 256) M = fmaxf(M, ml[s * p.ml_part_stride]);
+  float m0 = -3.0e38f, l0 = 0.f, m1 = -3.0e38f, l1 = 0.f;
+  if ((uint32_t)tid < ns) { m0 = ml[tid * p.ml_part_stride]; l0 = ml[tid * p.ml_part_stride + 1]; }
+  if ((uint32_t)tid + 256 < ns) { m1 = ml[(tid + 256) * p.ml_part_stride]; l1 = ml[(tid + 256) * p.ml_part_stride + 1]; }
+  float M = fmaxf(m0, m1);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
   if (lane == 0) s_red[warp] = M;
@@ -444,49 +449,49 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   M = s_red[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) M = fmaxf(M, s_red[i]);
-  __syncthreads();
-  float Lp = 0.f;
-  for (uint32_t s = tid; s < ns; s += 256) {
-    const float wgt = __expf(ml[s * p.ml_part_stride] - M);
-    s_w[s] = wgt;
-    Lp += ml[s * p.ml_part_stride + 1] * wgt;
-  }
+  const float w0 = (uint32_t)tid < ns ? __expf(m0 - M) : 0.f, w1 = (uint32_t)tid + 256 < ns ? __expf(m1 - M) : 0.f;
+  s_w[tid] = w0; s_w[tid + 256] = w1;
+  float Lp = l0 * w0 + l1 * w1;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) Lp += __shfl_xor_sync(0xffffffffu, Lp, o);
-  if (lane == 0) s_red[warp] = Lp;
+  if (lane == 0) s_red2[warp] = Lp;
   __syncthreads();
   float Lsum = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) Lsum += s_red[i];
+  for (int i = 0; i < 8; ++i) Lsum += s_red2[i];
 
-  constexpr int V4 = HD / 128;   // float4s per lane
-  float4 acc[V4];
+  const int grp = tid >> 4, ln = tid & 15;
+  const float* ob = p.o + prow * p.o_row_stride + slice * 64 + ln * 4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t s0 = grp; s0 < ns; s0 += 64) {
+    float4 x[4];
 #pragma unroll
-  for (int v = 0; v < V4; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float* ob = p.o + prow * p.o_row_stride;
-  for (uint32_t s = warp; s < ns; s += 8) {
-    const float wgt = s_w[s];
-    const float4* src = reinterpret_cast<const float4*>(ob + s * p.o_part_stride);
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t s = s0 + 16 * u;
+      x[u] = s < ns ? *reinterpret_cast<const float4*>(ob + s * p.o_part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 #pragma unroll
-    for (int v = 0; v < V4; ++v) {
-      const float4 x = src[v * 32 + lane];
-      acc[v].x += x.x * wgt; acc[v].y += x.y * wgt; acc[v].z += x.z * wgt; acc[v].w += x.w * wgt;
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t s = s0 + 16 * u;
+      const float wgt = s < ns ? s_w[s] : 0.f;
+      acc.x += x[u].x * wgt; acc.y += x[u].y * wgt; acc.z += x[u].z * wgt; acc.w += x[u].w * wgt;
     }
   }
-#pragma unroll
-  for (int v = 0; v < V4; ++v) *reinterpret_cast<float4*>(&s_acc[warp][(v * 32 + lane) * 4]) = acc[v];
+  s_acc[grp][ln] = acc;
   __syncthreads();
-  for (int d = tid; d < HD; d += 256) {
-    float t = s_acc[0][d];
+  if (tid < 64) {
+    const float* sa = reinterpret_cast<const float*>(s_acc);
+    float t = sa[tid];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) t += s_acc[i][d];
+    for (int i = 1; i < 16; ++i) t += sa[i * 64 + tid];
+    const uint32_t d = slice * 64 + tid;
     if (p.partial_out) {
       p.partial_out[(uint64_t)prow * HD + d] = t;
       if (d == 0) {
         float* mlo = p.partial_out + p.partial_rows * HD + (uint64_t)prow * 2;
         mlo[0] = M; mlo[1] = Lsum;
       }
-      continue;
+      return;
     }
     float rv = t / Lsum;
     if (p.gate) {
@@ -539,8 +544,8 @@ cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, i
 }
 
 cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, cudaStream_t st) {
-  if (head_dim == 256) return launch_pdl(pa_combine_kernel<256>, dim3(rows), dim3(256), 0, st, p);
-  if (head_dim == 128) return launch_pdl(pa_combine_kernel<128>, dim3(rows), dim3(256), 0, st, p);
+  if (head_dim == 256) return launch_pdl(pa_combine_kernel<256>, dim3(rows, 4), dim3(256), 0, st, p);
+  if (head_dim == 128) return launch_pdl(pa_combine_kernel<128>, dim3(rows, 2), dim3(256), 0, st, p);
   return cudaErrorInvalidValue;
 }
 

@@ -1,6 +1,365 @@
-// placeholder until the tiled prefill kernel lands
+// Tiled causal prefill attention on the 5th-generation tensor cores: tcgen05.mma with the accumulators in tensor
+// memory (TMEM), K/V tiles brought in by TMA.
+//
+// One CTA takes 128 consecutive query columns of one q head and walks the KV cache in tiles of 64 positions up to
+// the causal diagonal.  K/V tiles of the G heads of a GQA group are the same bytes, read by G CTAs that run at about
+// the same time; the caches of a prefill fit the 126 MB L2, so HBM sees them once.
+//
+//   warp 0      TMA producer: K and V tiles (64 x head_dim f16, 128-byte swizzle) into two-slot rings
+//   warp 1      MMA issuer (one thread): S = Q K^T into a double-buffered TMEM tile (128 x 64 f32), then
+//               O += P V into the TMEM accumulator (128 x head_dim f32); completion is signalled to mbarriers
+//               with tcgen05.commit
+//   warp 2      allocates / frees tensor memory
+//   warps 4-7   softmax: thread r owns query row r (TMEM lane r): tcgen05.ld of its S row, scale + causal mask,
+//               running max / sum, P = 2^(s - m) as f16 into shared memory in the K-major swizzled layout the
+//               second MMA reads, and the epilogue (O / l, sigmoid gate, store)
+// S(j+1) is issued before the softmax of tile j has finished, so the tensor cores work on the next scores while
+// the weights of the current tile are being formed.  O is rescaled only when a row's running maximum has grown by
+// more than 2^8 since its last rescale (weights stay below 2^8, exact in f32 sums and safe in f16); the rescale
+// waits for the previous P V to retire and rewrites the row's TMEM accumulator.
+//
+// Stands in for attn_flash_tile + attn_combine_tile + sigmoid_mul_mc of pooled (engine/wgsl/attn_tile.js:108-193,
+// engine/wgsl/qwen35.js:877-887); there the pass is 16 columns wide and split over the sequence, here a pass takes
+// the whole chunk and needs no split/combine because one CTA walks all of its keys.
 #include "pa_params.cuh"
+
 namespace pa {
-int prefill_supported(const pa_ctx*) { return 0; }
-cudaError_t launch_prefill(const pa_layer*, const PrefillParams&, cudaStream_t) { return cudaErrorNotSupported; }
+
+constexpr int kBM = 128;   // query rows per CTA
+constexpr int kBN = 64;    // keys per tile
+constexpr int kPfThreads = 256;
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
 }
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D (TMEM) (+)= A (smem descriptor) * B (smem descriptor), f16 inputs, f32 accumulate, issued by one thread
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// the mbarrier gets one arrival when every MMA issued so far by this thread has retired
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive f32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  K-major operand (rows of 64 f16 = 128 bytes, 8-row groups of
+// 1024 bytes): sbo = 1024, lbo unused.  MN-major operand (64 contiguous MN elements per row of 128 bytes, 8 rows
+// along K per 1024-byte group): lbo = distance between 64-element chunks along MN, sbo = 1024.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;   // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: f16 x f16 -> f32, A K-major, B K-major or MN-major, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t M, uint32_t N, uint32_t b_mn_major) {
+  return (1u << 4) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+template <int HD>
+struct PfSmem {
+  static constexpr int Q_BYTES = HD * 256;          // [HD/64][128 rows][128 B]
+  static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
+  static constexpr int P_BYTES = kBM * 128;         // [128 rows][64 keys f16]
+  static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES, OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int TOTAL = 1024 + OFF_BAR + 256;
+  static constexpr int TMEM_COLS = HD == 256 ? 512 : 256;   // S0, S1 (64 each) + O (HD), rounded to a power of two
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kPfThreads, 1)
+pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+  using L = PfSmem<HD>;
+  constexpr int CH = HD / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = base;
+  uint8_t* p_s = base + L::OFF_P;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 20);
+  volatile uint32_t* s_err = s_tmem + 1;
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which * 2 + idx); };
+  enum { K_FULL = 0, K_EMPTY, V_FULL, V_EMPTY, S_FULL, S_EMPTY, P_FULL, P_EMPTY, O_DONE };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t q_tile = gridDim.x - 1 - blockIdx.x;   // longest rows first
+  const uint32_t h = blockIdx.y, g = h / p.G;
+  const uint32_t c0 = q_tile * kBM;
+  const uint32_t rows_valid = min((uint32_t)kBM, p.n_cols - c0);
+  const uint32_t p0 = p.pos + c0;                       // cache row of column c0's own token
+  const uint32_t n_tiles = (p0 + rows_valid + kBN - 1) / kBN;
+
+  if (warp == 1 && lane == 0) {
+    *s_err = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(BAR(K_FULL, i), 1); mbar_init(BAR(K_EMPTY, i), 1);
+      mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1);
+      mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(S_EMPTY, i), 128);
+      mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(P_EMPTY, i), 1);
+    }
+    mbar_init(BAR(O_DONE, 0), 1);
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32((const void*)s_tmem), L::TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  pdl_wait();   // q (and, for a chunked prefill, the appended rows) come from the kernel before this one
+
+  // ---- Q tile -> shared memory: f16, K-major, 128-byte swizzle ----
+  for (int idx = tid; idx < kBM * (HD / 8); idx += kPfThreads) {
+    const uint32_t row = idx / (HD / 8), c16 = idx % (HD / 8);
+    uint4 packed = make_uint4(0, 0, 0, 0);
+    if (row < rows_valid) {
+      const uint64_t off = (uint64_t)(c0 + row) * p.q_col_stride + (uint64_t)h * p.q_head_stride + c16 * 8;
+      if (p.q_f16) {
+        packed = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off);
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off);
+        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + 4);
+        packed = make_uint4(pack_h2(a.x, a.y), pack_h2(a.z, a.w), pack_h2(b.x, b.y), pack_h2(b.z, b.w));
+      }
+    }
+    *reinterpret_cast<uint4*>(q_s + (c16 >> 3) * (kBM * 128) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4)) = packed;
+  }
+  fence_proxy_async();   // the tensor cores read Q through the async proxy
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t t_s0 = tmem, t_o = tmem + 2 * kBN;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer ----
+    if (lane == 0) {
+      prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+      for (uint32_t j = 0; j < n_tiles; ++j) {
+        const uint32_t st = j & 1, u = j >> 1;
+        mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
+        mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
+        tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)(j * kBN), (int)(g * CH), BAR(K_FULL, st));
+        mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
+        mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
+        tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)(j * kBN), (int)(g * CH), BAR(V_FULL, st));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
+      const uint32_t q_addr = smem_u32(q_s);
+      auto issue_qk = [&](uint32_t j) {
+        const uint32_t b = j & 1, u = j >> 1;
+        mbar_wait(BAR(K_FULL, b), u & 1, s_err, WAIT_KFULL);
+        mbar_wait(BAR(S_EMPTY, b), (u & 1) ^ 1, s_err, WAIT_EMPTY);
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(base + L::OFF_K + b * L::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t ad = smem_desc(q_addr + (ks >> 2) * (kBM * 128) + (ks & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc(k_addr + (ks >> 2) * (kBN * 128) + (ks & 3) * 32, 16, 1024);
+          umma_f16(t_s0 + b * kBN, ad, bd, idesc_qk, ks > 0);
+        }
+        umma_commit(BAR(K_EMPTY, b));
+        umma_commit(BAR(S_FULL, b));
+      };
+      issue_qk(0);
+      for (uint32_t j = 0; j < n_tiles; ++j) {
+        const uint32_t b = j & 1, u = j >> 1;
+        if (j + 1 < n_tiles) issue_qk(j + 1);
+        mbar_wait(BAR(P_FULL, b), u & 1, s_err, WAIT_QFULL);
+        mbar_wait(BAR(V_FULL, b), u & 1, s_err, WAIT_VFULL);
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(p_s + b * L::P_BYTES), v_addr = smem_u32(base + L::OFF_V + b * L::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const uint64_t ad = smem_desc(p_addr + ks * 32, 16, 1024);
+          const uint64_t bd = smem_desc(v_addr + ks * 2048, kBN * 128, 1024);
+          umma_f16(t_o, ad, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(BAR(V_EMPTY, b));
+        umma_commit(BAR(P_EMPTY, b));
+      }
+      umma_commit(BAR(O_DONE, 0));
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax + epilogue ----
+    const uint32_t qd = warp - 4, row = qd * 32 + lane;
+    const uint32_t lane_addr = (qd * 32) << 16;
+    const uint32_t lim = p0 + row + 1;      // keys [0, lim) are visible to this row
+    float m_st = -INFINITY, l_sum = 0.f;
+    for (uint32_t j = 0; j < n_tiles; ++j) {
+      const uint32_t b = j & 1, u = j >> 1, kv0 = j * kBN;
+      mbar_wait(BAR(S_FULL, b), u & 1, s_err, WAIT_MMA);
+      tc_fence_after();
+      float s[kBN];
+      {
+        float t0[32], t1[32];
+        tmem_ld32(t_s0 + b * kBN + lane_addr, t0);
+        tmem_ld32(t_s0 + b * kBN + 32 + lane_addr, t1);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
+      }
+      tc_fence_before();
+      mbar_arrive(BAR(S_EMPTY, b));
+      float mt = -INFINITY;
+      const bool diag = kv0 + kBN > lim;
+#pragma unroll
+      for (int i = 0; i < kBN; ++i) {
+        float x = s[i] * p.scale_log2;
+        if (diag && kv0 + i >= lim) x = -INFINITY;
+        s[i] = x;
+        mt = fmaxf(mt, x);
+      }
+      float alpha = 1.f;
+      bool grow = false;
+      if (j == 0) m_st = mt;                        // key 0 is visible to every row, so mt is finite
+      else if (mt > m_st + 8.f) { alpha = exp2f(m_st - mt); m_st = mt; l_sum *= alpha; grow = true; }
+      if (__any_sync(0xffffffffu, grow)) {
+        // O must not change under the previous P V: wait for it, then rescale this warp's 32 rows in TMEM
+        const uint32_t jb = (j - 1) & 1, ju = (j - 1) >> 1;
+        mbar_wait(BAR(P_EMPTY, jb), ju & 1, s_err, WAIT_MMA);
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          float o[32];
+          tmem_ld32(t_o + c * 32 + lane_addr, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(t_o + c * 32 + lane_addr, o);
+        }
+        tc_fence_before();
+      }
+      // P = 2^(s - m) as f16 into the swizzled K-major tile of buffer b (free once P V (j-2) has retired)
+      mbar_wait(BAR(P_EMPTY, b), (u & 1) ^ 1, s_err, WAIT_MMA);
+      uint8_t* prow = p_s + b * L::P_BYTES + row * 128;
+      float ls = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { e[i] = exp2f(s[c * 8 + i] - m_st); ls += e[i]; }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+            make_uint4(pack_h2(e[0], e[1]), pack_h2(e[2], e[3]), pack_h2(e[4], e[5]), pack_h2(e[6], e[7]));
+      }
+      l_sum += ls;
+      fence_proxy_async();
+      mbar_arrive(BAR(P_FULL, b));
+    }
+    // ---- epilogue: O / l, gate, store ----
+    mbar_wait(BAR(O_DONE, 0), 0, s_err, WAIT_MMA);
+    tc_fence_after();
+    const float inv_l = 1.f / l_sum;
+    const uint32_t col = c0 + row;
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; ++c) {
+      float o[32];
+      tmem_ld32(t_o + c * 32 + lane_addr, o);
+      if (row < rows_valid) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= inv_l;
+        if (p.gate) {
+          const uint64_t go = (uint64_t)col * p.gate_col_stride + (uint64_t)h * p.gate_head_stride + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float gv = p.act_f16 ? __half2float(reinterpret_cast<const __half*>(p.gate)[go + i]) : reinterpret_cast<const float*>(p.gate)[go + i];
+            o[i] *= 1.0f / (1.0f + __expf(-gv));
+          }
+        }
+        const uint64_t oo = (uint64_t)col * p.out_col_stride + (uint64_t)h * HD + c * 32;
+        if (p.act_f16) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + oo);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(pack_h2(o[8 * i], o[8 * i + 1]), pack_h2(o[8 * i + 2], o[8 * i + 3]), pack_h2(o[8 * i + 4], o[8 * i + 5]), pack_h2(o[8 * i + 6], o[8 * i + 7]));
+        } else {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + oo);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem, L::TMEM_COLS);
+  }
+  if (tid == 0 && *s_err) atomicMax(p.err, *s_err);
+}
+
+int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ctx->cfg.head_dim == 128; }
+
+cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
+  const dim3 grid((p.n_cols + kBM - 1) / kBM, p.n_heads);
+  static bool attr_set[64][2] = {};
+  const int dev = L->ctx->device & 63;
+  if (L->ctx->cfg.head_dim == 256) {
+    if (!attr_set[dev][0]) {
+      cudaError_t e = cudaFuncSetAttribute(pa_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<256>::TOTAL);
+      if (e != cudaSuccess) return e;
+      attr_set[dev][0] = true;
+    }
+    pa_prefill_kernel<256><<<grid, kPfThreads, PfSmem<256>::TOTAL, st>>>(tm_k, tm_v, p);
+  } else {
+    if (!attr_set[dev][1]) {
+      cudaError_t e = cudaFuncSetAttribute(pa_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<128>::TOTAL);
+      if (e != cudaSuccess) return e;
+      attr_set[dev][1] = true;
+    }
+    pa_prefill_kernel<128><<<grid, kPfThreads, PfSmem<128>::TOTAL, st>>>(tm_k, tm_v, p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace pa

@@ -1,7 +1,6 @@
 // RoPE (full or partial, NeoX pairing), the f16 KV-cache append and the standalone sigmoid gate.
 //
-// One CTA per column (token).  The cos / sin of the column's n_rot/2 angles are evaluated once per CTA
-// and shared by every head:
+// One small CTA per (column, head).  The cos / sin of an angle is evaluated by the thread that rotates the pair:
 //   PA_ROPE_F64    angle = pos * inv_freq[i] in float64 (inv_freq = theta^(-2i/n_rot) comes from the host's
 //                  libm), cos / sin in float64, the two products and their difference / sum rounded one by
 //                  one in float64, the result rounded to f32 — the arithmetic of pooled's CPU reference
@@ -26,69 +25,58 @@ __device__ __forceinline__ __half f16_rne(float x) {
   return __float2half_rn(x);
 }
 
-__global__ void __launch_bounds__(256) pa_rope_append_kernel(const RopeParams p) {
-  __shared__ double s_c[128], s_s[128];
-  __shared__ float s_cf[128], s_sf[128];
-  const uint32_t col = blockIdx.x, half = p.n_rot / 2;
+// grid (n_cols, q heads + k heads + v heads); one thread per pair of elements of the head.  Thread t < n_rot/2
+// evaluates its own cos / sin and rotates dims (t, t + n_rot/2); the other threads pass dims n_rot + 2(t - n_rot/2),
+// +1 through.  No shared memory and no barrier: every global load of the call is in flight at once, which is what
+// the latency of a one-token call consists of.
+__global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p) {
+  const uint32_t col = blockIdx.x, half = p.n_rot / 2, hd = p.hd, pr = threadIdx.x;
   // The kernel after this one may start fetching old cache rows while this one runs (it never touches the rows or
   // the rotated q written here before its own wait); this kernel itself writes nothing before its predecessor ends.
   pdl_trigger();
   pdl_wait();
-  if (p.mode == PA_ROPE_F64) {
-    for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
-      const double ang = __dmul_rn((double)(p.pos + col), p.inv_freq[i]);
-      double sv, cv;
-      sincos(ang, &sv, &cv);
-      s_c[i] = cv; s_s[i] = sv;
-    }
-  } else if (p.mode == PA_ROPE_TABLE) {
-    for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
-      s_cf[i] = p.cs_table[(uint64_t)col * p.n_rot + 2 * i];
-      s_sf[i] = p.cs_table[(uint64_t)col * p.n_rot + 2 * i + 1];
-    }
+  if (pr >= hd / 2) return;
+  const uint32_t nq = p.q ? p.q_heads : 0, nk = p.k ? p.kv_heads : 0;
+  uint32_t slot = blockIdx.y;
+  if (slot >= nq + nk) {
+    // V head: conversion only
+    const uint32_t head = slot - nq - nk, kvd = p.kv_heads * hd;
+    const uint64_t so = (uint64_t)col * p.kv_col_stride + (uint64_t)head * hd + 2 * pr;
+    __half* dst = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd + (uint64_t)head * hd + 2 * pr;
+    dst[0] = f16_rne(ld_act(p.v, so, p.in_f16));
+    dst[1] = f16_rne(ld_act(p.v, so + 1, p.in_f16));
+    return;
   }
-  __syncthreads();
-
-  const uint32_t hd = p.hd, pairs = hd / 2;
-  // work items: (head, pair) over q heads then k heads; pair < half rotates dims (pair, pair + half), the rest
-  // pass dims n_rot + 2*(pair-half), +1 through
-  const uint32_t nq = p.q ? p.q_heads * pairs : 0, nk = p.k ? p.kv_heads * pairs : 0;
-  for (uint32_t w = threadIdx.x; w < nq + nk; w += blockDim.x) {
-    const bool is_q = w < nq;
-    const uint32_t ww = is_q ? w : w - nq;
-    const uint32_t head = ww / pairs, pr = ww % pairs;
-    uint32_t d0, d1;
-    const bool rot = p.mode != PA_ROPE_NONE && pr < half;
-    if (pr < half) { d0 = pr; d1 = pr + half; } else { d0 = p.n_rot + 2 * (pr - half); d1 = d0 + 1; }
-    const void* src = is_q ? p.q : p.k;
-    const uint64_t sb = is_q ? (uint64_t)col * p.q_col_stride + (uint64_t)head * p.q_head_stride
-                             : (uint64_t)col * p.kv_col_stride + (uint64_t)head * hd;
-    float a = ld_act(src, sb + d0, p.in_f16), b = ld_act(src, sb + d1, p.in_f16);
-    float ra = a, rb = b;
-    if (rot) {
-      if (p.mode == PA_ROPE_F64) {
-        const double c = s_c[pr], s = s_s[pr], ad = (double)a, bd = (double)b;
-        ra = (float)__dsub_rn(__dmul_rn(ad, c), __dmul_rn(bd, s));
-        rb = (float)__dadd_rn(__dmul_rn(bd, c), __dmul_rn(ad, s));
-      } else {
-        const float c = s_cf[pr], s = s_sf[pr];
-        ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-        rb = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
-      }
-    }
-    if (is_q) {
-      float* dst = p.q_out + (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
-      dst[d0] = ra; dst[d1] = rb;
+  const bool is_q = slot < nq;
+  const uint32_t head = is_q ? slot : slot - nq;
+  uint32_t d0, d1;
+  const bool rot = p.mode != PA_ROPE_NONE && pr < half;
+  if (pr < half) { d0 = pr; d1 = pr + half; } else { d0 = p.n_rot + 2 * (pr - half); d1 = d0 + 1; }
+  const void* src = is_q ? p.q : p.k;
+  const uint64_t sb = is_q ? (uint64_t)col * p.q_col_stride + (uint64_t)head * p.q_head_stride
+                           : (uint64_t)col * p.kv_col_stride + (uint64_t)head * hd;
+  const float a = ld_act(src, sb + d0, p.in_f16), b = ld_act(src, sb + d1, p.in_f16);
+  float ra = a, rb = b;
+  if (rot) {
+    if (p.mode == PA_ROPE_F64) {
+      const double ang = __dmul_rn((double)(p.pos + col), p.inv_freq[pr]);
+      double s, c;
+      sincos(ang, &s, &c);
+      const double ad = (double)a, bd = (double)b;
+      ra = (float)__dsub_rn(__dmul_rn(ad, c), __dmul_rn(bd, s));
+      rb = (float)__dadd_rn(__dmul_rn(bd, c), __dmul_rn(ad, s));
     } else {
-      __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
-      dst[d0] = f16_rne(ra); dst[d1] = f16_rne(rb);
+      const float c = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr], s = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr + 1];
+      ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+      rb = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
     }
   }
-  if (p.v) {
-    const uint32_t kvd = p.kv_heads * hd;
-    __half* dst = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd;
-    for (uint32_t i = threadIdx.x; i < kvd; i += blockDim.x)
-      dst[i] = f16_rne(ld_act(p.v, (uint64_t)col * p.kv_col_stride + i, p.in_f16));
+  if (is_q) {
+    float* dst = p.q_out + (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
+    dst[d0] = ra; dst[d1] = rb;
+  } else {
+    __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
+    dst[d0] = f16_rne(ra); dst[d1] = f16_rne(rb);
   }
 }
 
@@ -105,7 +93,8 @@ __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams
 }
 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
-  return launch_pdl(pa_rope_append_kernel, dim3(n_cols), dim3(256), 0, st, p);
+  const uint32_t slots = (p.q ? p.q_heads : 0) + (p.k ? p.kv_heads : 0) + (p.v ? p.kv_heads : 0);
+  return launch_pdl(pa_rope_append_kernel, dim3(n_cols, slots), dim3(128), 0, st, p);
 }
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st) {
   pa_sigmoid_mul_kernel<<<n_cols, 256, 0, st>>>(p);
