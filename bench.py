@@ -40,18 +40,20 @@ WORKLOADS = {
                desc="config 2: Qwen3.6-35B-MoE-shaped decode attention, 16q/2kv hd256 partial RoPE 64, gate, ctx 32768, 10 attention layers"),
     "c4": dict(nH=24, nKV=4, hd=256, n_rot=64, theta=1e7, ctx=16384, n_cols=5, n_seqs=1, layers=16, gate=True, outliers=False,
                desc="config 4: 27B-hybrid-shaped 5-token verify block, 24q/4kv hd256, ctx 16384, 16 attention layers"),
+    "c3": dict(nH=24, nKV=4, hd=256, n_rot=64, theta=1e7, ctx=0, n_cols=8192, n_seqs=1, layers=4, gate=False, outliers=False,
+               desc="config 3: 27B-hybrid-shaped causal prefill, 8192-token prompt into an empty cache, 24q/4kv hd256 partial RoPE 64, 4 layers per step"),
     "c5": dict(nH=16, nKV=2, hd=256, n_rot=64, theta=1e7, ctx=131072, n_cols=1, n_seqs=8, layers=2, gate=True, outliers=False,
                desc="config 5: 8 sequences x 131072-token context, 16q/2kv hd256, gate, KV sequence sharded across the GPUs (strong scaling), 2 layers"),
 }
 
 
-def peaks():
+def peaks(key="hbm_gbs", fallback=6650.0):
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             p = json.load(f)
-        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        return float(p[key]), "measured (MEASURED_PEAKS.json)"
     except Exception:
-        return 6650.0, "fallback (6.65 TB/s)"
+        return fallback, "fallback"
 
 
 class ClockSampler:
@@ -294,6 +296,93 @@ def run_ours(args, w):
         dist.barrier(); dist.destroy_process_group()
 
 
+def run_prefill(args, w):
+    """Config 3: tiled causal prefill.  With N > 1 the kv-head groups are dealt to the ranks (no collective: heads
+    never interact inside attention); value is the whole job's causal FLOP/s (strong scaling)."""
+    import torch
+    import torch.distributed as dist
+    from pooled_b200 import AttnConfig, AttnEngine
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    nH, nKV, hd, T, layers = w["nH"], w["nKV"], w["hd"], w["n_cols"], w["layers"]
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if nKV % world:
+        if rank == 0:
+            print(json.dumps({"metric": "prefill attn TFLOP/s", "n_gpus": world, "unavailable": f"{nKV} kv-head groups do not divide over {world} GPUs"}))
+        return
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    nH_r, nKV_r = nH // world, nKV // world          # this rank's heads
+    qd, kvd = nH_r * hd, nKV_r * hd
+    eng = AttnEngine(AttnConfig(n_heads=nH_r, n_kv_heads=nKV_r, head_dim=hd, n_rot=w["n_rot"], rope_theta=w["theta"], max_seq=T, n_layers=layers,
+                                act_dtype=torch.float16, max_cols=T), device=local)
+    gh = torch.Generator(); gh.manual_seed(7 + rank)
+    mk = lambda n: torch.randn((T, n), generator=gh).to(torch.float16).pin_memory()
+    hq, hk, hv = mk(qd), mk(kvd), mk(kvd)
+    hout = torch.empty((T, qd), dtype=torch.float16).pin_memory()
+    dq, dk, dv = hq.to(dev), hk.to(dev), hv.to(dev)
+    dout = torch.empty((layers, T, qd), dtype=torch.float16, device=dev)
+
+    def step():
+        for li in range(layers):
+            eng.encode_layer(li, 0, dq, dk, dv, None, dout[li], mode="prefill")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    flops_layer = 4.0 * nH * hd * T * (T + 1) / 2          # whole job, causal half only
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    clocks = ClockSampler(local); clocks.start()
+    st0 = eng.stats()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(); e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record(); barrier()
+    ms = e0.elapsed_time(e1)
+    st1 = eng.stats()
+    eng.timing_begin(layers * args.steps + 8)
+    for _ in range(args.steps):
+        step()
+    core_ms, core_n = eng.timing_end()
+
+    def step_host():
+        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
+        step()
+        hout.copy_(dout[layers - 1], non_blocking=True)
+    step_host(); barrier(); e0.record()
+    for _ in range(args.steps):
+        step_host()
+    e1.record(); barrier()
+    ems = e0.elapsed_time(e1)
+    ck = clocks.stop()
+    if world > 1:
+        t = torch.tensor([ms, ems], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, ems = float(t[0]), float(t[1])
+    value = flops_layer * layers * args.steps / (ms * 1e-3) / 1e12
+    peak, src = peaks("bf16_tflops", 1590.0)
+    ach = flops_layer / world / (core_ms / max(core_n, 1) * 1e-3) / 1e12
+    line = {"metric": "prefill attn TFLOP/s", "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 operands, f32 accumulate", "data": "synthetic (seeded N(0,1) -> f16)",
+            "config": {"workload": w["desc"], "heads_per_gpu": f"{nH_r}q/{nKV_r}kv", "flops": "4*nH*hd*T(T+1)/2 per layer (masked half not credited)",
+                       "l2": "q, k, v and out of a layer are 235 MB, more than the 126 MB L2; each layer has its own caches"},
+            "roofline": {"bound": "tensor", "kernel": "pa_prefill_kernel", "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
+                         "peak_source": src + ", cuBLAS bf16 burst", "launches_timed": int(core_n), "us_per_launch": round(core_ms / max(core_n, 1) * 1e3, 1), "traffic": args.traffic},
+            "e2e": {"value": round(flops_layer * layers * args.steps / (ems * 1e-3) / 1e12, 1), "unit": "TFLOP/s", "h2d_bytes_per_step": int(hq.numel() + hk.numel() + hv.numel()) * 2 * world,
+                    "d2h_bytes_per_step": int(hout.numel()) * 2 * world},
+            "gpu_launches": int(st1["kernel_launches"] - st0["kernel_launches"]), "clocks": ck}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+
+
 def cpu_baseline(w, budget_s: float = 12.0, threads: int | None = None):
     """The reference's CPU attention (the oracle's threaded f32 restatement) on one layer call of the workload."""
     import numpy as np
@@ -348,6 +437,8 @@ def main():
         w["layers"] = args.layers
     if args.impl == "reference":
         run_reference(args, w)
+    elif args.workload == "c3":
+        run_prefill(args, w)
     else:
         run_ours(args, w)
 
