@@ -211,6 +211,24 @@ PA_API int pa_attn_layer_host(pa_layer* layer, uint32_t seq, uint32_t pos, uint3
                               uint64_t gate_head_stride, const float* cs_table, void* out,
                               uint64_t out_col_stride, void* stream);
 
+/* Decode / verify + combine + gate for callers that cannot allocate device memory (code running inside a stream
+ * capture, on a thread that must not block on the allocator, or handed raw device pointers by a host that owns the
+ * memory pool): such a caller cannot create a pa_ctx / pa_layer, so everything arrives as plain pointers and the
+ * per-split partial records live in a fixed array inside the library image (2048 records, about 2.1 MB held by every
+ * GPU that loads the library until the process exits).  It has no counterpart in the reference.
+ *   k_cache, v_cache: f16 [cache_rows][n_kv_heads*head_dim]; q (already rotated), gate (may be NULL), out: f32
+ *   [n_cols][n_heads*head_dim]; columns at positions pos .. pos+n_cols-1, their K/V rows already in the caches.
+ *   Limits: head_dim 128 or 256; n_cols * (n_heads / n_kv_heads) <= 64; n_cols * n_heads <= 2048 (the split count is
+ *   lowered so that rows * splits fits the array).  Anything beyond is refused with PA_EUNSUPPORTED and a message.
+ *   The first call on a device looks up the array's address and sets kernel attributes: make it outside any stream
+ *   capture.  All calls on a device share the array (it keeps the last call's records, which are rewritten before they
+ *   are read; the status word is cleared on the stream by each call), so calls that overlap on the GPU race: keep
+ *   them on one stream or order them with events.  Calls no cudaMalloc / cudaFree / allocating routine.
+ *   msg (may be NULL): receives the error text. */
+PA_API int pa_decode_static(int device, const void* k_cache, const void* v_cache, uint32_t cache_rows, uint32_t n_heads,
+                            uint32_t n_kv_heads, uint32_t head_dim, uint32_t pos, uint32_t n_cols, const float* q,
+                            const float* gate, float* out, void* stream, char* msg, size_t msg_len);
+
 /* Counters since creation: what tests/bench_attn_ctx.js collects with timestamp queries. */
 typedef struct pa_stats {
   uint64_t kernel_launches; /* this library's kernels launched */
