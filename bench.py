@@ -238,20 +238,20 @@ def run_ours(args, w):
     # end to end: host buffers in, host result out, every layer, through the C ABI's host entry point
     e2e = None
     if not sharded and n_seqs == 1:
+        # one C-ABI call per token step: pinned host q/k/v/gate of all layers up, the layers back to back, out down
         for _ in range(3):
-            for li in range(layers):
-                eng.encode_layer_host(li, ctx, hq[li], hk[li], hv[li], gate(hg, li), hout[li], mode="decode")
+            eng.encode_step_host(ctx, hq, hk, hv, hg if w["gate"] else None, hout, mode="decode")
         barrier()
         e0.record()
         for _ in range(args.steps):
-            for li in range(layers):
-                eng.encode_layer_host(li, ctx, hq[li], hk[li], hv[li], gate(hg, li), hout[li], mode="decode")
+            eng.encode_step_host(ctx, hq, hk, hv, hg if w["gate"] else None, hout, mode="decode")
         e1.record()
         barrier()
         ems = e0.elapsed_time(e1)
         es = 2
         e2e = {"value": round(bytes_per_step * args.steps / (ems * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ems / args.steps, 4),
-               "h2d_bytes_per_step": layers * T * (qd + 2 * kvd + (qd if w["gate"] else 0)) * es, "d2h_bytes_per_step": layers * T * qd * es}
+               "h2d_bytes_per_step": layers * T * (qd + 2 * kvd + (qd if w["gate"] else 0)) * es, "d2h_bytes_per_step": layers * T * qd * es,
+               "call": "pa_attn_step_host (one upload per array, all layers, one download, stream drained) per step"}
     else:
         # sharded / batched steps: the same step with a pinned-host upload of its inputs and a download of its result
         def step_host():

@@ -211,6 +211,17 @@ PA_API int pa_attn_layer_host(pa_layer* layer, uint32_t seq, uint32_t pos, uint3
                               uint64_t gate_head_stride, const float* cs_table, void* out,
                               uint64_t out_col_stride, void* stream);
 
+/* One token step through several attention layers with HOST buffers: q, k, v, gate and out are [n_layers][n_cols][...]
+ * arrays (layer strides in elements); each array is uploaded once, the layers run back to back, out comes back in
+ * one copy and the call returns when the stream has drained.  This is the granularity at which pooled's engine
+ * touches the host: forwardToken encodes every layer, submits once and maps the result once
+ * (engine/qwen35.js:4214-4228).  PA_ROPE_TABLE contexts are not supported here (use pa_attn_layer_host). */
+PA_API int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode,
+                             const void* q, uint64_t q_layer_stride, uint64_t q_col_stride, uint64_t q_head_stride, const void* k,
+                             const void* v, uint64_t kv_layer_stride, uint64_t kv_col_stride, const void* gate,
+                             uint64_t gate_layer_stride, uint64_t gate_col_stride, uint64_t gate_head_stride, void* out,
+                             uint64_t out_layer_stride, uint64_t out_col_stride, void* stream);
+
 /* Decode / verify + combine + gate for callers that cannot allocate device memory (code running inside a stream
  * capture, on a thread that must not block on the allocator, or handed raw device pointers by a host that owns the
  * memory pool): such a caller cannot create a pa_ctx / pa_layer, so everything arrives as plain pointers and the

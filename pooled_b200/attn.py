@@ -295,3 +295,15 @@ class AttnEngine:
         self._ck(self.L.pa_attn_layer_host(self.layers[li], seq, pos, n_cols, _MODE[mode], self._p(q), q.stride(0), q_head_stride or self.cfg.head_dim,
                                            self._p(k), self._p(v), k.stride(0), gp, gcs, ghs, self._p(cs_table), self._p(out), out.stride(0), self._st()))
         return out
+
+    def encode_step_host(self, pos: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor,
+                         seq: int = 0, mode: str = "auto", q_head_stride: int | None = None, gate_head_stride: int | None = None) -> torch.Tensor:
+        """One token step through every layer with HOST tensors [n_layers, n_cols, ...]: one upload per tensor, the layers
+        back to back, one download (forwardToken's submit-once / map-once, engine/qwen35.js:4214-4228)."""
+        assert not q.is_cuda and not out.is_cuda and q.shape[0] == len(self.layers)
+        arr = (C.c_void_p * len(self.layers))(*[lh.value for lh in self.layers])
+        self._ck(self.L.pa_attn_step_host(arr, len(self.layers), seq, pos, q.shape[1], _MODE[mode], self._p(q), q.stride(0), q.stride(1),
+                                          q_head_stride or self.cfg.head_dim, self._p(k), self._p(v), k.stride(0), k.stride(1), self._p(gate),
+                                          gate.stride(0) if gate is not None else 0, gate.stride(1) if gate is not None else 0,
+                                          gate_head_stride or self.cfg.head_dim, self._p(out), out.stride(0), out.stride(1), self._st()))
+        return out

@@ -630,3 +630,49 @@ extern "C" int pa_attn_layer_host(pa_layer* L, uint32_t seq, uint32_t pos, uint3
   }
   return pa_sync(ctx, stream);
 }
+
+// One token step over several layers with HOST buffers: one upload per array, the layers back to back, one download.
+extern "C" int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q,
+                                 uint64_t q_layer_stride, uint64_t qcs, uint64_t qhs, const void* k, const void* v, uint64_t kv_layer_stride, uint64_t kvcs,
+                                 const void* gate, uint64_t gate_layer_stride, uint64_t gcs, uint64_t ghs, void* out, uint64_t out_layer_stride, uint64_t ocs,
+                                 void* stream) {
+  if (!layers || n_layers < 1 || !layers[0]) return PA_EINVAL;
+  pa_ctx* ctx = layers[0]->ctx;
+  GUARD(ctx);
+  if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_step_host: null q, k, v or out");
+  for (uint32_t l = 0; l < n_layers; ++l) {
+    if (!layers[l] || layers[l]->ctx != ctx) return fail(ctx, PA_EINVAL, "pa_attn_step_host: layer %u belongs to another context", l);
+    if (int rc = check_cols(layers[l], seq, pos, n_cols, "pa_attn_step_host")) return rc;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaSetDevice(ctx->device);
+  const size_t es = ctx->cfg.act_dtype == PA_F16 ? 2 : 4;
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  const size_t qb = up((size_t)n_layers * q_layer_stride * es), kb = up((size_t)n_layers * kv_layer_stride * es);
+  const size_t gb = gate ? up((size_t)n_layers * gate_layer_stride * es) : 0, ob = up((size_t)n_layers * out_layer_stride * es);
+  const uint8_t* qh = (const uint8_t*)q; const uint8_t* gh = (const uint8_t*)gate;
+  const bool gate_in_q = gate && gh >= qh && gh < qh + qb;     // interleaved q_full: the gate rides in the q upload
+  const size_t need = qb + 2 * kb + (gate_in_q ? 0 : gb) + ob;
+  if (need > ctx->stage_bytes) {
+    CU_TRY(ctx, cudaStreamSynchronize(st));
+    cudaFree(ctx->stage_dev); ctx->stage_dev = nullptr; ctx->stage_bytes = 0;
+    if (cudaMalloc(&ctx->stage_dev, need) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_attn_step_host: %zu staging bytes do not fit on the device", need); }
+    ctx->stage_bytes = need;
+  }
+  uint8_t* d = (uint8_t*)ctx->stage_dev;
+  uint8_t *dq = d, *dk = dq + qb, *dv = dk + kb, *dg = dv + kb, *dout = dg + (gate_in_q ? 0 : gb);
+  CU_TRY(ctx, cudaMemcpyAsync(dq, q, (size_t)n_layers * q_layer_stride * es, cudaMemcpyHostToDevice, st));
+  CU_TRY(ctx, cudaMemcpyAsync(dk, k, (size_t)n_layers * kv_layer_stride * es, cudaMemcpyHostToDevice, st));
+  CU_TRY(ctx, cudaMemcpyAsync(dv, v, (size_t)n_layers * kv_layer_stride * es, cudaMemcpyHostToDevice, st));
+  const uint8_t* dgate = nullptr;
+  if (gate_in_q) dgate = dq + (gh - qh);
+  else if (gate) { CU_TRY(ctx, cudaMemcpyAsync(dg, gate, (size_t)n_layers * gate_layer_stride * es, cudaMemcpyHostToDevice, st)); dgate = dg; }
+  for (uint32_t l = 0; l < n_layers; ++l) {
+    if (int rc = layer_impl(layers[l], seq, pos, n_cols, mode, dq + l * q_layer_stride * es, qcs, qhs, dk + l * kv_layer_stride * es,
+                            dv + l * kv_layer_stride * es, kvcs, dgate ? dgate + l * gate_layer_stride * es : nullptr, gcs, ghs, nullptr,
+                            dout + l * out_layer_stride * es, ocs, st))
+      return rc;
+  }
+  CU_TRY(ctx, cudaMemcpyAsync(out, dout, (size_t)n_layers * out_layer_stride * es, cudaMemcpyDeviceToHost, st));
+  return pa_sync(ctx, stream);
+}

@@ -68,6 +68,7 @@ SYMBOLS = {
     "pa_sigmoid_mul": (_i, [_vp, _vp, _u64, _vp, _u64, _u64, _u32, _vp]),
     "pa_attn_layer": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
     "pa_attn_layer_host": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
+    "pa_attn_step_host": (_i, [C.POINTER(_vp), _u32, _u32, _u32, _u32, _i, _vp, _u64, _u64, _u64, _vp, _vp, _u64, _u64, _vp, _u64, _u64, _u64, _vp, _u64, _u64, _vp]),
     "pa_decode_static": (_i, [_i, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, C.c_char_p, _sz]),
     "pa_get_stats": (_i, [_vp, C.POINTER(PaStats)]),
     "pa_timing_begin": (_i, [_vp, _u32]),

@@ -253,3 +253,25 @@ def test_unsupported_shapes_are_refused_with_a_message():
         eng.decode(0, [(0, 100, 9)], q)     # 9 columns x 8 heads = 72 query rows per kv head
     assert e.value.code == -2 and "pa_prefill" in str(e.value)
     assert eng.stats()["calls"] == 0
+
+
+def test_host_buffer_entry_points_match_the_device_path():
+    # pa_attn_layer_host (one layer) and pa_attn_step_host (all layers of a token step) against pa_attn_layer
+    import torch
+    nH, nKV, hd, ctx, layers = 16, 2, 256, 3000, 3
+    from pooled_b200 import AttnConfig, AttnEngine
+    eng = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=64, rope_theta=1e7, max_seq=ctx + 8, n_layers=layers,
+                                act_dtype=torch.float16, max_cols=8))
+    for li in range(layers):
+        _, K, V, _ = _config_inputs(20 + li, nH, nKV, hd, ctx, 1)
+        util.load_cache(eng, li, 0, po.np_f16_rne(K), po.np_f16_rne(V))
+    mk = lambda seed, n: torch.from_numpy(util.normal_f16(seed, (layers, 2, n))).to(torch.float16).pin_memory()
+    hq, hk, hv, hg = mk(1, nH * hd), mk(2, nKV * hd), mk(3, nKV * hd), mk(4, nH * hd)
+    want = torch.stack([eng.encode_layer(li, ctx, hq[li].cuda(), hk[li].cuda(), hv[li].cuda(), hg[li].cuda(), mode="decode") for li in range(layers)]).cpu()
+    eng.sync()
+    hout = torch.empty((layers, 2, nH * hd), dtype=torch.float16).pin_memory()
+    eng.encode_step_host(ctx, hq, hk, hv, hg, hout, mode="decode")
+    assert torch.equal(hout, want)
+    one = torch.empty((2, nH * hd), dtype=torch.float16).pin_memory()
+    eng.encode_layer_host(1, ctx, hq[1], hk[1], hv[1], hg[1], one, mode="decode")
+    assert torch.equal(one, want[1])
