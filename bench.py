@@ -430,11 +430,14 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager C-ABI calls instead of a CUDA-graph replay of the step")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling captures)")
+    ap.add_argument("--cols", type=int, default=0, help="override the prompt length of the prefill workload (small profiling captures)")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the decode kernel, if known")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.layers > 0:
         w["layers"] = args.layers
+    if args.cols > 0 and args.workload == "c3":
+        w["n_cols"] = args.cols
     if args.impl == "reference":
         run_reference(args, w)
     elif args.workload == "c3":
