@@ -345,9 +345,10 @@ static int check_cols(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
 }
 
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
-                            uint32_t q_heads, float* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
-                            uint32_t mode, int in_f16, cudaStream_t st) {
+                            uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
+                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0) {
   RopeParams p{};
+  p.q_out_f16 = q_out_f16;
   p.q = q; p.q_col_stride = qcs; p.q_head_stride = qhs; p.q_heads = q_heads; p.q_out = q_out; p.q_out_col_stride = q_out_cs;
   p.k = k; p.v = v; p.kv_col_stride = kvcs; p.kv_heads = ctx->cfg.n_kv_heads;
   if (L) { p.k_cache = L->k; p.v_cache = L->v; p.cache_row0 = (uint64_t)seq * L->max_seq + (pos - L->origin); }
@@ -562,15 +563,16 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer: null q, k, v or out");
   if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer")) return rc;
   cudaSetDevice(ctx->device);
-  if (!ctx->core_only)
-    if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
-                                  ctx->cfg.act_dtype == PA_F16, st))
-      return rc;
   // the decode / verify kernel carries at most 64 query rows per kv head; wider passes are prefill chunks
   // (the reference takes the tiled kernel on full-width non-verify passes, engine/qwen35.js:2489)
-  bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
+  const bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
+  // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic)
+  if (!ctx->core_only)
+    if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
+                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : 0))
+      return rc;
   if (prefill)
-    return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
+    return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
   pa_item it{seq, pos, n_cols, 0};
   return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", !ctx->core_only);
 }

@@ -35,7 +35,7 @@ struct CombineParams {
 
 struct RopeParams {
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
-  float* q_out; uint64_t q_out_col_stride;                                  // f32, heads packed [q_heads][hd]
+  void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
   const void* k; const void* v; uint64_t kv_col_stride; uint32_t kv_heads;  // k == nullptr: skip
   __half* k_cache; __half* v_cache; uint64_t cache_row0;                    // row of column 0
   uint32_t hd, n_rot, pos, mode;

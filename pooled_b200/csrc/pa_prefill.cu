@@ -5,11 +5,11 @@
 // the causal diagonal.  K/V tiles of the G heads of a GQA group are the same bytes, read by G CTAs that run at about
 // the same time; the caches of a prefill fit the 126 MB L2, so HBM sees them once.
 //
-//   warp 0      TMA producer: K and V tiles (64 x head_dim f16, 128-byte swizzle) into two-slot rings
+//   warps 0, 3  TMA producers: K tiles and V tiles (64 x head_dim f16, 128-byte swizzle), a two-slot ring each
 //   warp 1      MMA issuer (one thread): S = Q K^T into a double-buffered TMEM tile (128 x 64 f32), then
 //               O += P V into the TMEM accumulator (128 x head_dim f32); completion is signalled to mbarriers
 //               with tcgen05.commit
-//   warp 2      allocates / frees tensor memory
+//   warp 2      allocates / frees tensor memory; with warps 4-7 stages the Q tile (f16, swizzled) while K/V stream in
 //   warps 4-7   softmax: thread r owns query row r (TMEM lane r): tcgen05.ld of its S row, scale + causal mask,
 //               running max / sum, P = 2^(s - m) as f16 into shared memory in the K-major swizzled layout the
 //               second MMA reads, and the epilogue (O / l, sigmoid gate, store)
@@ -87,6 +87,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle.  K-major operand (rows of 64 f16 = 128 bytes, 8-row groups of
 // 1024 bytes): sbo = 1024, lbo unused.  MN-major operand (64 contiguous MN elements per row of 128 bytes, 8 rows
 // along K per 1024-byte group): lbo = distance between 64-element chunks along MN, sbo = 1024.
@@ -138,6 +144,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const uint32_t p0 = p.pos + c0;                       // cache row of column c0's own token
   const uint32_t n_tiles = (p0 + rows_valid + kBN - 1) / kBN;
 
+  enum { Q_FULL_IDX = 17 };
+  constexpr int kQLoaders = 160;   // warps 2, 4, 5, 6, 7 stage Q; warps 0 / 3 feed K / V; warp 1 issues the MMAs
   if (warp == 1 && lane == 0) {
     *s_err = 0;
     for (int i = 0; i < 2; ++i) {
@@ -147,6 +155,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(P_EMPTY, i), 1);
     }
     mbar_init(BAR(O_DONE, 0), 1);
+    mbar_init(bar0 + 8u * Q_FULL_IDX, kQLoaders);
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -155,38 +164,66 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     tc_fence_before();
   }
   pdl_wait();   // q (and, for a chunked prefill, the appended rows) come from the kernel before this one
-
-  // ---- Q tile -> shared memory: f16, K-major, 128-byte swizzle ----
-  for (int idx = tid; idx < kBM * (HD / 8); idx += kPfThreads) {
-    const uint32_t row = idx / (HD / 8), c16 = idx % (HD / 8);
-    uint4 packed = make_uint4(0, 0, 0, 0);
-    if (row < rows_valid) {
-      const uint64_t off = (uint64_t)(c0 + row) * p.q_col_stride + (uint64_t)h * p.q_head_stride + c16 * 8;
-      if (p.q_f16) {
-        packed = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off);
-      } else {
-        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off);
-        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + 4);
-        packed = make_uint4(pack_h2(a.x, a.y), pack_h2(a.z, a.w), pack_h2(b.x, b.y), pack_h2(b.z, b.w));
-      }
-    }
-    *reinterpret_cast<uint4*>(q_s + (c16 >> 3) * (kBM * 128) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4)) = packed;
-  }
-  fence_proxy_async();   // the tensor cores read Q through the async proxy
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
   const uint32_t t_s0 = tmem, t_o = tmem + 2 * kBN;
 
+  if (warp != 0 && warp != 1 && warp != 3) {
+    // ---- Q tile -> shared memory: f16, K-major, 128-byte swizzle; eight 16-byte pieces per thread in flight ----
+    const int qt = warp == 2 ? lane : (warp - 3) * 32 + lane;   // 0 .. 159
+    constexpr int ITEMS = kBM * (HD / 8);
+    for (int i0 = qt; i0 < ITEMS; i0 += kQLoaders * 8) {
+      uint4 lo[8], hi[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = i0 + u * kQLoaders;
+        const uint32_t row = idx / (HD / 8), c16 = idx % (HD / 8);
+        lo[u] = hi[u] = make_uint4(0, 0, 0, 0);
+        if (idx < ITEMS && row < rows_valid) {
+          const uint64_t off = (uint64_t)(c0 + row) * p.q_col_stride + (uint64_t)h * p.q_head_stride + c16 * 8;
+          if (p.q_f16) {
+            lo[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off);
+          } else {
+            lo[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.q) + off);
+            hi[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.q) + off + 4);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = i0 + u * kQLoaders;
+        if (idx >= ITEMS) continue;
+        const uint32_t row = idx / (HD / 8), c16 = idx % (HD / 8);
+        uint4 packed = lo[u];
+        if (!p.q_f16)
+          packed = make_uint4(pack_h2(__uint_as_float(lo[u].x), __uint_as_float(lo[u].y)), pack_h2(__uint_as_float(lo[u].z), __uint_as_float(lo[u].w)),
+                              pack_h2(__uint_as_float(hi[u].x), __uint_as_float(hi[u].y)), pack_h2(__uint_as_float(hi[u].z), __uint_as_float(hi[u].w)));
+        *reinterpret_cast<uint4*>(q_s + (c16 >> 3) * (kBM * 128) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4)) = packed;
+      }
+    }
+    fence_proxy_async();   // the tensor cores read Q through the async proxy
+    mbar_arrive(bar0 + 8u * Q_FULL_IDX);
+  }
+
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer ----
+    // ------------------------------------------------------------------ TMA producer, K ----
     if (lane == 0) {
-      prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+      prefetch_tmap(&tm_k);
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j & 1, u = j >> 1;
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
         tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)(j * kBN), (int)(g * CH), BAR(K_FULL, st));
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ TMA producer, V ----
+    // (its own thread: behind the K loads in one loop, K(j+1) would wait for the V slot that P V (j-1) still reads)
+    if (lane == 0) {
+      prefetch_tmap(&tm_v);
+      for (uint32_t j = 0; j < n_tiles; ++j) {
+        const uint32_t st = j & 1, u = j >> 1;
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
         tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)(j * kBN), (int)(g * CH), BAR(V_FULL, st));
@@ -197,6 +234,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
       const uint32_t q_addr = smem_u32(q_s);
+      mbar_wait(bar0 + 8u * Q_FULL_IDX, 0, s_err, WAIT_QFULL);
+      tc_fence_after();
       auto issue_qk = [&](uint32_t j) {
         const uint32_t b = j & 1, u = j >> 1;
         mbar_wait(BAR(K_FULL, b), u & 1, s_err, WAIT_KFULL);
@@ -251,15 +290,15 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(BAR(S_EMPTY, b));
-      float mt = -INFINITY;
-      const bool diag = kv0 + kBN > lim;
+      // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
+      if (kv0 + kBN > lim) {
 #pragma unroll
-      for (int i = 0; i < kBN; ++i) {
-        float x = s[i] * p.scale_log2;
-        if (diag && kv0 + i >= lim) x = -INFINITY;
-        s[i] = x;
-        mt = fmaxf(mt, x);
+        for (int i = 0; i < kBN; ++i) if (kv0 + i >= lim) s[i] = -INFINITY;
       }
+      float mt = s[0];
+#pragma unroll
+      for (int i = 1; i < kBN; ++i) mt = fmaxf(mt, s[i]);
+      mt *= p.scale_log2;
       float alpha = 1.f;
       bool grow = false;
       if (j == 0) m_st = mt;                        // key 0 is visible to every row, so mt is finite
@@ -287,7 +326,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (int c = 0; c < 8; ++c) {
         float e[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { e[i] = exp2f(s[c * 8 + i] - m_st); ls += e[i]; }
+        for (int i = 0; i < 8; ++i) { e[i] = ex2_approx(fmaf(s[c * 8 + i], p.scale_log2, -m_st)); ls += e[i]; }
         *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
             make_uint4(pack_h2(e[0], e[1]), pack_h2(e[2], e[3]), pack_h2(e[4], e[5]), pack_h2(e[6], e[7]));
       }

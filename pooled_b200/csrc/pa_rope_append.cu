@@ -72,11 +72,84 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
     }
   }
   if (is_q) {
-    float* dst = p.q_out + (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
-    dst[d0] = ra; dst[d1] = rb;
+    const uint64_t o = (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
+    if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
+    else { float* dst = reinterpret_cast<float*>(p.q_out) + o; dst[d0] = ra; dst[d1] = rb; }
   } else {
     __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
     dst[d0] = f16_rne(ra); dst[d1] = f16_rne(rb);
+  }
+}
+
+// Many columns (prefill chunks): one 256-thread CTA per column.  The column's n_rot/2 angles are evaluated once and
+// shared by every head through shared memory; each thread then takes (head, pair) items four at a time so that its
+// loads overlap.  Same arithmetic, element for element, as the per-head kernel above.
+__global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopeParams p) {
+  __shared__ double s_c[128], s_s[128];
+  const uint32_t col = blockIdx.x, half = p.n_rot / 2, hd = p.hd, pairs = hd / 2;
+  pdl_trigger();
+  pdl_wait();
+  if (p.mode == PA_ROPE_F64) {
+    for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
+      double sv, cv;
+      sincos(__dmul_rn((double)(p.pos + col), p.inv_freq[i]), &sv, &cv);
+      s_c[i] = cv; s_s[i] = sv;
+    }
+  }
+  __syncthreads();
+  const uint32_t nq = p.q ? p.q_heads * pairs : 0, nk = p.k ? p.kv_heads * pairs : 0, nv = p.v ? p.kv_heads * pairs : 0;
+  const uint32_t total = nq + nk + nv, kvd = p.kv_heads * hd;
+  for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * blockDim.x) {
+    float a[4], b[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = w0 + u * blockDim.x;
+      a[u] = b[u] = 0.f;
+      if (w >= total) continue;
+      if (w >= nq + nk) {                      // V: elements 2i, 2i+1
+        const uint64_t so = (uint64_t)col * p.kv_col_stride + 2 * (w - nq - nk);
+        a[u] = ld_act(p.v, so, p.in_f16); b[u] = ld_act(p.v, so + 1, p.in_f16);
+      } else {
+        const bool is_q = w < nq;
+        const uint32_t ww = is_q ? w : w - nq, head = ww / pairs, pr = ww % pairs;
+        const uint32_t d0 = pr < half ? pr : p.n_rot + 2 * (pr - half), d1 = pr < half ? pr + half : d0 + 1;
+        const uint64_t sb = is_q ? (uint64_t)col * p.q_col_stride + (uint64_t)head * p.q_head_stride : (uint64_t)col * p.kv_col_stride + (uint64_t)head * hd;
+        a[u] = ld_act(is_q ? p.q : p.k, sb + d0, p.in_f16); b[u] = ld_act(is_q ? p.q : p.k, sb + d1, p.in_f16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = w0 + u * blockDim.x;
+      if (w >= total) continue;
+      if (w >= nq + nk) {
+        __half* dst = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd + 2 * (w - nq - nk);
+        dst[0] = f16_rne(a[u]); dst[1] = f16_rne(b[u]);
+        continue;
+      }
+      const bool is_q = w < nq;
+      const uint32_t ww = is_q ? w : w - nq, head = ww / pairs, pr = ww % pairs;
+      const uint32_t d0 = pr < half ? pr : p.n_rot + 2 * (pr - half), d1 = pr < half ? pr + half : d0 + 1;
+      float ra = a[u], rb = b[u];
+      if (p.mode != PA_ROPE_NONE && pr < half) {
+        if (p.mode == PA_ROPE_F64) {
+          const double c = s_c[pr], sn = s_s[pr], ad = (double)a[u], bd = (double)b[u];
+          ra = (float)__dsub_rn(__dmul_rn(ad, c), __dmul_rn(bd, sn));
+          rb = (float)__dadd_rn(__dmul_rn(bd, c), __dmul_rn(ad, sn));
+        } else {
+          const float c = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr], sn = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr + 1];
+          ra = __fsub_rn(__fmul_rn(a[u], c), __fmul_rn(b[u], sn));
+          rb = __fadd_rn(__fmul_rn(a[u], sn), __fmul_rn(b[u], c));
+        }
+      }
+      if (is_q) {
+        const uint64_t o = (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
+        if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
+        else { float* dst = reinterpret_cast<float*>(p.q_out) + o; dst[d0] = ra; dst[d1] = rb; }
+      } else {
+        __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)kvd + (uint64_t)head * hd;
+        dst[d0] = f16_rne(ra); dst[d1] = f16_rne(rb);
+      }
+    }
   }
 }
 
@@ -93,6 +166,7 @@ __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams
 }
 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
+  if (n_cols >= 16) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
   const uint32_t slots = (p.q ? p.q_heads : 0) + (p.k ? p.kv_heads : 0) + (p.v ? p.kv_heads : 0);
   return launch_pdl(pa_rope_append_kernel, dim3(n_cols, slots), dim3(128), 0, st, p);
 }
