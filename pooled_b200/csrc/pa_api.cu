@@ -524,6 +524,15 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   const uint64_t seq_off = (uint64_t)seq * L->max_seq * ctx->kv_dim;
   if (int rc = make_cache_map(ctx, &tm_k, L->k + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
   if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
+#ifdef PA_TRACE
+  {
+    static unsigned long long* tr = nullptr;
+    if (!tr) cudaMalloc(&tr, 4096 * 256 * 8);
+    cudaMemsetAsync(tr, 0, 4096 * 256 * 8, st);
+    p.trace = tr;
+    if (getenv("PA_TRACE_PTR")) { FILE* f = fopen(getenv("PA_TRACE_PTR"), "w"); fprintf(f, "%llu\n", (unsigned long long)(uintptr_t)tr); fclose(f); }
+  }
+#endif
   timing_mark(ctx, st, 0);
   CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, st));
   timing_mark(ctx, st, 1);

@@ -56,6 +56,7 @@ struct PrefillParams {
   uint32_t seq, pos, n_cols, n_heads, G, max_seq;
   float scale_log2;
   uint32_t* err;
+  unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
 };
 
 }  // namespace pa

@@ -25,6 +25,13 @@
 
 namespace pa {
 
+#ifdef PA_TRACE   // development builds: per-CTA timestamps of the pipeline stages
+__device__ __forceinline__ unsigned long long pf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define PTR(slot) do { if (p.trace && lane == 0 && (slot) < 256) p.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + (slot)] = pf_gtime(); } while (0)
+#else
+#define PTR(slot) do {} while (0)
+#endif
+
 constexpr int kBM = 128;   // query rows per CTA
 constexpr int kBN = 64;    // keys per tile
 constexpr int kPfThreads = 256;
@@ -48,8 +55,7 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
 // the mbarrier gets one arrival when every MMA issued so far by this thread has retired
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -143,6 +149,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const uint32_t rows_valid = min((uint32_t)kBM, p.n_cols - c0);
   const uint32_t p0 = p.pos + c0;                       // cache row of column c0's own token
   const uint32_t n_tiles = (p0 + rows_valid + kBN - 1) / kBN;
+  if (warp == 4) PTR(0);
 
   enum { Q_FULL_IDX = 17 };
   constexpr int kQLoaders = 160;   // warps 2, 4, 5, 6, 7 stage Q; warps 0 / 3 feed K / V; warp 1 issues the MMAs
@@ -204,6 +211,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
     fence_proxy_async();   // the tensor cores read Q through the async proxy
     mbar_arrive(bar0 + 8u * Q_FULL_IDX);
+    if (warp == 4) PTR(1);
   }
 
   if (warp == 0) {
@@ -213,6 +221,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j & 1, u = j >> 1;
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
+        if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
         tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)(j * kBN), (int)(g * CH), BAR(K_FULL, st));
       }
@@ -225,6 +234,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j & 1, u = j >> 1;
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
+        if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
         tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)(j * kBN), (int)(g * CH), BAR(V_FULL, st));
       }
@@ -233,38 +243,43 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer ----
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
-      const uint32_t q_addr = smem_u32(q_s);
+      // descriptors are built once; a k-step only adds a byte offset (>> 4) to the address field
+      const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
+      const uint64_t k_desc[2] = {smem_desc(smem_u32(base + L::OFF_K), 16, 1024), smem_desc(smem_u32(base + L::OFF_K + L::KV_BYTES), 16, 1024)};
+      const uint64_t p_desc[2] = {smem_desc(smem_u32(p_s), 16, 1024), smem_desc(smem_u32(p_s + L::P_BYTES), 16, 1024)};
+      const uint64_t v_desc[2] = {smem_desc(smem_u32(base + L::OFF_V), kBN * 128, 1024), smem_desc(smem_u32(base + L::OFF_V + L::KV_BYTES), kBN * 128, 1024)};
       mbar_wait(bar0 + 8u * Q_FULL_IDX, 0, s_err, WAIT_QFULL);
       tc_fence_after();
       auto issue_qk = [&](uint32_t j) {
         const uint32_t b = j & 1, u = j >> 1;
+        if (j < 10) PTR(90 + 3 * j);
         mbar_wait(BAR(K_FULL, b), u & 1, s_err, WAIT_KFULL);
+        if (j < 10) PTR(91 + 3 * j);
         mbar_wait(BAR(S_EMPTY, b), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(base + L::OFF_K + b * L::KV_BYTES);
+        const uint64_t kd = k_desc[b];
+        const uint32_t ts = t_s0 + b * kBN;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t ad = smem_desc(q_addr + (ks >> 2) * (kBM * 128) + (ks & 3) * 32, 16, 1024);
-          const uint64_t bd = smem_desc(k_addr + (ks >> 2) * (kBN * 128) + (ks & 3) * 32, 16, 1024);
-          umma_f16(t_s0 + b * kBN, ad, bd, idesc_qk, ks > 0);
-        }
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16(ts, q_desc + (uint64_t)(((ks >> 2) * (kBM * 128) + (ks & 3) * 32) >> 4), kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4),
+                   idesc_qk, ks > 0);
         umma_commit(BAR(K_EMPTY, b));
         umma_commit(BAR(S_FULL, b));
+        if (j < 10) PTR(92 + 3 * j);
       };
       issue_qk(0);
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t b = j & 1, u = j >> 1;
         if (j + 1 < n_tiles) issue_qk(j + 1);
+        if (j < 10) PTR(130 + 3 * j);
         mbar_wait(BAR(P_FULL, b), u & 1, s_err, WAIT_QFULL);
+        if (j < 10) PTR(131 + 3 * j);
         mbar_wait(BAR(V_FULL, b), u & 1, s_err, WAIT_VFULL);
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(p_s + b * L::P_BYTES), v_addr = smem_u32(base + L::OFF_V + b * L::KV_BYTES);
+        if (j < 10) PTR(132 + 3 * j);
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          const uint64_t ad = smem_desc(p_addr + ks * 32, 16, 1024);
-          const uint64_t bd = smem_desc(v_addr + ks * 2048, kBN * 128, 1024);
-          umma_f16(t_o, ad, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < kBN / 16; ++ks)
+          umma_f16(t_o, p_desc[b] + (uint64_t)((ks * 32) >> 4), v_desc[b] + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         umma_commit(BAR(V_EMPTY, b));
         umma_commit(BAR(P_EMPTY, b));
       }
@@ -280,6 +295,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       const uint32_t b = j & 1, u = j >> 1, kv0 = j * kBN;
       mbar_wait(BAR(S_FULL, b), u & 1, s_err, WAIT_MMA);
       tc_fence_after();
+      if (warp == 4 && j < 10) PTR(8 + 6 * j);
       float s[kBN];
       {
         float t0[32], t1[32];
@@ -290,6 +306,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(BAR(S_EMPTY, b));
+      if (warp == 4 && j < 10) PTR(9 + 6 * j);
       // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
       if (kv0 + kBN > lim) {
 #pragma unroll
@@ -318,8 +335,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         }
         tc_fence_before();
       }
+      if (warp == 4 && j < 10) PTR(10 + 6 * j);
       // P = 2^(s - m) as f16 into the swizzled K-major tile of buffer b (free once P V (j-2) has retired)
       mbar_wait(BAR(P_EMPTY, b), (u & 1) ^ 1, s_err, WAIT_MMA);
+      if (warp == 4 && j < 10) PTR(11 + 6 * j);
       uint8_t* prow = p_s + b * L::P_BYTES + row * 128;
       float ls = 0.f;
 #pragma unroll
@@ -331,12 +350,15 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             make_uint4(pack_h2(e[0], e[1]), pack_h2(e[2], e[3]), pack_h2(e[4], e[5]), pack_h2(e[6], e[7]));
       }
       l_sum += ls;
+      if (warp == 4 && j < 10) PTR(12 + 6 * j);
       fence_proxy_async();
       mbar_arrive(BAR(P_FULL, b));
+      if (warp == 4 && j < 10) PTR(13 + 6 * j);
     }
     // ---- epilogue: O / l, gate, store ----
     mbar_wait(BAR(O_DONE, 0), 0, s_err, WAIT_MMA);
     tc_fence_after();
+    if (warp == 4) PTR(2);
     const float inv_l = 1.f / l_sum;
     const uint32_t col = c0 + row;
 #pragma unroll 1
@@ -368,6 +390,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       }
     }
     tc_fence_before();
+    if (warp == 4) PTR(3);
   }
   __syncthreads();
   if (warp == 2) {
