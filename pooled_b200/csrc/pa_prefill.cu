@@ -5,14 +5,15 @@
 // the causal diagonal.  K/V tiles of the G heads of a GQA group are the same bytes, read by G CTAs that run at about
 // the same time; the caches of a prefill fit the 126 MB L2, so HBM sees them once.
 //
-//   warps 0, 3  TMA producers: K tiles and V tiles (64 x head_dim f16, 128-byte swizzle), a two-slot ring each
+//   warps 0, 3  TMA producers: K tiles and V tiles (64 x head_dim f16, 128-byte swizzle), a three-slot ring each
 //   warp 1      MMA issuer (one thread): S = Q K^T into a double-buffered TMEM tile (128 x 64 f32), then
-//               O += P V into the TMEM accumulator (128 x head_dim f32); completion is signalled to mbarriers
-//               with tcgen05.commit
-//   warp 2      allocates / frees tensor memory; with warps 4-7 stages the Q tile (f16, swizzled) while K/V stream in
-//   warps 4-7   softmax: thread r owns query row r (TMEM lane r): tcgen05.ld of its S row, scale + causal mask,
-//               running max / sum, P = 2^(s - m) as f16 into shared memory in the K-major swizzled layout the
-//               second MMA reads, and the epilogue (O / l, sigmoid gate, store)
+//               O += P V into the TMEM accumulator (128 x head_dim f32).  Both A operands come from tensor memory
+//               (Q sits there for the CTA's life, P is written over its own S tile), so shared-memory bandwidth
+//               carries the K / V slices only; completion is signalled to mbarriers with tcgen05.commit
+//   warp 2      allocates / frees tensor memory
+//   warps 4-7   softmax: thread r owns query row r (TMEM lane r): stores its Q row into TMEM as f16 pairs, then per
+//               tile tcgen05.ld of its S row, causal mask, running max / sum, P = 2^(s - m) as f16 pairs back into
+//               TMEM (tcgen05.st), and the epilogue (O / l, sigmoid gate, store)
 // S(j+1) is issued before the softmax of tile j has finished, so the tensor cores work on the next scores while
 // the weights of the current tile are being formed.  O is rescaled only when a row's running maximum has grown by
 // more than 2^8 since its last rescale (weights stay below 2^8, exact in f32 sums and safe in f16); the rescale
@@ -116,14 +117,36 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t M, uint32_t N, uint32
   return (1u << 4) | (b_mn_major << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+// TMEM loads / stores of 32 raw 32-bit columns (packed f16 pairs)
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+        "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D (TMEM) (+)= A (TMEM, packed f16 pairs: lane = row, column c = elements 2c, 2c+1) * B (smem descriptor)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate));
+}
+
+constexpr int kStages = 3;   // K ring and V ring depth
+
 template <int HD>
 struct PfSmem {
-  static constexpr int Q_BYTES = HD * 256;          // [HD/64][128 rows][128 B]
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
-  static constexpr int P_BYTES = kBM * 128;         // [128 rows][64 keys f16]
-  static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES, OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_K = 0, OFF_V = kStages * KV_BYTES, OFF_BAR = 2 * kStages * KV_BYTES;
   static constexpr int TOTAL = 1024 + OFF_BAR + 256;
-  static constexpr int TMEM_COLS = HD == 256 ? 512 : 256;   // S0, S1 (64 each) + O (HD), rounded to a power of two
+  // tensor memory columns: Q (HD/2: f16 pairs) | S0 | S1 (64 each; P overwrites the first 32 of its S) | O (HD)
+  static constexpr int T_Q = 0, T_S = HD / 2, T_O = HD / 2 + 2 * kBN;
+  static constexpr int TMEM_COLS = 512;
 };
 
 template <int HD>
@@ -133,14 +156,12 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   constexpr int CH = HD / 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = base;
-  uint8_t* p_s = base + L::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 20);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 24);
   volatile uint32_t* s_err = s_tmem + 1;
   const uint32_t bar0 = smem_u32(bars);
-  auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which * 2 + idx); };
-  enum { K_FULL = 0, K_EMPTY, V_FULL, V_EMPTY, S_FULL, S_EMPTY, P_FULL, P_EMPTY, O_DONE };
+  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 14, PV_DONE = 16, O_DONE = 18, Q_FULL = 19 };
+  auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t q_tile = gridDim.x - 1 - blockIdx.x;   // longest rows first
@@ -151,18 +172,15 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const uint32_t n_tiles = (p0 + rows_valid + kBN - 1) / kBN;
   if (warp == 4) PTR(0);
 
-  enum { Q_FULL_IDX = 17 };
-  constexpr int kQLoaders = 160;   // warps 2, 4, 5, 6, 7 stage Q; warps 0 / 3 feed K / V; warp 1 issues the MMAs
   if (warp == 1 && lane == 0) {
     *s_err = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       mbar_init(BAR(K_FULL, i), 1); mbar_init(BAR(K_EMPTY, i), 1);
       mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1);
-      mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(S_EMPTY, i), 128);
-      mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(P_EMPTY, i), 1);
     }
+    for (int i = 0; i < 2; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
-    mbar_init(bar0 + 8u * Q_FULL_IDX, kQLoaders);
+    mbar_init(BAR(Q_FULL, 0), 128);
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -174,52 +192,14 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t t_s0 = tmem, t_o = tmem + 2 * kBN;
-
-  if (warp != 0 && warp != 1 && warp != 3) {
-    // ---- Q tile -> shared memory: f16, K-major, 128-byte swizzle; eight 16-byte pieces per thread in flight ----
-    const int qt = warp == 2 ? lane : (warp - 3) * 32 + lane;   // 0 .. 159
-    constexpr int ITEMS = kBM * (HD / 8);
-    for (int i0 = qt; i0 < ITEMS; i0 += kQLoaders * 8) {
-      uint4 lo[8], hi[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int idx = i0 + u * kQLoaders;
-        const uint32_t row = idx / (HD / 8), c16 = idx % (HD / 8);
-        lo[u] = hi[u] = make_uint4(0, 0, 0, 0);
-        if (idx < ITEMS && row < rows_valid) {
-          const uint64_t off = (uint64_t)(c0 + row) * p.q_col_stride + (uint64_t)h * p.q_head_stride + c16 * 8;
-          if (p.q_f16) {
-            lo[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off);
-          } else {
-            lo[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.q) + off);
-            hi[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.q) + off + 4);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int idx = i0 + u * kQLoaders;
-        if (idx >= ITEMS) continue;
-        const uint32_t row = idx / (HD / 8), c16 = idx % (HD / 8);
-        uint4 packed = lo[u];
-        if (!p.q_f16)
-          packed = make_uint4(pack_h2(__uint_as_float(lo[u].x), __uint_as_float(lo[u].y)), pack_h2(__uint_as_float(lo[u].z), __uint_as_float(lo[u].w)),
-                              pack_h2(__uint_as_float(hi[u].x), __uint_as_float(hi[u].y)), pack_h2(__uint_as_float(hi[u].z), __uint_as_float(hi[u].w)));
-        *reinterpret_cast<uint4*>(q_s + (c16 >> 3) * (kBM * 128) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4)) = packed;
-      }
-    }
-    fence_proxy_async();   // the tensor cores read Q through the async proxy
-    mbar_arrive(bar0 + 8u * Q_FULL_IDX);
-    if (warp == 4) PTR(1);
-  }
+  const uint32_t t_q = tmem + L::T_Q, t_s0 = tmem + L::T_S, t_o = tmem + L::T_O;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer, K ----
     if (lane == 0) {
       prefetch_tmap(&tm_k);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t st = j & 1, u = j >> 1;
+        const uint32_t st = j % kStages, u = j / kStages;
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
@@ -232,7 +212,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (lane == 0) {
       prefetch_tmap(&tm_v);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t st = j & 1, u = j >> 1;
+        const uint32_t st = j % kStages, u = j / kStages;
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
@@ -243,45 +223,50 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer ----
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
-      // descriptors are built once; a k-step only adds a byte offset (>> 4) to the address field
-      const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
-      const uint64_t k_desc[2] = {smem_desc(smem_u32(base + L::OFF_K), 16, 1024), smem_desc(smem_u32(base + L::OFF_K + L::KV_BYTES), 16, 1024)};
-      const uint64_t p_desc[2] = {smem_desc(smem_u32(p_s), 16, 1024), smem_desc(smem_u32(p_s + L::P_BYTES), 16, 1024)};
-      const uint64_t v_desc[2] = {smem_desc(smem_u32(base + L::OFF_V), kBN * 128, 1024), smem_desc(smem_u32(base + L::OFF_V + L::KV_BYTES), kBN * 128, 1024)};
-      mbar_wait(bar0 + 8u * Q_FULL_IDX, 0, s_err, WAIT_QFULL);
+      // Both A operands live in tensor memory (Q for the whole CTA, P per tile), so a k-step costs shared-memory
+      // bandwidth for the K or V slice only.  B descriptors are built once; a k-step adds a byte offset (>> 4).
+      uint64_t k_desc[kStages], v_desc[kStages];
+#pragma unroll
+      for (int i = 0; i < kStages; ++i) {
+        k_desc[i] = smem_desc(smem_u32(base + L::OFF_K + i * L::KV_BYTES), 16, 1024);
+        v_desc[i] = smem_desc(smem_u32(base + L::OFF_V + i * L::KV_BYTES), kBN * 128, 1024);
+      }
+      mbar_wait(BAR(Q_FULL, 0), 0, s_err, WAIT_QFULL);
       tc_fence_after();
       auto issue_qk = [&](uint32_t j) {
-        const uint32_t b = j & 1, u = j >> 1;
+        const uint32_t b = j & 1, u = j >> 1, st = j % kStages;
         if (j < 10) PTR(90 + 3 * j);
-        mbar_wait(BAR(K_FULL, b), u & 1, s_err, WAIT_KFULL);
+        mbar_wait(BAR(K_FULL, st), (j / kStages) & 1, s_err, WAIT_KFULL);
         if (j < 10) PTR(91 + 3 * j);
-        mbar_wait(BAR(S_EMPTY, b), (u & 1) ^ 1, s_err, WAIT_EMPTY);
-        tc_fence_after();
-        const uint64_t kd = k_desc[b];
+        (void)u;
+        const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[2]);
         const uint32_t ts = t_s0 + b * kBN;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16(ts, q_desc + (uint64_t)(((ks >> 2) * (kBM * 128) + (ks & 3) * 32) >> 4), kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4),
-                   idesc_qk, ks > 0);
-        umma_commit(BAR(K_EMPTY, b));
+          umma_f16_ts(ts, t_q + ks * 8, kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
+        umma_commit(BAR(K_EMPTY, st));
         umma_commit(BAR(S_FULL, b));
         if (j < 10) PTR(92 + 3 * j);
       };
       issue_qk(0);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t b = j & 1, u = j >> 1;
+        const uint32_t b = j & 1, u = j >> 1, st = j % kStages;
+        // S(j+1) overwrites the buffer that held S(j-1) / P(j-1): P V (j-1) was issued before it and the tensor
+        // pipe runs one thread's MMAs in order, so no extra wait is needed
         if (j + 1 < n_tiles) issue_qk(j + 1);
         if (j < 10) PTR(130 + 3 * j);
         mbar_wait(BAR(P_FULL, b), u & 1, s_err, WAIT_QFULL);
         if (j < 10) PTR(131 + 3 * j);
-        mbar_wait(BAR(V_FULL, b), u & 1, s_err, WAIT_VFULL);
+        mbar_wait(BAR(V_FULL, st), (j / kStages) & 1, s_err, WAIT_VFULL);
         tc_fence_after();
         if (j < 10) PTR(132 + 3 * j);
+        const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[2]);
+        const uint32_t tp = t_s0 + b * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s buffer
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
-          umma_f16(t_o, p_desc[b] + (uint64_t)((ks * 32) >> 4), v_desc[b] + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(BAR(V_EMPTY, b));
-        umma_commit(BAR(P_EMPTY, b));
+          umma_f16_ts(t_o, tp + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(BAR(V_EMPTY, st));
+        umma_commit(BAR(PV_DONE, b));
       }
       umma_commit(BAR(O_DONE, 0));
     }
@@ -289,6 +274,35 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ softmax + epilogue ----
     const uint32_t qd = warp - 4, row = qd * 32 + lane;
     const uint32_t lane_addr = (qd * 32) << 16;
+    // ---- this thread's Q row -> tensor memory as packed f16 pairs (rows past the chunk are zero) ----
+    {
+      const bool live = row < rows_valid;
+      const uint64_t off = (uint64_t)(c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)h * p.q_head_stride;
+#pragma unroll 1
+      for (int c = 0; c < HD / 64; ++c) {          // 64 elements = 32 columns per step
+        uint32_t w[32];
+        if (p.q_f16) {
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c * 64);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 x = live ? src[i] : make_uint4(0, 0, 0, 0);
+            w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+          }
+        } else {
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c * 64);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float4 x = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
+          }
+        }
+        tmem_st32u(t_q + c * 32 + lane_addr, w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(Q_FULL, 0));
+    }
+    if (warp == 4) PTR(1);
     const uint32_t lim = p0 + row + 1;      // keys [0, lim) are visible to this row
     float m_st = -INFINITY, l_sum = 0.f;
     for (uint32_t j = 0; j < n_tiles; ++j) {
@@ -304,8 +318,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
       }
-      tc_fence_before();
-      mbar_arrive(BAR(S_EMPTY, b));
       if (warp == 4 && j < 10) PTR(9 + 6 * j);
       // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
       if (kv0 + kBN > lim) {
@@ -319,11 +331,11 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       float alpha = 1.f;
       bool grow = false;
       if (j == 0) m_st = mt;                        // key 0 is visible to every row, so mt is finite
-      else if (mt > m_st + 8.f) { alpha = exp2f(m_st - mt); m_st = mt; l_sum *= alpha; grow = true; }
+      else if (mt > m_st + 8.f) { alpha = ex2_approx(m_st - mt); m_st = mt; l_sum *= alpha; grow = true; }
       if (__any_sync(0xffffffffu, grow)) {
         // O must not change under the previous P V: wait for it, then rescale this warp's 32 rows in TMEM
         const uint32_t jb = (j - 1) & 1, ju = (j - 1) >> 1;
-        mbar_wait(BAR(P_EMPTY, jb), ju & 1, s_err, WAIT_MMA);
+        mbar_wait(BAR(PV_DONE, jb), ju & 1, s_err, WAIT_MMA);
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
@@ -333,25 +345,22 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           for (int i = 0; i < 32; ++i) o[i] *= alpha;
           tmem_st32(t_o + c * 32 + lane_addr, o);
         }
-        tc_fence_before();
       }
       if (warp == 4 && j < 10) PTR(10 + 6 * j);
-      // P = 2^(s - m) as f16 into the swizzled K-major tile of buffer b (free once P V (j-2) has retired)
-      mbar_wait(BAR(P_EMPTY, b), (u & 1) ^ 1, s_err, WAIT_MMA);
-      if (warp == 4 && j < 10) PTR(11 + 6 * j);
-      uint8_t* prow = p_s + b * L::P_BYTES + row * 128;
+      // P = 2^(s - m) as packed f16 pairs over the first 32 columns of this S buffer (its scores are in registers now)
+      uint32_t pw[32];
       float ls = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float e[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { e[i] = ex2_approx(fmaf(s[c * 8 + i], p.scale_log2, -m_st)); ls += e[i]; }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
-            make_uint4(pack_h2(e[0], e[1]), pack_h2(e[2], e[3]), pack_h2(e[4], e[5]), pack_h2(e[6], e[7]));
+      for (int i = 0; i < 32; ++i) {
+        const float e0 = ex2_approx(fmaf(s[2 * i], p.scale_log2, -m_st)), e1 = ex2_approx(fmaf(s[2 * i + 1], p.scale_log2, -m_st));
+        ls += e0 + e1;
+        pw[i] = pack_h2(e0, e1);
       }
       l_sum += ls;
+      tmem_st32u(t_s0 + b * kBN + lane_addr, pw);
+      tmem_wait_st();
       if (warp == 4 && j < 10) PTR(12 + 6 * j);
-      fence_proxy_async();
+      tc_fence_before();
       mbar_arrive(BAR(P_FULL, b));
       if (warp == 4 && j < 10) PTR(13 + 6 * j);
     }
