@@ -129,12 +129,28 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[3
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // D (TMEM) (+)= A (TMEM, packed f16 pairs: lane = row, column c = elements 2c, 2c+1) * B (smem descriptor)
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// The whole MMA warp runs the issue loop with identical values and only the elected lane executes the instruction:
+// the operands of tcgen05.mma live in uniform registers, which the compiler can only use where control flow is
+// warp-uniform (inside an `if (lane == 0)` every operand would be copied over one by one before each MMA).
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t leader;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+  return leader;
+}
+__device__ __forceinline__ void umma_f16_ts(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, e;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate));
+      "setp.ne.b32 e, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader));
+}
+__device__ __forceinline__ void umma_commit_elected(uint32_t leader, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "setp.ne.b32 e, %1, 0;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar), "r"(leader) : "memory");
 }
 
 constexpr int kStages = 3;   // K ring and V ring depth
@@ -221,7 +237,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer ----
-    if (lane == 0) {
+    {
+      const uint32_t leader = elect_one();
       constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
       // Both A operands live in tensor memory (Q for the whole CTA, P per tile), so a k-step costs shared-memory
       // bandwidth for the K or V slice only.  B descriptors are built once; a k-step adds a byte offset (>> 4).
@@ -243,9 +260,9 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         const uint32_t ts = t_s0 + b * kBN;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16_ts(ts, t_q + ks * 8, kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
-        umma_commit(BAR(K_EMPTY, st));
-        umma_commit(BAR(S_FULL, b));
+          umma_f16_ts(leader, ts, t_q + ks * 8, kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
+        umma_commit_elected(leader, BAR(K_EMPTY, st));
+        umma_commit_elected(leader, BAR(S_FULL, b));
         if (j < 10) PTR(92 + 3 * j);
       };
       issue_qk(0);
@@ -264,11 +281,11 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         const uint32_t tp = t_s0 + b * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s buffer
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
-          umma_f16_ts(t_o, tp + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(BAR(V_EMPTY, st));
-        umma_commit(BAR(PV_DONE, b));
+          umma_f16_ts(leader, t_o, tp + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit_elected(leader, BAR(V_EMPTY, st));
+        umma_commit_elected(leader, BAR(PV_DONE, b));
       }
-      umma_commit(BAR(O_DONE, 0));
+      umma_commit_elected(leader, BAR(O_DONE, 0));
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax + epilogue ----
