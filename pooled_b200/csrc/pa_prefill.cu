@@ -145,6 +145,14 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t leader, uint32_t d_tmem, ui
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader));
 }
+__device__ __forceinline__ void umma_f16_ss(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 e, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader));
+}
 __device__ __forceinline__ void umma_commit_elected(uint32_t leader, uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred e;\n\t"
@@ -155,13 +163,17 @@ __device__ __forceinline__ void umma_commit_elected(uint32_t leader, uint32_t ba
 
 constexpr int kStages = 3;   // K ring and V ring depth
 
+constexpr int kSBuf = 3;     // S / P tiles in tensor memory: S(j+2) is formed while softmax(j) runs and P(j-1) is consumed
+
 template <int HD>
 struct PfSmem {
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
-  static constexpr int OFF_K = 0, OFF_V = kStages * KV_BYTES, OFF_BAR = 2 * kStages * KV_BYTES;
+  static constexpr int QS_BYTES = HD * 128;         // upper half of the head dims of Q: [HD/128][128 rows][128 B]
+  static constexpr int OFF_K = 0, OFF_V = kStages * KV_BYTES, OFF_Q = 2 * kStages * KV_BYTES, OFF_BAR = OFF_Q + QS_BYTES;
   static constexpr int TOTAL = 1024 + OFF_BAR + 256;
-  // tensor memory columns: Q (HD/2: f16 pairs) | S0 | S1 (64 each; P overwrites the first 32 of its S) | O (HD)
-  static constexpr int T_Q = 0, T_S = HD / 2, T_O = HD / 2 + 2 * kBN;
+  // tensor memory columns: lower half of Q (HD/4: f16 pairs) | S0 S1 S2 (64 each; P overwrites the first 32 of
+  // its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
+  static constexpr int T_Q = 0, T_S = HD / 4, T_O = HD / 4 + kSBuf * kBN;
   static constexpr int TMEM_COLS = 512;
 };
 
@@ -176,7 +188,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 24);
   volatile uint32_t* s_err = s_tmem + 1;
   const uint32_t bar0 = smem_u32(bars);
-  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 14, PV_DONE = 16, O_DONE = 18, Q_FULL = 19 };
+  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22 };
+  uint8_t* q_s = base + L::OFF_Q;
   auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -194,7 +207,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mbar_init(BAR(K_FULL, i), 1); mbar_init(BAR(K_EMPTY, i), 1);
       mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1);
     }
-    for (int i = 0; i < 2; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
+    for (int i = 0; i < kSBuf; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
     mbar_init(BAR(Q_FULL, 0), 128);
     fence_barrier_init();
@@ -248,42 +261,50 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         k_desc[i] = smem_desc(smem_u32(base + L::OFF_K + i * L::KV_BYTES), 16, 1024);
         v_desc[i] = smem_desc(smem_u32(base + L::OFF_V + i * L::KV_BYTES), kBN * 128, 1024);
       }
+      const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
       mbar_wait(BAR(Q_FULL, 0), 0, s_err, WAIT_QFULL);
       tc_fence_after();
       auto issue_qk = [&](uint32_t j) {
-        const uint32_t b = j & 1, u = j >> 1, st = j % kStages;
+        const uint32_t sb = j % kSBuf, st = j % kStages;
         if (j < 10) PTR(90 + 3 * j);
         mbar_wait(BAR(K_FULL, st), (j / kStages) & 1, s_err, WAIT_KFULL);
+        tc_fence_after();
         if (j < 10) PTR(91 + 3 * j);
-        (void)u;
         const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[2]);
-        const uint32_t ts = t_s0 + b * kBN;
+        const uint32_t ts = t_s0 + sb * kBN;
+        // lower half of the head dims: Q from tensor memory; upper half: Q from shared memory
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
+        for (int ks = 0; ks < HD / 32; ++ks)
           umma_f16_ts(leader, ts, t_q + ks * 8, kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
+#pragma unroll
+        for (int ks = HD / 32; ks < HD / 16; ++ks)
+          umma_f16_ss(leader, ts, q_desc + (uint64_t)(((((ks - HD / 32) >> 2)) * (kBM * 128) + (ks & 3) * 32) >> 4),
+                      kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, 1u);
         umma_commit_elected(leader, BAR(K_EMPTY, st));
-        umma_commit_elected(leader, BAR(S_FULL, b));
+        umma_commit_elected(leader, BAR(S_FULL, sb));
         if (j < 10) PTR(92 + 3 * j);
       };
+      // The scores run two tiles ahead of the weights: S(j+2) is issued before P V (j), so the softmax of tile j+1
+      // never waits behind the P V of tile j-1.  S(j+2) reuses the TMEM tile of S(j-1) / P(j-1); P V (j-1) was issued
+      // earlier and one thread's MMAs retire in order.
       issue_qk(0);
+      if (n_tiles > 1) issue_qk(1);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t b = j & 1, u = j >> 1, st = j % kStages;
-        // S(j+1) overwrites the buffer that held S(j-1) / P(j-1): P V (j-1) was issued before it and the tensor
-        // pipe runs one thread's MMAs in order, so no extra wait is needed
-        if (j + 1 < n_tiles) issue_qk(j + 1);
+        const uint32_t sb = j % kSBuf, st = j % kStages;
+        if (j + 2 < n_tiles) issue_qk(j + 2);
         if (j < 10) PTR(130 + 3 * j);
-        mbar_wait(BAR(P_FULL, b), u & 1, s_err, WAIT_QFULL);
+        mbar_wait(BAR(P_FULL, sb), (j / kSBuf) & 1, s_err, WAIT_QFULL);
         if (j < 10) PTR(131 + 3 * j);
         mbar_wait(BAR(V_FULL, st), (j / kStages) & 1, s_err, WAIT_VFULL);
         tc_fence_after();
         if (j < 10) PTR(132 + 3 * j);
         const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[2]);
-        const uint32_t tp = t_s0 + b * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s buffer
+        const uint32_t tp = t_s0 + sb * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s tile
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
           umma_f16_ts(leader, t_o, tp + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         umma_commit_elected(leader, BAR(V_EMPTY, st));
-        umma_commit_elected(leader, BAR(PV_DONE, b));
+        umma_commit_elected(leader, BAR(PV_DONE, sb));
       }
       umma_commit_elected(leader, BAR(O_DONE, 0));
     }
@@ -296,7 +317,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       const bool live = row < rows_valid;
       const uint64_t off = (uint64_t)(c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)h * p.q_head_stride;
 #pragma unroll 1
-      for (int c = 0; c < HD / 64; ++c) {          // 64 elements = 32 columns per step
+      for (int c = 0; c < HD / 64; ++c) {          // 64 elements per step: 32 TMEM columns, or one 128-byte row chunk
         uint32_t w[32];
         if (p.q_f16) {
           const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c * 64);
@@ -313,8 +334,16 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
-        tmem_st32u(t_q + c * 32 + lane_addr, w);
+        if (c < HD / 128) {
+          tmem_st32u(t_q + c * 32 + lane_addr, w);
+        } else {
+          uint8_t* dst = q_s + (c - HD / 128) * (kBM * 128) + row * 128;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint4*>(dst + ((i ^ (row & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
       }
+      fence_proxy_async();
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(Q_FULL, 0));
@@ -323,7 +352,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t lim = p0 + row + 1;      // keys [0, lim) are visible to this row
     float m_st = -INFINITY, l_sum = 0.f;
     for (uint32_t j = 0; j < n_tiles; ++j) {
-      const uint32_t b = j & 1, u = j >> 1, kv0 = j * kBN;
+      const uint32_t b = j % kSBuf, u = j / kSBuf, kv0 = j * kBN;
       mbar_wait(BAR(S_FULL, b), u & 1, s_err, WAIT_MMA);
       tc_fence_after();
       if (warp == 4 && j < 10) PTR(8 + 6 * j);
@@ -351,7 +380,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       else if (mt > m_st + 8.f) { alpha = ex2_approx(m_st - mt); m_st = mt; l_sum *= alpha; grow = true; }
       if (__any_sync(0xffffffffu, grow)) {
         // O must not change under the previous P V: wait for it, then rescale this warp's 32 rows in TMEM
-        const uint32_t jb = (j - 1) & 1, ju = (j - 1) >> 1;
+        const uint32_t jb = (j - 1) % kSBuf, ju = (j - 1) / kSBuf;
         mbar_wait(BAR(PV_DONE, jb), ju & 1, s_err, WAIT_MMA);
         tc_fence_after();
 #pragma unroll 1
