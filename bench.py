@@ -138,7 +138,9 @@ def run_ours(args, w):
     sharded = world > 1
     if sharded:
         plan = ShardPlan(world, chunk)
-        sd = ShardedDecoder(eng, plan, rank, dist)
+        if args.exchange == "peer":
+            eng.exchange_setup(rank, world, dist, max_rows=max(64, T * nH))
+        sd = ShardedDecoder(eng, plan, rank, dist, exchange=args.exchange)
         gbuf = torch.empty((world, T * nH * (hd + 2)), dtype=torch.float32, device=dev)
         new_pos = total_ctx - 1   # the new token is the last row of the last rank's chunk
         seqs_pos = [(s, new_pos) for s in range(n_seqs)]
@@ -179,7 +181,7 @@ def run_ours(args, w):
     launches_per_step = None
     run_step = step
     graph = None
-    if args.graph and not sharded:
+    if args.graph and (not sharded or args.exchange == "peer"):   # NCCL inside a captured step is left to eager launches
         s0 = eng.stats()
         cs = torch.cuda.Stream(device=dev)
         cs.wait_stream(torch.cuda.current_stream(dev))
@@ -282,6 +284,7 @@ def run_ours(args, w):
         "config": {"workload": w["desc"], "kv_rows_per_gpu": chunk, "total_context": total_ctx, "layers_per_step": layers,
                    "l2": "each layer has its own caches; a step touches %d MB per GPU, more than the 126 MB L2, before any row is reused" % (layers * kernel_bytes // 1_000_000),
                    "launch": "CUDA graph replay of the step" if graph is not None else "eager C-ABI calls",
+                   "exchange": (args.exchange if sharded else None),
                    "pct_of_8TBs_nominal": round(100 * value / world / 8000, 1)},
         "roofline": {"bound": "hbm", "kernel": "pa_decode_kernel", "achieved": round(achieved, 1) if achieved else None, "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4) if achieved else None, "peak_source": peak_src, "launches_timed": int(core_n),
@@ -429,6 +432,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager C-ABI calls instead of a CUDA-graph replay of the step")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="sharded decode (N > 1): merge inside the combine kernel over peer memory, or NCCL all-gather + merge kernel")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling captures)")
     ap.add_argument("--cols", type=int, default=0, help="override the prompt length of the prefill workload (small profiling captures)")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the decode kernel, if known")

@@ -178,6 +178,26 @@ PA_API int pa_merge(pa_ctx* ctx, const float* parts, uint32_t n_parts, uint32_t 
                     uint64_t gate_col_stride, uint64_t gate_head_stride, void* out, uint64_t out_col_stride,
                     void* stream);
 
+/* ---- KV-sequence-sharded decode with the merge fused over peer memory ---------------------------------------- */
+
+/* Peer exchange set-up (one process per GPU of one box; no counterpart in the reference).  Each rank allocates one
+ * exchange buffer of pa_exchange_bytes() with pa_shared_alloc (zeroed, with a 64-byte IPC handle to hand to the
+ * other ranks over any channel), opens the other ranks' handles with pa_shared_open, and passes all `world`
+ * pointers (its own included, in rank order) to pa_exchange_init.  max_rows bounds columns * n_heads of one call. */
+PA_API size_t pa_exchange_bytes(pa_ctx* ctx, uint32_t world, uint32_t max_rows);
+PA_API int pa_shared_alloc(pa_ctx* ctx, size_t bytes, void** dev_ptr, void* ipc_handle_out);
+PA_API int pa_shared_open(pa_ctx* ctx, const void* ipc_handle, void** dev_ptr);
+PA_API int pa_shared_close(pa_ctx* ctx, void* dev_ptr);
+PA_API int pa_exchange_init(pa_ctx* ctx, uint32_t rank, uint32_t world, void* const* bufs, uint32_t max_rows);
+/* pa_decode over this rank's shard with the cross-GPU merge inside the combine kernel: each CTA stores its merged
+ * (o, m, l) slice into every rank's exchange buffer with plain stores over NVLink, raises a per-(row, slice) flag,
+ * waits (bounded) for the other ranks' flags, merges and writes the gated output.  Every rank must make the same
+ * call in the same order; every rank ends with the full result.  The arithmetic is attn_dec_combine(_g)'s
+ * (engine/wgsl/attn_dec.js:215-287) applied to per-GPU records. */
+PA_API int pa_decode_exchange(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q, int q_dtype,
+                              uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
+                              uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);
+
 /* Tiled causal prefill of n_cols columns of one sequence starting at pos (their K/V already appended).
  * Replaces attn_flash_tile + attn_combine_tile + sigmoid_mul_mc (engine/wgsl/attn_tile.js:108-193,
  * engine/wgsl/qwen35.js:877-887) as dispatched by _encAttnCore (engine/qwen35.js:2489-2493, :2516). */

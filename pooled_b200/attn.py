@@ -307,3 +307,38 @@ class AttnEngine:
                                           gate.stride(0) if gate is not None else 0, gate.stride(1) if gate is not None else 0,
                                           gate_head_stride or self.cfg.head_dim, self._p(out), out.stride(0), out.stride(1), self._st()))
         return out
+
+    # ---- sharded decode with the merge over peer memory ----
+    def exchange_setup(self, rank: int, world: int, dist=None, max_rows: int = 512):
+        """Allocate this rank's exchange buffer, swap IPC handles with the other ranks (torch.distributed object
+        all-gather; any channel would do) and open theirs.  world == 1 needs no peers."""
+        nbytes = self.L.pa_exchange_bytes(self.ctx, world, max_rows)
+        own, handle = C.c_void_p(), C.create_string_buffer(64)
+        self._ck(self.L.pa_shared_alloc(self.ctx, nbytes, C.byref(own), handle))
+        handles = [handle.raw]
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw)
+        ptrs = (C.c_void_p * world)()
+        for r in range(world):
+            if r == rank:
+                ptrs[r] = own.value
+            else:
+                pp = C.c_void_p()
+                self._ck(self.L.pa_shared_open(self.ctx, C.create_string_buffer(handles[r], 64), C.byref(pp)))
+                ptrs[r] = pp.value
+        self._xc_keep = (own, ptrs)
+        self._ck(self.L.pa_exchange_init(self.ctx, rank, world, ptrs, max_rows))
+        if world > 1:
+            dist.barrier()   # nobody writes into a buffer that is not mapped yet
+
+    def decode_exchange(self, li: int, items, q: torch.Tensor, gate: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                        q_head_stride: int | None = None, gate_head_stride: int | None = None) -> torch.Tensor:
+        """decode() over this rank's shard, merged across the ranks inside the combine kernel (peer stores + flags)."""
+        total = sum(it[2] for it in items)
+        if out is None:
+            out = torch.empty((total, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_decode_exchange(self.layers[li], self._items(items), len(items), self._p(q), _dt(q.dtype), q.stride(0),
+                                           q_head_stride or self.cfg.head_dim, gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
+        return out

@@ -420,14 +420,20 @@ static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, Item
 }
 
 static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
-                       uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false) {
+                       uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false,
+                       bool exchange = false) {
   pa_ctx* ctx = L->ctx;
   if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
   if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
   DecodeParams p{};
   uint32_t total_cols, max_rows, max_cols; uint64_t kv_bytes;
   // partial records may come from a shard that holds only part (or none) of the rows the columns see
-  if (int rc = build_items(L, items, n_items, &p.items, &total_cols, &max_rows, &max_cols, &kv_bytes, who, partial != nullptr)) return rc;
+  if (int rc = build_items(L, items, n_items, &p.items, &total_cols, &max_rows, &max_cols, &kv_bytes, who, partial != nullptr || exchange)) return rc;
+  if (exchange) {
+    if (!ctx->xc.world) return fail(ctx, PA_EINVAL, "%s: call pa_exchange_init first", who);
+    if ((uint64_t)total_cols * ctx->cfg.n_heads > ctx->xc.max_rows)
+      return fail(ctx, PA_EUNSUPPORTED, "%s: %u query rows exceed the %u rows of the exchange buffers", who, total_cols * ctx->cfg.n_heads, ctx->xc.max_rows);
+  }
   cudaSetDevice(ctx->device);
   const uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols);
   p.q = q; p.q_f16 = q_dtype == PA_F16; p.q_col_stride = qcs; p.q_head_stride = qhs;
@@ -459,6 +465,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   c.gate = gate; c.gate_col_stride = gcs; c.gate_head_stride = ghs; c.out = out; c.out_col_stride = ocs;
   c.act_f16 = ctx->cfg.act_dtype == PA_F16;
   c.partial_out = partial; c.partial_rows = (uint64_t)total_cols * ctx->cfg.n_heads;
+  c.exchange = exchange ? 1 : 0; c.xc = ctx->xc; c.err = ctx->dev_err;
   c.items = p.items; c.n_items = n_items;
   if (!ctx->core_only) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
   ctx->stats.kernel_launches += ctx->core_only ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
@@ -496,6 +503,7 @@ extern "C" int pa_merge(pa_ctx* ctx, const float* parts, uint32_t n_parts, uint3
   c.n_heads = ctx->cfg.n_heads; c.fixed_parts = n_parts; c.n_splits = 1;
   c.gate = gate; c.gate_col_stride = gate_col_stride; c.gate_head_stride = gate_head_stride; c.out = out; c.out_col_stride = out_col_stride;
   c.act_f16 = ctx->cfg.act_dtype == PA_F16;
+  c.err = ctx->dev_err;
   CU_TRY(ctx, launch_combine((int)hd, c, (uint32_t)rows, (cudaStream_t)stream));
   ctx->stats.kernel_launches++;
   return PA_OK;
@@ -686,4 +694,59 @@ extern "C" int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uin
   }
   CU_TRY(ctx, cudaMemcpyAsync(out, dout, (size_t)n_layers * out_layer_stride * es, cudaMemcpyDeviceToHost, st));
   return pa_sync(ctx, stream);
+}
+
+// ------------------------------------------------------------------------------ peer exchange --
+
+extern "C" size_t pa_exchange_bytes(pa_ctx* ctx, uint32_t world, uint32_t max_rows) {
+  if (!ctx || world < 1 || world > 8 || max_rows < 1) return 0;
+  const size_t blk = (size_t)max_rows * (ctx->cfg.head_dim + 2) * 4;
+  return 2 * (size_t)world * blk + 2 * (size_t)world * max_rows * (ctx->cfg.head_dim / 64) * 4;
+}
+
+extern "C" int pa_shared_alloc(pa_ctx* ctx, size_t bytes, void** dev_ptr, void* ipc_handle_out) {
+  if (!ctx || !dev_ptr || !ipc_handle_out || !bytes) return PA_EINVAL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "ipc handle size");
+  cudaSetDevice(ctx->device);
+  if (cudaMalloc(dev_ptr, bytes) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_shared_alloc: %zu bytes do not fit on the device", bytes); }
+  CU_TRY(ctx, cudaMemset(*dev_ptr, 0, bytes));
+  CU_TRY(ctx, cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(ipc_handle_out), *dev_ptr));
+  return PA_OK;
+}
+extern "C" int pa_shared_open(pa_ctx* ctx, const void* ipc_handle, void** dev_ptr) {
+  if (!ctx || !ipc_handle || !dev_ptr) return PA_EINVAL;
+  cudaSetDevice(ctx->device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle, sizeof h);
+  cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ECUDA, "pa_shared_open: cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e)); }
+  return PA_OK;
+}
+extern "C" int pa_shared_close(pa_ctx* ctx, void* dev_ptr) {
+  if (!ctx) return PA_EINVAL;
+  cudaSetDevice(ctx->device);
+  cudaIpcCloseMemHandle(dev_ptr);
+  return PA_OK;
+}
+extern "C" int pa_exchange_init(pa_ctx* ctx, uint32_t rank, uint32_t world, void* const* bufs, uint32_t max_rows) {
+  if (!ctx || !bufs || world < 1 || world > 8 || rank >= world || max_rows < 1) return fail(ctx, PA_EINVAL, "pa_exchange_init: bad rank / world (1..8) / buffers");
+  cudaSetDevice(ctx->device);
+  ExchangeView x{};
+  for (uint32_t r = 0; r < world; ++r) { if (!bufs[r]) return fail(ctx, PA_EINVAL, "pa_exchange_init: null buffer of rank %u", r); x.peer[r] = (float*)bufs[r]; }
+  x.world = world; x.rank = rank; x.max_rows = max_rows; x.hd = ctx->cfg.head_dim;
+  if (!ctx->xc.ctr) {
+    if (cudaMalloc(&x.ctr, 8) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_exchange_init: out of device memory"); }
+  } else x.ctr = ctx->xc.ctr;
+  CU_TRY(ctx, cudaMemset(x.ctr, 0, 8));
+  ctx->xc = x;
+  return PA_OK;
+}
+extern "C" int pa_decode_exchange(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t q_col_stride,
+                                  uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride, uint64_t gate_head_stride, void* out,
+                                  uint64_t out_col_stride, void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  if (!out) return fail(L->ctx, PA_EINVAL, "pa_decode_exchange: null out");
+  return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
+                     (cudaStream_t)stream, "pa_decode_exchange", false, true);
 }

@@ -142,6 +142,16 @@ struct ItemList {
   uint32_t col0[kMaxItems];    // first column of the item in q / gate / out
 };
 
+// Peer exchange of merged (o, m, l) records between the GPUs of one box.  Every rank owns one buffer that all ranks
+// (itself included) write into with plain stores over NVLink; peer[r] is rank r's buffer as seen from this GPU.
+// Layout of a buffer, in floats, for parity p in {0,1} and source rank s: block (p * world + s) of max_rows * (hd + 2)
+// floats (o rows first, then (m, l) pairs); after all blocks, one uint32 flag per (p, s, row, 64-dim slice).
+struct ExchangeView {
+  float* peer[8];
+  uint32_t world, rank, max_rows, hd;
+  unsigned int* ctr;   // local: [0] call counter (epoch), [1] CTA ticket of the running launch
+};
+
 }  // namespace pa
 
 struct pa_ctx {
@@ -161,6 +171,7 @@ struct pa_ctx {
   void* stage_dev = nullptr;     // device staging of the host-buffer entry point
   void* stage_host = nullptr;    // pinned staging
   size_t stage_bytes = 0;
+  pa::ExchangeView xc{};         // peer exchange (pa_exchange_init); world == 0: not set up
   std::vector<cudaEvent_t> ev;   // timing: event pairs around core-kernel launches
   size_t ev_used = 0;
   bool timing = false;

@@ -479,12 +479,71 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   }
   s_acc[grp][ln] = acc;
   __syncthreads();
+  __shared__ float s_xm[8], s_xl[8];
+  __shared__ unsigned int s_epoch;
+  float t = 0.f;
   if (tid < 64) {
     const float* sa = reinterpret_cast<const float*>(s_acc);
-    float t = sa[tid];
+    t = sa[tid];
 #pragma unroll
     for (int i = 1; i < 16; ++i) t += sa[i * 64 + tid];
-    const uint32_t d = slice * 64 + tid;
+  }
+  const uint32_t d = slice * 64 + tid;
+  if (p.exchange) {
+    // ---- publish this rank's record slice to every rank, wait for theirs, merge across ranks ----
+    const ExchangeView& x = p.xc;
+    const uint32_t n_slices = HD / 64;
+    if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(x.ctr);
+    __syncthreads();
+    const uint32_t epoch = s_epoch, parity = epoch & 1u, tag = epoch + 1u;
+    const size_t blk = (size_t)x.max_rows * (HD + 2);
+    const size_t flags_off = (size_t)2 * x.world * blk;      // in floats (= uint32 words)
+    for (uint32_t r = 0; r < x.world; ++r) {
+      float* dst = x.peer[r] + (size_t)(parity * x.world + x.rank) * blk;
+      if (tid < 64) dst[(size_t)prow * HD + d] = t;
+      if (slice == 0 && tid == 64) { dst[(size_t)x.max_rows * HD + prow * 2] = M; dst[(size_t)x.max_rows * HD + prow * 2 + 1] = Lsum; }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < x.world) {
+      // one flag per (source rank, row, slice) in the destination's buffer: the record slice above is complete
+      unsigned int* f = reinterpret_cast<unsigned int*>(x.peer[tid] + flags_off) + ((size_t)(parity * x.world + x.rank) * x.max_rows + prow) * n_slices + slice;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tag) : "memory");
+    }
+    if (tid < x.world) {
+      // wait (bounded) for source rank `tid`: its slice of this row, and slice 0 of this row, which carries (m, l)
+      const unsigned int* fl = reinterpret_cast<const unsigned int*>(x.peer[x.rank] + flags_off) + ((size_t)(parity * x.world + tid) * x.max_rows + prow) * n_slices;
+      bool ok = false;
+      for (uint32_t it = 0; it < (1u << 22); ++it) {
+        unsigned int a, b;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(a) : "l"(fl + slice) : "memory");
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(b) : "l"(fl) : "memory");
+        if (a == tag && b == tag) { ok = true; break; }
+        if (it > 32) __nanosleep(64);
+      }
+      if (!ok) atomicMax(p.err, 7u);   // a peer never published: report and carry on
+      const float* src = x.peer[x.rank] + (size_t)(parity * x.world + tid) * blk + (size_t)x.max_rows * HD + prow * 2;
+      s_xm[tid] = __ldcg(src); s_xl[tid] = __ldcg(src + 1);
+    }
+    __syncthreads();
+    if (tid < 64) {
+      float Mg = -3.0e38f;
+      for (uint32_t r = 0; r < x.world; ++r) Mg = fmaxf(Mg, s_xm[r]);
+      float Lg = 0.f, og = 0.f;
+      for (uint32_t r = 0; r < x.world; ++r) {
+        const float w = __expf(s_xm[r] - Mg);
+        Lg += s_xl[r] * w;
+        og += __ldcg(x.peer[x.rank] + (size_t)(parity * x.world + r) * blk + (size_t)prow * HD + d) * w;
+      }
+      t = og; Lsum = Lg;
+    }
+    // the last CTA of the launch advances the call counter (every CTA read it before any CTA could get here last)
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(x.ctr + 1, 1u) == gridDim.x * gridDim.y - 1) { x.ctr[1] = 0; __threadfence(); atomicAdd(x.ctr, 1u); }
+    }
+  }
+  if (tid < 64) {
     if (p.partial_out) {
       p.partial_out[(uint64_t)prow * HD + d] = t;
       if (d == 0) {

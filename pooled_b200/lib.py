@@ -64,6 +64,12 @@ SYMBOLS = {
     "pa_decode": (_i, [_vp, C.POINTER(PaItem), _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_decode_partial": (_i, [_vp, C.POINTER(PaItem), _u32, _vp, _i, _u64, _u64, _vp, _vp]),
     "pa_merge": (_i, [_vp, _vp, _u32, _u32, _vp, _u64, _u64, _vp, _u64, _vp]),
+    "pa_exchange_bytes": (_sz, [_vp, _u32, _u32]),
+    "pa_shared_alloc": (_i, [_vp, _sz, C.POINTER(_vp), _vp]),
+    "pa_shared_open": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "pa_shared_close": (_i, [_vp, _vp]),
+    "pa_exchange_init": (_i, [_vp, _u32, _u32, C.POINTER(_vp), _u32]),
+    "pa_decode_exchange": (_i, [_vp, C.POINTER(PaItem), _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_prefill": (_i, [_vp, _u32, _u32, _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_sigmoid_mul": (_i, [_vp, _vp, _u64, _vp, _u64, _u64, _u32, _vp]),
     "pa_attn_layer": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),

@@ -38,8 +38,10 @@ class ShardedDecoder:
     merge() with AttnEngine's signatures; `dist` is torch.distributed (or a stand-in with all_gather_into_tensor).
     Every position stays global: the engine's layers are told which global row their cache starts at."""
 
-    def __init__(self, engine, plan: ShardPlan, rank: int, dist, group=None):
-        self.eng, self.plan, self.rank, self.dist, self.group = engine, plan, rank, dist, group
+    def __init__(self, engine, plan: ShardPlan, rank: int, dist, group=None, exchange: str = "nccl"):
+        """exchange: "nccl" (all-gather of the record blocks, then pa_merge) or "peer" (pa_decode_exchange: the combine
+        kernel itself stores the records into every rank's buffer over NVLink and merges; needs engine.exchange_setup)."""
+        self.eng, self.plan, self.rank, self.dist, self.group, self.exchange = engine, plan, rank, dist, group, exchange
         for li in range(engine.cfg.n_layers):
             engine.set_origin(li, rank * plan.chunk)
 
@@ -55,6 +57,8 @@ class ShardedDecoder:
             else:
                 q_rot.append(eng.rope(q[i:i + 1], eng.cfg.n_heads, pos))
         q_rot = q_rot[0] if n == 1 else _cat(q_rot)
+        if self.exchange == "peer":
+            return eng.decode_exchange(li, [(seq, pos, 1) for seq, pos in seqs_pos], q_rot, gate, out)
         part = eng.decode_partial(li, [(seq, pos, 1) for seq, pos in seqs_pos], q_rot)
         if plan.world == 1:
             return eng.merge(part[None], n, gate, out)

@@ -275,3 +275,24 @@ def test_host_buffer_entry_points_match_the_device_path():
     one = torch.empty((2, nH * hd), dtype=torch.float16).pin_memory()
     eng.encode_layer_host(1, ctx, hq[1], hk[1], hv[1], hg[1], one, mode="decode")
     assert torch.equal(one, want[1])
+
+
+def test_exchange_merge_with_one_rank_matches_decode_over_many_calls():
+    # the peer-exchange combine with world = 1 (the rank publishes to and reads from its own buffer): the call counter,
+    # the two buffer parities and the flags are exercised by consecutive calls of different sizes
+    import torch
+    nH, nKV, hd, ctx = 16, 2, 256, 5000
+    eng = _engine(nH, nKV, hd, ctx + 8, act="f32", rope_mode="none", max_cols=8)
+    q, K, V, g = _config_inputs(11, nH, nKV, hd, ctx + 8, 4)
+    Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+    util.load_cache(eng, 0, 0, Kc, Vc)
+    eng.exchange_setup(0, 1, max_rows=64)
+    qd, gd = util.torch_dev(q), util.torch_dev(g)
+    for pos, nc in [(4999, 1), (100, 4), (4096, 2), (63, 1), (4999, 1), (2000, 3)]:
+        want = eng.decode(0, [(0, pos, nc)], qd[:nc], gd[:nc]).cpu().numpy()
+        got = eng.decode_exchange(0, [(0, pos, nc)], qd[:nc], gd[:nc]).cpu().numpy()
+        eng.sync()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"pos {pos} nc {nc}"
+    from pooled_b200 import PaError
+    with pytest.raises(PaError):
+        eng.decode_exchange(0, [(0, 100, 8)], torch.zeros((8, nH * hd), device="cuda"))   # 128 rows > max_rows 64

@@ -1,0 +1,61 @@
+"""KV-sequence-sharded decode over two GPUs with the merge fused into the combine kernel (peer stores over NVLink +
+flags), against the float64 oracle.  Needs two GPUs: skipped elsewhere."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import po
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, ret):
+    import torch
+    import torch.distributed as dist
+    from pooled_b200 import AttnConfig, AttnEngine
+    from pooled_b200.shard import ShardPlan, ShardedDecoder
+    from tests import util
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        nH, nKV, hd, chunk, steps = 16, 2, 256, 4096, 6
+        total = chunk + 1000                       # rank 0 holds 4096 rows, rank 1 holds 1000 and grows
+        K = util.normal_f16(1, (total + steps, nKV * hd)); V = util.normal_f16(2, (total + steps, nKV * hd))
+        Kc, Vc = po.np_f16_rne(K), po.np_f16_rne(V)
+        eng = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=64, rope_theta=1e7, max_seq=chunk, act_dtype=torch.float16), device=rank)
+        eng.exchange_setup(rank, world, dist, max_rows=64)
+        errs = []
+        for mode in ("peer", "nccl"):
+            sd = ShardedDecoder(eng, ShardPlan(world, chunk), rank, dist, exchange=mode)
+            lo, hi = rank * chunk, min(total, (rank + 1) * chunk)
+            eng.cache(0, "k")[0, :hi - lo] = torch.from_numpy(Kc[lo:hi].view(np.int16)).cuda()
+            eng.cache(0, "v")[0, :hi - lo] = torch.from_numpy(Vc[lo:hi].view(np.int16)).cuda()
+            Kf, Vf = Kc[:total].copy(), Vc[:total].copy()
+            for t in range(steps):
+                pos = total + t
+                q = util.normal_f16(100 + t, (1, nH * hd)); g = util.normal_f16(200 + t, (1, nH * hd))
+                d = lambda a: torch.from_numpy(a).to(torch.float16).cuda()
+                out = sd.step(0, [(0, pos)], d(q), d(K[pos:pos + 1]), d(V[pos:pos + 1]), d(g)).float().cpu().numpy()
+                eng.sync()
+                Kf = np.concatenate([Kf, po.f16_rne(po.rope_neox_f64(K[pos], nKV, hd, 64, pos, 1e7))[None]])
+                Vf = np.concatenate([Vf, Vc[pos][None]])
+                ref = po.attn_f64(po.rope_neox_f64(q[0], nH, hd, 64, pos, 1e7)[None], Kf, Vf, nH, nKV, hd, pos, 1, g)
+                errs.append(float(np.abs(out - ref).max()))
+        ret[rank] = max(errs)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sharded_decode_peer_and_nccl():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert set(ret.keys()) == {0, 1} and max(ret.values()) <= 2e-3, dict(ret)
