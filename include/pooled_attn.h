@@ -198,6 +198,15 @@ PA_API int pa_decode_exchange(pa_layer* layer, const pa_item* items, uint32_t n_
                               uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
                               uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);
 
+/* pa_attn_layer for a KV-sequence shard (pa_layer_set_origin + pa_exchange_init): RoPE on q everywhere, append of
+ * k / v on the rank whose shard holds the new positions, decode over the local rows, cross-GPU merge and gate inside
+ * the combine kernel.  Same call, same order, on every rank. */
+PA_API int pa_attn_layer_sharded(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q,
+                                 uint64_t q_col_stride, uint64_t q_head_stride, const void* k, const void* v,
+                                 uint64_t kv_col_stride, const void* gate, uint64_t gate_col_stride,
+                                 uint64_t gate_head_stride, const float* cs_table, void* out, uint64_t out_col_stride,
+                                 void* stream);
+
 /* Tiled causal prefill of n_cols columns of one sequence starting at pos (their K/V already appended).
  * Replaces attn_flash_tile + attn_combine_tile + sigmoid_mul_mc (engine/wgsl/attn_tile.js:108-193,
  * engine/wgsl/qwen35.js:877-887) as dispatched by _encAttnCore (engine/qwen35.js:2489-2493, :2516). */

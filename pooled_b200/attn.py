@@ -342,3 +342,16 @@ class AttnEngine:
         self._ck(self.L.pa_decode_exchange(self.layers[li], self._items(items), len(items), self._p(q), _dt(q.dtype), q.stride(0),
                                            q_head_stride or self.cfg.head_dim, gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
         return out
+
+    def encode_layer_sharded(self, li: int, pos: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor | None = None,
+                             out: torch.Tensor | None = None, seq: int = 0, q_head_stride: int | None = None, gate_head_stride: int | None = None,
+                             cs_table: torch.Tensor | None = None) -> torch.Tensor:
+        """encode_layer on a KV-sequence shard: one C-ABI call per layer; the owner of the new rows appends, every rank
+        decodes its rows, the combine kernel merges across the ranks (needs set_origin and exchange_setup)."""
+        n_cols = q.shape[0]
+        if out is None:
+            out = torch.empty((n_cols, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_attn_layer_sharded(self.layers[li], seq, pos, n_cols, self._p(q), q.stride(0), q_head_stride or self.cfg.head_dim,
+                                              self._p(k), self._p(v), k.stride(0), gp, gcs, ghs, self._p(cs_table), self._p(out), out.stride(0), self._st()))
+        return out

@@ -575,11 +575,20 @@ extern "C" int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const
 
 static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t qcs, uint64_t qhs, const void* k,
                       const void* v, uint64_t kvcs, const void* gate, uint64_t gcs, uint64_t ghs, const float* cs_table, void* out, uint64_t ocs,
-                      cudaStream_t st) {
+                      cudaStream_t st, bool sharded = false) {
   pa_ctx* ctx = L->ctx;
   if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer: null q, k, v or out");
-  if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer")) return rc;
+  if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer", !sharded)) return rc;
   cudaSetDevice(ctx->device);
+  if (sharded) {
+    // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
+    const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
+    if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
+                                  owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st))
+      return rc;
+    pa_item it{seq, pos, n_cols, 0};
+    return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true);
+  }
   // the decode / verify kernel carries at most 64 query rows per kv head; wider passes are prefill chunks
   // (the reference takes the tiled kernel on full-width non-verify passes, engine/qwen35.js:2489)
   const bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
@@ -749,4 +758,14 @@ extern "C" int pa_decode_exchange(pa_layer* L, const pa_item* items, uint32_t n_
   if (!out) return fail(L->ctx, PA_EINVAL, "pa_decode_exchange: null out");
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
                      (cudaStream_t)stream, "pa_decode_exchange", false, true);
+}
+
+extern "C" int pa_attn_layer_sharded(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t q_col_stride,
+                                     uint64_t q_head_stride, const void* k, const void* v, uint64_t kv_col_stride, const void* gate,
+                                     uint64_t gate_col_stride, uint64_t gate_head_stride, const float* cs_table, void* out, uint64_t out_col_stride,
+                                     void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  return layer_impl(L, seq, pos, n_cols, PA_MODE_DECODE, q, q_col_stride, q_head_stride, k, v, kv_col_stride, gate, gate_col_stride, gate_head_stride,
+                    cs_table, out, out_col_stride, (cudaStream_t)stream, true);
 }

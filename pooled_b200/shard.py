@@ -50,6 +50,8 @@ class ShardedDecoder:
         on every rank (the projections are replicated).  Returns out [n_seqs, q_dim] on every rank."""
         eng, plan = self.eng, self.plan
         n = len(seqs_pos)
+        if self.exchange == "peer" and n == 1:      # one sequence: the whole layer step is one library call
+            return eng.encode_layer_sharded(li, seqs_pos[0][1], q, k, v, gate, out, seq=seqs_pos[0][0])
         q_rot = []
         for i, (seq, pos) in enumerate(seqs_pos):
             if plan.owner(pos) == self.rank:   # this rank owns the new row: rotate q and k, append k and v
