@@ -496,33 +496,31 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(x.ctr);
     __syncthreads();
     const uint32_t epoch = s_epoch, parity = epoch & 1u, tag = epoch + 1u;
-    const size_t blk = (size_t)x.max_rows * (HD + 2);
-    const size_t flags_off = (size_t)2 * x.world * blk;      // in floats (= uint32 words)
+    const size_t blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // o rows, then (m, l) per (row, slice)
+    const size_t flags_off = (size_t)2 * x.world * blk;            // in floats (= uint32 words)
+    const size_t ml_off = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + slice) * 2;
     for (uint32_t r = 0; r < x.world; ++r) {
       float* dst = x.peer[r] + (size_t)(parity * x.world + x.rank) * blk;
       if (tid < 64) dst[(size_t)prow * HD + d] = t;
-      if (slice == 0 && tid == 64) { dst[(size_t)x.max_rows * HD + prow * 2] = M; dst[(size_t)x.max_rows * HD + prow * 2 + 1] = Lsum; }
+      if (tid == 64) { dst[ml_off] = M; dst[ml_off + 1] = Lsum; }
     }
-    __threadfence_system();
     __syncthreads();
     if (tid < x.world) {
-      // one flag per (source rank, row, slice) in the destination's buffer: the record slice above is complete
+      // one flag per (source rank, row, slice) in the destination's buffer.  The release store at system scope orders
+      // the CTA's record stores (which this thread observed through the barrier) before the flag.
       unsigned int* f = reinterpret_cast<unsigned int*>(x.peer[tid] + flags_off) + ((size_t)(parity * x.world + x.rank) * x.max_rows + prow) * n_slices + slice;
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tag) : "memory");
-    }
-    if (tid < x.world) {
-      // wait (bounded) for source rank `tid`: its slice of this row, and slice 0 of this row, which carries (m, l)
-      const unsigned int* fl = reinterpret_cast<const unsigned int*>(x.peer[x.rank] + flags_off) + ((size_t)(parity * x.world + tid) * x.max_rows + prow) * n_slices;
+      // wait (bounded) for source rank `tid`'s slice of this row
+      const unsigned int* fl = reinterpret_cast<const unsigned int*>(x.peer[x.rank] + flags_off) + ((size_t)(parity * x.world + tid) * x.max_rows + prow) * n_slices + slice;
       bool ok = false;
       for (uint32_t it = 0; it < (1u << 22); ++it) {
-        unsigned int a, b;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(a) : "l"(fl + slice) : "memory");
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(b) : "l"(fl) : "memory");
-        if (a == tag && b == tag) { ok = true; break; }
-        if (it > 32) __nanosleep(64);
+        unsigned int a;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(a) : "l"(fl) : "memory");
+        if (a == tag) { ok = true; break; }
+        if (it > 4096) __nanosleep(64);
       }
       if (!ok) atomicMax(p.err, 7u);   // a peer never published: report and carry on
-      const float* src = x.peer[x.rank] + (size_t)(parity * x.world + tid) * blk + (size_t)x.max_rows * HD + prow * 2;
+      const float* src = x.peer[x.rank] + (size_t)(parity * x.world + tid) * blk + ml_off;
       s_xm[tid] = __ldcg(src); s_xl[tid] = __ldcg(src + 1);
     }
     __syncthreads();
