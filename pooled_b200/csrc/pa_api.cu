@@ -19,6 +19,7 @@ cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
+cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
 }  // namespace pa
 
 using namespace pa;
@@ -454,8 +455,25 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   }
 #endif
   const int nt = (int)ceil_div(max_cols * ctx->G, 8);
+  // One sequence with more than 8 query rows per kv head (a k-token verify block) goes to the tensor-core split-K
+  // kernel; single tokens and batches of sequences stay on the streaming mma.sync kernel.
+  const bool verify_tc = n_items == 1 && nt > 1 && max_rows > 0 && !getenv("POOLED_ATTN_VERIFY_MMA_SYNC");
+  CUtensorMap tm_k, tm_v;
+  PrefillParams vp{};
+  if (verify_tc) {
+    const uint64_t seq_off = (uint64_t)items[0].seq * L->max_seq * ctx->kv_dim;
+    if (int rc = make_cache_map(ctx, &tm_k, L->k + seq_off, max_rows, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
+    if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, max_rows, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
+    vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs;
+    vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
+    vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
+    vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
+    const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
+    if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);
+  }
   timing_mark(ctx, st, 0);
-  if (max_rows > 0) CU_TRY(ctx, launch_decode(L, p, dim3(ns, ctx->cfg.n_kv_heads, n_items), nt, st));
+  if (verify_tc) CU_TRY(ctx, launch_verify(L, vp, tm_k, tm_v, ctx->cfg.n_kv_heads, st));
+  else if (max_rows > 0) CU_TRY(ctx, launch_decode(L, p, dim3(ns, ctx->cfg.n_kv_heads, n_items), nt, st));
   timing_mark(ctx, st, 1);
   CombineParams c{};
   c.o = ctx->part_o; c.ml = ctx->part_ml;

@@ -59,6 +59,8 @@ struct PrefillParams {
   uint32_t seq, pos, n_cols, n_heads, G, max_seq;
   float scale_log2;
   uint32_t* err;
+  // split-K form (k-token verify on the tensor cores): one CTA per (split, kv head), rows = columns x heads of the group
+  float* part_o; float* part_ml; uint32_t n_splits; int32_t lim0; uint32_t n_rows, col0;
   unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
 };
 

@@ -161,15 +161,23 @@ __device__ __forceinline__ void umma_commit_elected(uint32_t leader, uint32_t ba
       ::"r"(bar), "r"(leader) : "memory");
 }
 
-constexpr int kStages = 3;   // K ring and V ring depth
-
 constexpr int kSBuf = 3;     // S / P tiles in tensor memory: S(j+2) is formed while softmax(j) runs and P(j-1) is consumed
 
-template <int HD>
+// MODE 0: causal prefill, one CTA per (128 query columns, q head).
+// MODE 1 / 2: split-K form for a k-token verify block: one CTA per (split of the KV sequence, kv head); the rows of the
+//   tile are (column, head of the GQA group) pairs, at most 64 of them, and the CTA writes an unnormalised (o, m, l)
+//   partial per row for the LSE combine.  MODE 2 keeps about 22 bits of q and of the softmax weights at no extra
+//   tensor work: rows 0..63 carry the f16 high parts (q_hi, P_hi), rows 64..127 the low parts (q_lo, P_lo) of the same
+//   query rows; S_hi + S_lo is formed in the softmax, O_hi + O_lo in the epilogue.
+constexpr int kXStride = 65;   // floats per row of the hi/lo exchange buffer (odd: no bank conflicts)
+
+template <int HD, int MODE>
 struct PfSmem {
+  static constexpr int NSTG = MODE == 2 ? 2 : 3;    // K ring and V ring depth
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
   static constexpr int QS_BYTES = HD * 128;         // upper half of the head dims of Q: [HD/128][128 rows][128 B]
-  static constexpr int OFF_K = 0, OFF_V = kStages * KV_BYTES, OFF_Q = 2 * kStages * KV_BYTES, OFF_BAR = OFF_Q + QS_BYTES;
+  static constexpr int X_BYTES = MODE == 2 ? 2 * kBM * kXStride * 4 : 0;   // S rows swapped between the hi and lo halves
+  static constexpr int OFF_K = 0, OFF_V = NSTG * KV_BYTES, OFF_Q = 2 * NSTG * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
   static constexpr int TOTAL = 1024 + OFF_BAR + 256;
   // tensor memory columns: lower half of Q (HD/4: f16 pairs) | S0 S1 S2 (64 each; P overwrites the first 32 of
   // its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
@@ -177,11 +185,13 @@ struct PfSmem {
   static constexpr int TMEM_COLS = 512;
 };
 
-template <int HD>
+template <int HD, int MODE>
 __global__ void __launch_bounds__(kPfThreads, 1)
 pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
-  using L = PfSmem<HD>;
+  using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
+  constexpr bool SK = MODE != 0, PREC = MODE == 2;
+  constexpr int kStages = L::NSTG;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
@@ -193,12 +203,19 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t q_tile = gridDim.x - 1 - blockIdx.x;   // longest rows first
-  const uint32_t h = blockIdx.y, g = h / p.G;
+  // prefill: q tile (longest rows first) x q head.  split-K: split x kv head.
+  const uint32_t q_tile = gridDim.x - 1 - blockIdx.x;
+  const uint32_t h = blockIdx.y, g = SK ? blockIdx.y : h / p.G;
   const uint32_t c0 = q_tile * kBM;
-  const uint32_t rows_valid = min((uint32_t)kBM, p.n_cols - c0);
+  const uint32_t rows_valid = SK ? 0u : min((uint32_t)kBM, p.n_cols - c0);
   const uint32_t p0 = p.pos + c0;                       // cache row of column c0's own token
-  const uint32_t n_tiles = (p0 + rows_valid + kBN - 1) / kBN;
+  uint32_t tile0 = 0, n_tiles = (p0 + rows_valid + kBN - 1) / kBN;
+  if (SK) {
+    const uint32_t tiles = (p.n_rows + kBN - 1) / kBN, tps = (tiles + p.n_splits - 1) / p.n_splits;
+    tile0 = blockIdx.x * tps;
+    if (tile0 >= tiles) return;                         // this split holds no row (uniform for the CTA)
+    n_tiles = min(tiles, tile0 + tps) - tile0;
+  }
   if (warp == 4) PTR(0);
 
   if (warp == 1 && lane == 0) {
@@ -232,7 +249,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
-        tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)(j * kBN), (int)(g * CH), BAR(K_FULL, st));
+        tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(K_FULL, st));
       }
     }
   } else if (warp == 3) {
@@ -245,7 +262,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
-        tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)(j * kBN), (int)(g * CH), BAR(V_FULL, st));
+        tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(V_FULL, st));
       }
     }
   } else if (warp == 1) {
@@ -270,7 +287,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         mbar_wait(BAR(K_FULL, st), (j / kStages) & 1, s_err, WAIT_KFULL);
         tc_fence_after();
         if (j < 10) PTR(91 + 3 * j);
-        const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[2]);
+        const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[kStages - 1]);
         const uint32_t ts = t_s0 + sb * kBN;
         // lower half of the head dims: Q from tensor memory; upper half: Q from shared memory
 #pragma unroll
@@ -298,7 +315,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         mbar_wait(BAR(V_FULL, st), (j / kStages) & 1, s_err, WAIT_VFULL);
         tc_fence_after();
         if (j < 10) PTR(132 + 3 * j);
-        const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[2]);
+        const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[kStages - 1]);
         const uint32_t tp = t_s0 + sb * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s tile
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
@@ -312,10 +329,16 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ softmax + epilogue ----
     const uint32_t qd = warp - 4, row = qd * 32 + lane;
     const uint32_t lane_addr = (qd * 32) << 16;
-    // ---- this thread's Q row -> tensor memory as packed f16 pairs (rows past the chunk are zero) ----
+    // split-K: rows 0..63 are (column, head-of-group) pairs; with MODE 2 rows 64..127 repeat them for the low parts
+    const bool is_lo = SK && row >= 64;
+    const uint32_t lr = SK ? (row & 63u) : row;
+    const uint32_t sk_c = lr / p.G, sk_hh = lr % p.G;
+    const uint32_t head = SK ? g * p.G + sk_hh : h;
+    const bool live = SK ? (lr < p.n_cols * p.G && (PREC || !is_lo)) : row < rows_valid;
+    float* x_s = reinterpret_cast<float*>(base + L::OFF_X);
+    // ---- this thread's Q row -> f16 pairs: lower half of the dims to tensor memory, upper half to shared memory ----
     {
-      const bool live = row < rows_valid;
-      const uint64_t off = (uint64_t)(c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)h * p.q_head_stride;
+      const uint64_t off = (uint64_t)(SK ? p.col0 + (live ? sk_c : 0) : c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)head * p.q_head_stride;
 #pragma unroll 1
       for (int c = 0; c < HD / 64; ++c) {          // 64 elements per step: 32 TMEM columns, or one 128-byte row chunk
         uint32_t w[32];
@@ -323,14 +346,18 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c * 64);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const uint4 x = live ? src[i] : make_uint4(0, 0, 0, 0);
+            const uint4 x = (live && !is_lo) ? src[i] : make_uint4(0, 0, 0, 0);     // f16 q has no low part
             w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
           }
         } else {
           const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c * 64);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float4 x = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 x = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (is_lo) {   // what the f16 high part leaves over
+              x.x -= __half2float(__float2half_rn(x.x)); x.y -= __half2float(__float2half_rn(x.y));
+              x.z -= __half2float(__float2half_rn(x.z)); x.w -= __half2float(__float2half_rn(x.w));
+            }
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
@@ -349,10 +376,11 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mbar_arrive(BAR(Q_FULL, 0));
     }
     if (warp == 4) PTR(1);
-    const uint32_t lim = p0 + row + 1;      // keys [0, lim) are visible to this row
-    float m_st = -INFINITY, l_sum = 0.f;
+    // keys [0, lim) are visible to this row
+    const uint32_t lim = SK ? (uint32_t)min(max(p.lim0 + (int32_t)min(sk_c, p.n_cols - 1), 0), (int32_t)p.n_rows) : p0 + row + 1;
+    float m_st = SK ? -1.0e30f : -INFINITY, l_sum = 0.f;   // split-K: a split may hold no visible key of a row
     for (uint32_t j = 0; j < n_tiles; ++j) {
-      const uint32_t b = j % kSBuf, u = j / kSBuf, kv0 = j * kBN;
+      const uint32_t b = j % kSBuf, u = j / kSBuf, kv0 = (tile0 + j) * kBN;
       mbar_wait(BAR(S_FULL, b), u & 1, s_err, WAIT_MMA);
       tc_fence_after();
       if (warp == 4 && j < 10) PTR(8 + 6 * j);
@@ -363,6 +391,16 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         tmem_ld32(t_s0 + b * kBN + 32 + lane_addr, t1);
 #pragma unroll
         for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
+      }
+      if (PREC) {
+        // S = S_hi + S_lo: the two halves of a query row swap their score rows through shared memory
+        float* xb = x_s + (j & 1) * (kBM * kXStride);
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) xb[row * kXStride + i] = s[i];
+        named_bar_sync(1, 128);
+        const float* xp = xb + (row ^ 64u) * kXStride;
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) s[i] += xp[i];
       }
       if (warp == 4 && j < 10) PTR(9 + 6 * j);
       // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
@@ -376,9 +414,9 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mt *= p.scale_log2;
       float alpha = 1.f;
       bool grow = false;
-      if (j == 0) m_st = mt;                        // key 0 is visible to every row, so mt is finite
+      if (!SK && j == 0) m_st = mt;                 // key 0 is visible to every row, so mt is finite
       else if (mt > m_st + 8.f) { alpha = ex2_approx(m_st - mt); m_st = mt; l_sum *= alpha; grow = true; }
-      if (__any_sync(0xffffffffu, grow)) {
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // O must not change under the previous P V: wait for it, then rescale this warp's 32 rows in TMEM
         const uint32_t jb = (j - 1) % kSBuf, ju = (j - 1) / kSBuf;
         mbar_wait(BAR(PV_DONE, jb), ju & 1, s_err, WAIT_MMA);
@@ -398,8 +436,9 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       float ls = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float e0 = ex2_approx(fmaf(s[2 * i], p.scale_log2, -m_st)), e1 = ex2_approx(fmaf(s[2 * i + 1], p.scale_log2, -m_st));
+        float e0 = ex2_approx(fmaf(s[2 * i], p.scale_log2, -m_st)), e1 = ex2_approx(fmaf(s[2 * i + 1], p.scale_log2, -m_st));
         ls += e0 + e1;
+        if (is_lo) { e0 -= __half2float(__float2half_rn(e0)); e1 -= __half2float(__float2half_rn(e1)); }
         pw[i] = pack_h2(e0, e1);
       }
       l_sum += ls;
@@ -416,6 +455,34 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (warp == 4) PTR(2);
     const float inv_l = 1.f / l_sum;
     const uint32_t col = c0 + row;
+    if (SK) {
+      // unnormalised partial (o, m, l) of this split for the LSE combine; MODE 2 adds the low-part rows' O first
+      const uint64_t prow = (uint64_t)(p.col0 + sk_c) * p.n_heads + head;
+      const uint64_t slot = prow * p.n_splits + blockIdx.x;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        float o[32];
+        tmem_ld32(t_o + c * 32 + lane_addr, o);
+        if (PREC) {
+          if (is_lo) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x_s[lr * kXStride + i] = o[i];
+          }
+          named_bar_sync(1, 128);
+          if (!is_lo) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] += x_s[lr * kXStride + i];
+          }
+          named_bar_sync(1, 128);
+        }
+        if (live && !is_lo) {
+          float4* dst = reinterpret_cast<float4*>(p.part_o + slot * HD + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+      }
+      if (live && !is_lo) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
+    } else {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
       float o[32];
@@ -444,6 +511,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         }
       }
     }
+    }
     tc_fence_before();
     if (warp == 4) PTR(3);
   }
@@ -457,26 +525,31 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
 int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ctx->cfg.head_dim == 128; }
 
+template <int HD, int MODE>
+static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, dim3 grid, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  const int dev = L->ctx->device & 63;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(pa_prefill_kernel<HD, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<HD, MODE>::TOTAL);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  pa_prefill_kernel<HD, MODE><<<grid, kPfThreads, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, p);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
   const dim3 grid((p.n_cols + kBM - 1) / kBM, p.n_heads);
-  static bool attr_set[64][2] = {};
-  const int dev = L->ctx->device & 63;
-  if (L->ctx->cfg.head_dim == 256) {
-    if (!attr_set[dev][0]) {
-      cudaError_t e = cudaFuncSetAttribute(pa_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<256>::TOTAL);
-      if (e != cudaSuccess) return e;
-      attr_set[dev][0] = true;
-    }
-    pa_prefill_kernel<256><<<grid, kPfThreads, PfSmem<256>::TOTAL, st>>>(tm_k, tm_v, p);
-  } else {
-    if (!attr_set[dev][1]) {
-      cudaError_t e = cudaFuncSetAttribute(pa_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<128>::TOTAL);
-      if (e != cudaSuccess) return e;
-      attr_set[dev][1] = true;
-    }
-    pa_prefill_kernel<128><<<grid, kPfThreads, PfSmem<128>::TOTAL, st>>>(tm_k, tm_v, p);
-  }
-  return cudaGetLastError();
+  return L->ctx->cfg.head_dim == 256 ? launch_pf<256, 0>(L, p, tm_k, tm_v, grid, st) : launch_pf<128, 0>(L, p, tm_k, tm_v, grid, st);
+}
+
+// k-token verify block (more than 8 query rows per kv head) on the tensor cores: split-K form of the same kernel
+cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st) {
+  const dim3 grid(p.n_splits, n_kv);
+  const bool precise = !(L->ctx->cfg.flags & PA_FLAG_FAST);
+  if (L->ctx->cfg.head_dim == 256)
+    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, grid, st);
+  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, grid, st);
 }
 
 }  // namespace pa
