@@ -173,11 +173,11 @@ constexpr int kXStride = 65;   // floats per row of the hi/lo exchange buffer (o
 
 template <int HD, int MODE>
 struct PfSmem {
-  static constexpr int NSTG = MODE == 2 ? 2 : 3;    // K ring and V ring depth
+  static constexpr int NK = 3, NV = MODE == 2 ? 2 : 3;   // K ring and V ring depth (the scores run two tiles ahead)
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
   static constexpr int QS_BYTES = HD * 128;         // upper half of the head dims of Q: [HD/128][128 rows][128 B]
-  static constexpr int X_BYTES = MODE == 2 ? 2 * kBM * kXStride * 4 : 0;   // S rows swapped between the hi and lo halves
-  static constexpr int OFF_K = 0, OFF_V = NSTG * KV_BYTES, OFF_Q = 2 * NSTG * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
+  static constexpr int X_BYTES = MODE == 2 ? kBM * kXStride * 4 : 0;   // S rows swapped between the hi and lo halves
+  static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
   static constexpr int TOTAL = 1024 + OFF_BAR + 256;
   // tensor memory columns: lower half of Q (HD/4: f16 pairs) | S0 S1 S2 (64 each; P overwrites the first 32 of
   // its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
@@ -191,7 +191,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
   constexpr bool SK = MODE != 0, PREC = MODE == 2;
-  constexpr int kStages = L::NSTG;
+  constexpr int NK = L::NK, NV = L::NV;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
@@ -220,10 +220,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
   if (warp == 1 && lane == 0) {
     *s_err = 0;
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(BAR(K_FULL, i), 1); mbar_init(BAR(K_EMPTY, i), 1);
-      mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1);
-    }
+    for (int i = 0; i < NK; ++i) { mbar_init(BAR(K_FULL, i), 1); mbar_init(BAR(K_EMPTY, i), 1); }
+    for (int i = 0; i < NV; ++i) { mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1); }
     for (int i = 0; i < kSBuf; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
     mbar_init(BAR(Q_FULL, 0), 128);
@@ -245,7 +243,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (lane == 0) {
       prefetch_tmap(&tm_k);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t st = j % kStages, u = j / kStages;
+        const uint32_t st = j % NK, u = j / NK;
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
@@ -258,7 +256,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (lane == 0) {
       prefetch_tmap(&tm_v);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t st = j % kStages, u = j / kStages;
+        const uint32_t st = j % NV, u = j / NV;
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
@@ -272,22 +270,21 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
       // Both A operands live in tensor memory (Q for the whole CTA, P per tile), so a k-step costs shared-memory
       // bandwidth for the K or V slice only.  B descriptors are built once; a k-step adds a byte offset (>> 4).
-      uint64_t k_desc[kStages], v_desc[kStages];
+      uint64_t k_desc[NK], v_desc[NV];
 #pragma unroll
-      for (int i = 0; i < kStages; ++i) {
-        k_desc[i] = smem_desc(smem_u32(base + L::OFF_K + i * L::KV_BYTES), 16, 1024);
-        v_desc[i] = smem_desc(smem_u32(base + L::OFF_V + i * L::KV_BYTES), kBN * 128, 1024);
-      }
+      for (int i = 0; i < NK; ++i) k_desc[i] = smem_desc(smem_u32(base + L::OFF_K + i * L::KV_BYTES), 16, 1024);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v_desc[i] = smem_desc(smem_u32(base + L::OFF_V + i * L::KV_BYTES), kBN * 128, 1024);
       const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
       mbar_wait(BAR(Q_FULL, 0), 0, s_err, WAIT_QFULL);
       tc_fence_after();
       auto issue_qk = [&](uint32_t j) {
-        const uint32_t sb = j % kSBuf, st = j % kStages;
+        const uint32_t sb = j % kSBuf, st = j % NK;
         if (j < 10) PTR(90 + 3 * j);
-        mbar_wait(BAR(K_FULL, st), (j / kStages) & 1, s_err, WAIT_KFULL);
+        mbar_wait(BAR(K_FULL, st), (j / NK) & 1, s_err, WAIT_KFULL);
         tc_fence_after();
         if (j < 10) PTR(91 + 3 * j);
-        const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[kStages - 1]);
+        const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[NK - 1]);
         const uint32_t ts = t_s0 + sb * kBN;
         // lower half of the head dims: Q from tensor memory; upper half: Q from shared memory
 #pragma unroll
@@ -307,15 +304,15 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       issue_qk(0);
       if (n_tiles > 1) issue_qk(1);
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t sb = j % kSBuf, st = j % kStages;
+        const uint32_t sb = j % kSBuf, st = j % NV;
         if (j + 2 < n_tiles) issue_qk(j + 2);
         if (j < 10) PTR(130 + 3 * j);
         mbar_wait(BAR(P_FULL, sb), (j / kSBuf) & 1, s_err, WAIT_QFULL);
         if (j < 10) PTR(131 + 3 * j);
-        mbar_wait(BAR(V_FULL, st), (j / kStages) & 1, s_err, WAIT_VFULL);
+        mbar_wait(BAR(V_FULL, st), (j / NV) & 1, s_err, WAIT_VFULL);
         tc_fence_after();
         if (j < 10) PTR(132 + 3 * j);
-        const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[kStages - 1]);
+        const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[NV - 1]);
         const uint32_t tp = t_s0 + sb * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s tile
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
@@ -394,13 +391,13 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       }
       if (PREC) {
         // S = S_hi + S_lo: the two halves of a query row swap their score rows through shared memory
-        float* xb = x_s + (j & 1) * (kBM * kXStride);
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) xb[row * kXStride + i] = s[i];
+        for (int i = 0; i < kBN; ++i) x_s[row * kXStride + i] = s[i];
         named_bar_sync(1, 128);
-        const float* xp = xb + (row ^ 64u) * kXStride;
+        const float* xp = x_s + (row ^ 64u) * kXStride;
 #pragma unroll
         for (int i = 0; i < kBN; ++i) s[i] += xp[i];
+        named_bar_sync(1, 128);   // everyone has read before the next tile's rows are written
       }
       if (warp == 4 && j < 10) PTR(9 + 6 * j);
       // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
