@@ -435,12 +435,15 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="sharded decode (N > 1): merge inside the combine kernel over peer memory, or NCCL all-gather + merge kernel")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling captures)")
+    ap.add_argument("--ctx", type=int, default=0, help="override the decode workloads' context length (scaling probes)")
     ap.add_argument("--cols", type=int, default=0, help="override the prompt length of the prefill workload (small profiling captures)")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the decode kernel, if known")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.layers > 0:
         w["layers"] = args.layers
+    if args.ctx > 0 and args.workload != "c3":
+        w["ctx"] = args.ctx
     if args.cols > 0 and args.workload == "c3":
         w["n_cols"] = args.cols
     if args.impl == "reference":

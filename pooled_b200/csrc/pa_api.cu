@@ -436,7 +436,8 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
       return fail(ctx, PA_EUNSUPPORTED, "%s: %u query rows exceed the %u rows of the exchange buffers", who, total_cols * ctx->cfg.n_heads, ctx->xc.max_rows);
   }
   cudaSetDevice(ctx->device);
-  const uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols);
+  uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols);
+  if (n_items == 1 && max_cols * ctx->G > 8) { const uint32_t fit = (uint32_t)(ctx->part_slots / (2ull * total_cols * ctx->cfg.n_heads)); if (ns > fit) ns = fit; if (ns > 256) ns = 256; if (ns < 1) ns = 1; }
   p.q = q; p.q_f16 = q_dtype == PA_F16; p.q_col_stride = qcs; p.q_head_stride = qhs;
   p.part_o = ctx->part_o; p.part_ml = ctx->part_ml; p.n_splits = ns;
   p.n_heads = ctx->cfg.n_heads; p.G = ctx->G; p.max_seq = L->max_seq;
@@ -477,8 +478,11 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   timing_mark(ctx, st, 1);
   CombineParams c{};
   c.o = ctx->part_o; c.ml = ctx->part_ml;
-  c.o_row_stride = (uint64_t)ns * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
-  c.ml_row_stride = (uint64_t)ns * 2; c.ml_part_stride = 2;
+  const bool lo_rec = verify_tc && !(ctx->cfg.flags & PA_FLAG_FAST);   // the hi/lo verify kernel writes two records per split
+  const uint32_t rs = lo_rec ? 2 * ns : ns;
+  c.lo_records = lo_rec ? 1 : 0;
+  c.o_row_stride = (uint64_t)rs * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
+  c.ml_row_stride = (uint64_t)rs * 2; c.ml_part_stride = 2;
   c.n_heads = ctx->cfg.n_heads; c.fixed_parts = 0; c.n_splits = ns;
   c.gate = gate; c.gate_col_stride = gcs; c.gate_head_stride = ghs; c.out = out; c.out_col_stride = ocs;
   c.act_f16 = ctx->cfg.act_dtype == PA_F16;

@@ -436,6 +436,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     const uint32_t n_rows = p.items.n_rows[it];
     const uint32_t tiles = (n_rows + kT - 1) / kT, tps = (tiles + p.n_splits - 1) / p.n_splits;
     ns = tiles ? (tiles + tps - 1) / tps : 0;   // a shard that holds no row of the item: an empty record
+    if (p.lo_records) ns *= 2;
   }
   const float* ml = p.ml + prow * p.ml_row_stride;
   float m0 = -3.0e38f, l0 = 0.f, m1 = -3.0e38f, l1 = 0.f;

@@ -453,32 +453,24 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const float inv_l = 1.f / l_sum;
     const uint32_t col = c0 + row;
     if (SK) {
-      // unnormalised partial (o, m, l) of this split for the LSE combine; MODE 2 adds the low-part rows' O first
+      // unnormalised partial (o, m, l) of this split for the LSE combine.  MODE 2: the low-part rows write a record of
+      // their own right after the used splits' records, with the same m and l = 0: the combine adds its o with the
+      // same weight and nothing to the denominator, which is exactly O_hi + O_lo.
       const uint64_t prow = (uint64_t)(p.col0 + sk_c) * p.n_heads + head;
-      const uint64_t slot = prow * p.n_splits + blockIdx.x;
+      const uint32_t tiles_all = (p.n_rows + kBN - 1) / kBN, tps_all = (tiles_all + p.n_splits - 1) / p.n_splits;
+      const uint32_t used = (tiles_all + tps_all - 1) / tps_all;
+      const uint64_t slot = prow * (PREC ? 2 * p.n_splits : p.n_splits) + (is_lo ? used : 0) + blockIdx.x;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         float o[32];
         tmem_ld32(t_o + c * 32 + lane_addr, o);
-        if (PREC) {
-          if (is_lo) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x_s[lr * kXStride + i] = o[i];
-          }
-          named_bar_sync(1, 128);
-          if (!is_lo) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] += x_s[lr * kXStride + i];
-          }
-          named_bar_sync(1, 128);
-        }
-        if (live && !is_lo) {
+        if (live) {
           float4* dst = reinterpret_cast<float4*>(p.part_o + slot * HD + c * 32);
 #pragma unroll
           for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
       }
-      if (live && !is_lo) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
+      if (live) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = is_lo ? 0.f : l_sum; }
     } else {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
