@@ -210,16 +210,24 @@ def run_ours(args, w):
     st1 = eng.stats()
     n_launch = launches_per_step * args.steps if launches_per_step is not None else st1["kernel_launches"] - st0["kernel_launches"]
     # The dominant kernel alone.  Single-sequence steps: the same K steps with only the core kernel of every layer
-    # launched, back to back, between one CUDA-event pair (a pair around each 10-20 us launch would time the launch
-    # gap as well).  Batched / sharded steps: an event pair around every core launch.
+    # launched (a CUDA graph of `layers` core launches, replayed K times), back to back, between one CUDA-event pair (a
+    # pair around each 10-20 us launch would time the launch gap as well).  Batched / sharded steps: an event pair around every core launch.
     if not sharded and n_seqs == 1:
         eng.set_core_only(True)
-        for _ in range(3):
+        cs2 = torch.cuda.Stream(device=dev)
+        cs2.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(cs2):
             step()
+            core_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(core_graph, stream=cs2):     # host launch cost (~15 us per eager call) would hide a 10 us kernel
+                step()
+        torch.cuda.current_stream(dev).wait_stream(cs2)
+        for _ in range(3):
+            core_graph.replay()
         torch.cuda.synchronize()
         e0.record()
         for _ in range(args.steps):
-            step()
+            core_graph.replay()
         e1.record()
         torch.cuda.synchronize()
         core_ms, core_n = e0.elapsed_time(e1), layers * args.steps

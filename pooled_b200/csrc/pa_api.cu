@@ -468,6 +468,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs;
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
+    vp.prefetch_old_rows = after_own_append ? 1u : 0u;
     vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);

@@ -62,6 +62,7 @@ struct PrefillParams {
   uint32_t* err;
   // split-K form (k-token verify on the tensor cores): one CTA per (split, kv head), rows = columns x heads of the group
   float* part_o; float* part_ml; uint32_t n_splits; int32_t lim0; uint32_t n_rows, col0;
+  uint32_t prefetch_old_rows;   // split-K form: K/V tiles wholly below the call's new rows may be fetched before the predecessor ends
   unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
 };
 

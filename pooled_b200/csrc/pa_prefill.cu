@@ -232,7 +232,11 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     tmem_relinquish();
     tc_fence_before();
   }
-  pdl_wait();   // q (and, for a chunked prefill, the appended rows) come from the kernel before this one
+  // q, and the rows the RoPE/append kernel before this one writes, may only be touched after pdl_wait(); in the
+  // split-K form the producers may fetch older K/V tiles ahead of it when the caller allows
+  const bool early = SK && p.prefetch_old_rows;
+  const uint32_t old_rows = SK ? p.n_rows - min(p.n_rows, p.n_cols) : 0u;
+  if (!early) pdl_wait();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
@@ -242,8 +246,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ TMA producer, K ----
     if (lane == 0) {
       prefetch_tmap(&tm_k);
+      bool waited = !early;
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NK, u = j / NK;
+        if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
@@ -255,8 +261,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // (its own thread: behind the K loads in one loop, K(j+1) would wait for the V slot that P V (j-1) still reads)
     if (lane == 0) {
       prefetch_tmap(&tm_v);
+      bool waited = !early;
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NV, u = j / NV;
+        if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
@@ -327,6 +335,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t qd = warp - 4, row = qd * 32 + lane;
     const uint32_t lane_addr = (qd * 32) << 16;
     // split-K: rows 0..63 are (column, head-of-group) pairs; with MODE 2 rows 64..127 repeat them for the low parts
+    if (early) pdl_wait();
+    pdl_trigger();
     const bool is_lo = SK && row >= 64;
     const uint32_t lr = SK ? (row & 63u) : row;
     const uint32_t sk_c = lr / p.G, sk_hh = lr % p.G;
@@ -523,8 +533,11 @@ static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CU
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  pa_prefill_kernel<HD, MODE><<<grid, kPfThreads, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, p);
-  return cudaGetLastError();
+  if (MODE == 0) {
+    pa_prefill_kernel<HD, MODE><<<grid, kPfThreads, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, p);
+    return cudaGetLastError();
+  }
+  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(kPfThreads), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, p);
 }
 
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
