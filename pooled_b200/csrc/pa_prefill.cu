@@ -346,21 +346,26 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ---- this thread's Q row -> f16 pairs: lower half of the dims to tensor memory, upper half to shared memory ----
     {
       const uint64_t off = (uint64_t)(SK ? p.col0 + (live ? sk_c : 0) : c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)head * p.q_head_stride;
+      // 128 elements per round (the loads of a round are all in flight together): rounds below HD/2 go to tensor
+      // memory (64 columns), the others to shared memory (two 128-byte row chunks)
 #pragma unroll 1
-      for (int c = 0; c < HD / 64; ++c) {          // 64 elements per step: 32 TMEM columns, or one 128-byte row chunk
-        uint32_t w[32];
+      for (int c2 = 0; c2 < HD / 128; ++c2) {
+        uint32_t w[64];
         if (p.q_f16) {
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c * 64);
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c2 * 128);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const uint4 x = (live && !is_lo) ? src[i] : make_uint4(0, 0, 0, 0);     // f16 q has no low part
             w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
           }
         } else {
-          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c * 64);
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c2 * 128);
+          float4 xs[32];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float4 x = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int i = 0; i < 32; ++i) xs[i] = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float4 x = xs[i];
             if (is_lo) {   // what the f16 high part leaves over
               x.x -= __half2float(__float2half_rn(x.x)); x.y -= __half2float(__float2half_rn(x.y));
               x.z -= __half2float(__float2half_rn(x.z)); x.w -= __half2float(__float2half_rn(x.w));
@@ -368,13 +373,20 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
-        if (c < HD / 128) {
-          tmem_st32u(t_q + c * 32 + lane_addr, w);
-        } else {
-          uint8_t* dst = q_s + (c - HD / 128) * (kBM * 128) + row * 128;
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<uint4*>(dst + ((i ^ (row & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        for (int hc = 0; hc < 2; ++hc) {
+          const int c = 2 * c2 + hc;
+          uint32_t wc[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) wc[i] = w[32 * hc + i];
+          if (c < HD / 128) {
+            tmem_st32u(t_q + c * 32 + lane_addr, wc);
+          } else {
+            uint8_t* dst = q_s + (c - HD / 128) * (kBM * 128) + row * 128;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint4*>(dst + ((i ^ (row & 7)) << 4)) = make_uint4(wc[4 * i], wc[4 * i + 1], wc[4 * i + 2], wc[4 * i + 3]);
+          }
         }
       }
       fence_proxy_async();
