@@ -163,6 +163,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   if (half) {
     double host[128];
     for (uint32_t i = 0; i < half; ++i) host[i] = pow(cfg->rope_theta, -(2.0 * (double)i) / (double)cfg->n_rot);
+    memcpy(ctx->inv_freq_host, host, half * sizeof(double));
     if ((e = cudaMalloc(&ctx->inv_freq, half * sizeof(double))) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(inv_freq)", e);
     if ((e = cudaMemcpy(ctx->inv_freq, host, half * sizeof(double), cudaMemcpyHostToDevice)) != cudaSuccess) return bail(PA_ECUDA, "cudaMemcpy(inv_freq)", e);
   }
@@ -345,6 +346,22 @@ static int check_cols(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   return PA_OK;
 }
 
+#ifdef PA_TRACE
+// Development builds: one region of 256 CTAs x 256 timestamp slots per decode call, 32 regions in rotation, never
+// cleared (a replayed graph leaves the timestamps of its last replay).  Rows 0..159 decode CTAs, 160..223 combine
+// CTAs, 224..255 RoPE/append CTAs of the same layer call.
+static unsigned g_trace_call = 0;
+static unsigned long long* trace_region(unsigned call) {
+  static unsigned long long* tr = nullptr;
+  if (!tr) {
+    cudaMalloc(&tr, 32ull * 256 * 256 * 8);
+    cudaMemset(tr, 0, 32ull * 256 * 256 * 8);
+    if (getenv("PA_TRACE_PTR")) { FILE* f = fopen(getenv("PA_TRACE_PTR"), "w"); fprintf(f, "%llu\n", (unsigned long long)(uintptr_t)tr); fclose(f); }
+  }
+  return tr + (size_t)(call % 32) * 256 * 256;
+}
+#endif
+
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
                             uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
                             uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0) {
@@ -356,6 +373,9 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
   p.hd = ctx->cfg.head_dim; p.n_rot = ctx->cfg.n_rot; p.pos = pos; p.mode = mode; p.in_f16 = in_f16;
   p.inv_freq = ctx->inv_freq; p.cs_table = cs_table;
   if (mode == PA_ROPE_TABLE && !cs_table) return fail(ctx, PA_EINVAL, "rope: PA_ROPE_TABLE needs a cos/sin table");
+#ifdef PA_TRACE
+  if (n_cols == 1) p.trace = trace_region(g_trace_call);   // the decode call that follows takes the same region
+#endif
   CU_TRY(ctx, launch_rope_append(p, n_cols, st));
   ctx->stats.kernel_launches++;
   return PA_OK;
@@ -420,9 +440,13 @@ static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, Item
   return PA_OK;
 }
 
+
+// the token's unrotated k / v row for the fused front of the decode kernel
+struct FusedFront { const void* k; const void* v; bool append; uint32_t pos; };
+
 static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false,
-                       bool exchange = false) {
+                       bool exchange = false, const FusedFront* fz = nullptr) {
   pa_ctx* ctx = L->ctx;
   if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
   if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
@@ -446,14 +470,20 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   // after this library's own RoPE/append kernel the only rows in flux are the call's new ones: older rows may be
   // fetched while that kernel still runs
   p.prefetch_old_rows = after_own_append ? 1u : 0u;
-#ifdef PA_TRACE
   {
-    static unsigned long long* tr = nullptr;
-    if (!tr) cudaMalloc(&tr, 1024 * 256 * 8);
-    cudaMemsetAsync(tr, 0, 1024 * 256 * 8, st);
-    p.trace = tr;
-    if (getenv("PA_TRACE_PTR")) { FILE* f = fopen(getenv("PA_TRACE_PTR"), "w"); fprintf(f, "%llu\n", (unsigned long long)(uintptr_t)tr); fclose(f); }
+    static const int env_pre = getenv("POOLED_ATTN_PRE_STAGES") ? atoi(getenv("POOLED_ATTN_PRE_STAGES")) : -1;
+    p.pre_stages = env_pre >= 0 ? (uint32_t)env_pre : 2u;
   }
+  if (fz) {
+    p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
+    p.k_cache = L->k; p.v_cache = L->v;
+    for (uint32_t i = 0; i < 32; ++i) {
+      const double ang = (double)fz->pos * ctx->inv_freq_host[i];
+      p.rope_cs[i] = cos(ang); p.rope_cs[32 + i] = sin(ang);
+    }
+  }
+#ifdef PA_TRACE
+  p.trace = trace_region(g_trace_call++);
 #endif
   const int nt = (int)ceil_div(max_cols * ctx->G, 8);
   // One sequence with more than 8 query rows per kv head (a k-token verify block) goes to the tensor-core split-K
@@ -479,6 +509,9 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   timing_mark(ctx, st, 1);
   CombineParams c{};
   c.o = ctx->part_o; c.ml = ctx->part_ml;
+#ifdef PA_TRACE
+  c.trace = p.trace;
+#endif
   const bool lo_rec = verify_tc && !(ctx->cfg.flags & PA_FLAG_FAST);   // the hi/lo verify kernel writes two records per split
   const uint32_t rs = lo_rec ? 2 * ns : ns;
   c.lo_records = lo_rec ? 1 : 0;
@@ -596,6 +629,14 @@ extern "C" int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const
 
 // ------------------------------------------------------------------------------ one call --
 
+// One token of a partial-RoPE model (64 rotated dims, head_dim 256, at most 8 heads per kv head): the rotation of
+// q and k and the append ride inside the decode kernel (attn_glue_kv folded into attn_dec, in the reference's terms).
+static bool can_fuse_front(const pa_ctx* ctx, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs, const void* k, const void* v) {
+  const uint32_t nr = ctx->cfg.n_rot;
+  return !ctx->core_only && n_cols == 1 && ctx->cfg.rope_mode == PA_ROPE_F64 && ctx->cfg.head_dim == 256 && ctx->G <= 8 && nr == 64 &&
+         !(qcs & 1) && !(qhs & 1) && !((uintptr_t)q & 7) && !((uintptr_t)k & 7) && !((uintptr_t)v & 7) && !getenv("POOLED_ATTN_NO_FUSE");
+}
+
 static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t qcs, uint64_t qhs, const void* k,
                       const void* v, uint64_t kvcs, const void* gate, uint64_t gcs, uint64_t ghs, const float* cs_table, void* out, uint64_t ocs,
                       cudaStream_t st, bool sharded = false) {
@@ -606,6 +647,11 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   if (sharded) {
     // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
     const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
+    if (can_fuse_front(ctx, n_cols, q, qcs, qhs, k, v)) {
+      FusedFront fz{k, v, owns, pos};
+      pa_item it{seq, pos, 1, 0};
+      return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true, &fz);
+    }
     if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
                                   owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st))
       return rc;
@@ -615,6 +661,11 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // the decode / verify kernel carries at most 64 query rows per kv head; wider passes are prefill chunks
   // (the reference takes the tiled kernel on full-width non-verify passes, engine/qwen35.js:2489)
   const bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
+  if (!prefill && can_fuse_front(ctx, n_cols, q, qcs, qhs, k, v)) {
+    FusedFront fz{k, v, true, pos};
+    pa_item it{seq, pos, 1, 0};
+    return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", true, false, &fz);
+  }
   // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic)
   if (!ctx->core_only)
     if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,

@@ -4,6 +4,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <atomic>
+#include <cstdlib>
 #include <stdint.h>
 
 #include <string>
@@ -123,8 +125,28 @@ __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) 
 constexpr int kMaxItems = 32;     // items of one batched decode call
 constexpr int kMaxRows = 64;      // query rows (columns x heads of one kv head) one decode CTA carries
 
+// The small kernels of a layer ask for the largest shared-memory carveout although they need little of it: an SM
+// changes its carveout only when idle, so a decode CTA (about 205 KB) launched ahead of its predecessor's end could
+// otherwise not join an SM that still runs one of their CTAs.  Asked once per kernel and device.
+static inline void prefer_max_carveout(const void* fn) {
+  static std::atomic<const void*> seen[16][16];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return;
+  for (int i = 0; i < 16; ++i) {
+    const void* cur = seen[dev][i].load(std::memory_order_acquire);
+    if (cur == fn) return;
+    if (cur == nullptr) {
+      static const bool off = getenv("POOLED_ATTN_NO_CARVEOUT") != nullptr;
+      if (!off) cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      seen[dev][i].store(fn, std::memory_order_release);
+      return;
+    }
+  }
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  if (smem == 0) prefer_max_carveout(reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -162,6 +184,7 @@ struct pa_ctx {
   pa_config cfg{};
   uint32_t G = 1, q_dim = 0, kv_dim = 0;
   double* inv_freq = nullptr;  // device: theta^(-2i/n_rot), i < n_rot/2, evaluated on the host in float64
+  double inv_freq_host[128] = {};   // the same table on the host
   float* q_rot = nullptr;      // device: rotated q of the current call, f32 [max_cols][q_dim]
   float* part_o = nullptr;     // device: split partials, f32 [rows][splits][head_dim] of the current call
   float* part_ml = nullptr;    // device: f32 [rows][splits][2]

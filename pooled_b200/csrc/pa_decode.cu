@@ -28,6 +28,11 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #else
 #define TR(slot) do {} while (0)
 #endif
+#ifdef PA_TRACE
+#define CTR(slot) do { if (p.trace && threadIdx.x == 0) p.trace[(160 + blockIdx.y * 16 + (blockIdx.x & 15)) * 256 + (slot)] = gtime(); } while (0)
+#else
+#define CTR(slot) do {} while (0)
+#endif
 
 constexpr int kT = 64;             // positions per tile
 constexpr int kConsumers = 128;    // 4 consumer warps
@@ -102,10 +107,15 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if ((uint32_t)row < live_rows) {
       const uint32_t c = row / G, hh = row % G;
       const uint64_t off = (uint64_t)(p.items.col0[item] + c) * p.q_col_stride + (uint64_t)(g * G + hh) * p.q_head_stride + d;
-      if (p.q_f16) x = __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(p.q) + off));
+      if (p.q_f16) x.x = __uint_as_float(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(p.q) + off));
       else x = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.q) + off);
     }
-    return x;
+    return x;   // f16 input: the two halves, unconverted, in x.x -- nothing here waits for the load to land
+  };
+  auto act_cvt = [&](float2 raw) {
+    if (!p.q_f16) return raw;
+    const uint32_t u = __float_as_uint(raw.x);
+    return __half22float2(*reinterpret_cast<const __half2*>(&u));
   };
   auto q_store = [&](int idx, float2 x) {
     const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
@@ -114,20 +124,54 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     *reinterpret_cast<__half2*>(q_hi + row * QP + d * 2) = __halves2half2(h0, h1);
     if (PRECISE) *reinterpret_cast<__half2*>(q_lo + row * QP + d * 2) = __halves2half2(l0, l1);
   };
+  // Fused front (one token, 64 rotated dims, head_dim 256): q arrives unrotated.  Thread t holds dims (2t, 2t + 1) of
+  // every row, so the rotary pairs (d, d + 32) of the first 64 dims sit in lanes l and l ^ 16 of warp 0: one shuffle
+  // brings the partner, and cos / sin of the float64 angle come with the launch parameters.  In the CTA that walks the
+  // sequence's last tile the same threads also carry the token's own k / v row: rotated, rounded to f16, stored to
+  // the cache, and kept in two registers to be placed into the tile the TMA fetched before (or while) it was stored.
+  constexpr bool CAN_FUSE = NT == 1 && HD == 256;
+  const bool fused = CAN_FUSE && p.fused;
+  const bool own_new = fused && p.append && tile1 == tiles;
+  float2 kx = make_float2(0.f, 0.f), vx = make_float2(0.f, 0.f);
+  uint32_t k_new2 = 0, v_new2 = 0;
+  auto rotate = [&](float2 x) {   // warp 0 only, all lanes
+    const float2 y = make_float2(__shfl_xor_sync(0xffffffffu, x.x, 16), __shfl_xor_sync(0xffffffffu, x.y, 16));
+    const int i = 2 * (lane & 15);
+    const double c0 = p.rope_cs[i], c1 = p.rope_cs[i + 1], s0 = p.rope_cs[32 + i], s1 = p.rope_cs[33 + i];
+    // first element of a pair (lanes 0-15): a cos - b sin; second: b cos + a sin -- own * cos -/+ partner * sin
+    const double sg = lane < 16 ? -1.0 : 1.0;
+    float2 o;
+    o.x = (float)__dadd_rn(__dmul_rn((double)x.x, c0), sg * __dmul_rn((double)y.x, s0));
+    o.y = (float)__dadd_rn(__dmul_rn((double)x.y, c1), sg * __dmul_rn((double)y.y, s1));
+    return o;
+  };
   if (warp < 4) {
     pdl_wait();      // q (and the partial buffers written at the end) belong to earlier kernels until here
     pdl_trigger();
+    TR(4);
     if (Q_IN_REGS) {
 #pragma unroll
       for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = q_load(tid + it * kConsumers);
+      if (own_new) {
+        const uint64_t so = (uint64_t)g * HD + 2 * tid;
+        if (p.q_f16) {
+          kx.x = __uint_as_float(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(p.k_new) + so));
+          vx.x = __uint_as_float(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(p.v_new) + so));
+        } else {
+          kx = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.k_new) + so);
+          vx = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.v_new) + so);
+        }
+      }
     } else {
 #pragma unroll 8
-      for (int it = 0; it < QLD; ++it) q_store(tid + it * kConsumers, q_load(tid + it * kConsumers));
+      for (int it = 0; it < QLD; ++it) q_store(tid + it * kConsumers, act_cvt(q_load(tid + it * kConsumers)));
     }
   }
-  // The producer warp sets up the barriers and goes; the consumers meet it at named barrier 2.  When the call may
-  // not fetch ahead of its predecessor, the producer also waits (named barrier 3) until the q loads are in flight:
-  // a q load issued behind the first 190 KB of K/V tiles of every SM would queue behind all of them.
+  // The producer warp sets up the barriers and goes; the consumers meet it at named barrier 2.  Named barrier 3
+  // tells the producer that the q loads are in flight: a q load issued behind 190 KB of K/V tiles per SM queues
+  // behind all of them at the memory controllers.  A call that may not fetch ahead of its predecessor waits there
+  // before its first tile; one that may fetches `pre_stages` tiles first and the rest after it, so that the early
+  // burst has drained by the time the small loads of the critical path (q here, the predecessor's last stores) go.
   if (warp == 4) {
     if (lane == 0) {
       *s_err = 0;
@@ -141,24 +185,31 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     __syncwarp();
     named_bar_arrive(2, kDecThreads);
-    if (!p.prefetch_old_rows) named_bar_sync(3, kDecThreads);
   } else {
-    if (!p.prefetch_old_rows) named_bar_arrive(3, kDecThreads);
+    named_bar_arrive(3, kDecThreads);
     named_bar_sync(2, kDecThreads);
   }
   TR(warp == 4 ? 128 : 1);
 
   if (warp == 4) {
     // ---------------------------------------------------------------- producer ----
+    // the whole warp walks the loop (named barrier 3 wants all of it); lane 0 issues
+    const uint32_t pre = p.prefetch_old_rows ? p.pre_stages : 0u;
+    const int y0 = (int)(p.items.seq[item] * p.max_seq + tile0 * kT);
+    const int z = (int)(g * CH);
+    const uint32_t old_rows = n_rows - min(n_rows, n_cols);   // rows below the ones this call's columns added
+    bool waited = !p.prefetch_old_rows;
     if (lane == 0) {
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
-      const int y0 = (int)(p.items.seq[item] * p.max_seq + tile0 * kT);
-      const int z = (int)(g * CH);
-      const uint32_t old_rows = n_rows - min(n_rows, n_cols);   // rows below the ones this call's columns added
-      bool waited = !p.prefetch_old_rows;
-      if (waited) pdl_wait();
-      for (uint32_t i = 0; i < n_tiles; ++i) {
+    }
+    for (uint32_t i = 0; i < n_tiles; ++i) {
+      if (i == pre) {
+        __syncwarp();
+        named_bar_sync(3, kDecThreads);
+        if (!p.prefetch_old_rows && lane == 0) pdl_wait();
+      }
+      if (lane == 0) {
         const uint32_t s = i % NS, ph = (i / NS) & 1;
         if (!waited && (tile0 + i + 1) * kT > old_rows) { pdl_wait(); waited = true; }
         mbar_wait(kempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
@@ -170,6 +221,9 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         mbar_expect_tx(vfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
       }
+    }
+    if (n_tiles <= pre) { __syncwarp(); named_bar_sync(3, kDecThreads); }   // keeps the barrier balanced
+    if (lane == 0) {
       if (*s_err) {
         // a wait ran out somewhere: let the copies still in flight land (bounded) before the CTA exits
         const uint32_t first = n_tiles > NS ? n_tiles - NS : 0;
@@ -189,7 +243,25 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
   if (Q_IN_REGS) {
 #pragma unroll
+    for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = act_cvt(qreg[it]);
+    if (own_new) { kx = act_cvt(kx); vx = act_cvt(vx); }
+    if (fused && w == 0) {
+#pragma unroll
+      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = rotate(qreg[it]);
+      if (own_new) kx = rotate(kx);
+    }
+#pragma unroll
     for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) q_store(tid + it * kConsumers, qreg[it]);
+    if (own_new) {
+      auto h16 = [](float x) -> uint32_t {   // round to nearest even; NaN -> sign | 0x7e00, as the append kernel
+        return x != x ? (((__float_as_uint(x) >> 16) & 0x8000u) | 0x7e00u) : (uint32_t)__half_as_ushort(__float2half_rn(x));
+      };
+      k_new2 = h16(kx.x) | (h16(kx.y) << 16);
+      v_new2 = h16(vx.x) | (h16(vx.y) << 16);
+      const uint64_t ro = ((uint64_t)p.items.seq[item] * p.max_seq + (n_rows - 1)) * ((uint64_t)gridDim.y * HD) + (uint64_t)g * HD + 2 * tid;
+      *reinterpret_cast<uint32_t*>(p.k_cache + ro) = k_new2;
+      *reinterpret_cast<uint32_t*>(p.v_cache + ro) = v_new2;
+    }
   }
 
   // causal limit of the two rows this thread owns in every 8-row group
@@ -216,6 +288,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   }
   named_bar_sync(1, kConsumers);   // q visible
   TR(2);
+  TR(5);
 
   const uint32_t q_hi_s = smem_u32(q_hi), q_lo_s = smem_u32(q_lo), p_hi_s = smem_u32(p_hi), p_lo_s = smem_u32(p_lo);
 
@@ -237,6 +310,11 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     mbar_wait(kfull + 8 * s, ph, s_err, WAIT_KFULL);
     if (i < 15) TR(8 + 8 * i);
+    if (own_new && i == n_tiles - 1) {
+      const uint32_t rr = n_rows - 1 - tile_pos, c16g = tid >> 2;
+      *reinterpret_cast<uint32_t*>(k_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = k_new2;
+      named_bar_sync(1, kConsumers);
+    }
     {
       const uint32_t krow = 16 * w + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll 4
@@ -335,6 +413,10 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (i < 15) TR(11 + 8 * i);
     mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
     if (i < 15) TR(12 + 8 * i);
+    if (own_new && i == n_tiles - 1) {   // made visible by the barrier below
+      const uint32_t rr = n_rows - 1 - tile_pos, c16g = tid >> 2;
+      *reinterpret_cast<uint32_t*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = v_new2;
+    }
     if (tile_pos + kT > n_rows) {
       // rows of the tile past the sequence end hold whatever the cache holds there (possibly NaN):
       // their weights are zero, but 0 * NaN is NaN, so clear them
@@ -417,9 +499,9 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
 // ------------------------------------------------------------------------------ combine --
 
-// grid (query rows, HD / 64): one CTA per (column, head, 64-dim slice).  Two memory round trips in all: every
-// thread fetches the (m, l) of up to two splits at once, then 16 groups of 16 lanes (a float4 each) walk the splits
-// 16 apart with four loads in flight per lane.  Every sum has a fixed order.
+// grid (query rows, HD / 64): one CTA per (column, head, 64-dim slice).  Every thread fetches the (m, l) of up to two
+// splits while 16 groups of 16 lanes (a float4 each) fetch the o records, splits 16 apart, eight loads in flight per
+// lane; the weights are applied when both have arrived.  Every sum has a fixed order.
 template <int HD>
 __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) {
   __shared__ float s_w[512];
@@ -427,8 +509,10 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   __shared__ float4 s_acc[16][16];
   const uint32_t prow = blockIdx.x, slice = blockIdx.y, col = prow / p.n_heads, h = prow % p.n_heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  CTR(0);
   pdl_wait();      // the partial records belong to the kernel before this one
   pdl_trigger();
+  CTR(1);
   uint32_t ns = p.fixed_parts;
   if (ns == 0) {
     uint32_t it = 0;
@@ -438,10 +522,27 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     ns = tiles ? (tiles + tps - 1) / tps : 0;   // a shard that holds no row of the item: an empty record
     if (p.lo_records) ns *= 2;
   }
+  // Everything the CTA reads is requested before the first use: the (m, l) pairs, the o records of the first 128
+  // splits (eight float4 per lane, splits 16 apart) and the gate value.  One memory round trip instead of three.
   const float* ml = p.ml + prow * p.ml_row_stride;
+  const int grp = tid >> 4, ln = tid & 15;
+  const float* ob = p.o + prow * p.o_row_stride + slice * 64 + ln * 4;
+  const uint32_t d = slice * 64 + tid;
+  float gv = 0.f;
+  const bool gated = p.gate && tid < 64 && !p.partial_out;
+  if (gated) {
+    const uint64_t go = (uint64_t)col * p.gate_col_stride + (uint64_t)h * p.gate_head_stride + d;
+    gv = p.act_f16 ? __half2float(reinterpret_cast<const __half*>(p.gate)[go]) : reinterpret_cast<const float*>(p.gate)[go];
+  }
   float m0 = -3.0e38f, l0 = 0.f, m1 = -3.0e38f, l1 = 0.f;
   if ((uint32_t)tid < ns) { m0 = ml[tid * p.ml_part_stride]; l0 = ml[tid * p.ml_part_stride + 1]; }
   if ((uint32_t)tid + 256 < ns) { m1 = ml[(tid + 256) * p.ml_part_stride]; l1 = ml[(tid + 256) * p.ml_part_stride + 1]; }
+  float4 x8[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint32_t s = grp + 16 * u;
+    x8[u] = s < ns ? *reinterpret_cast<const float4*>(ob + s * p.o_part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   float M = fmaxf(m0, m1);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
@@ -460,11 +561,16 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   float Lsum = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) Lsum += s_red2[i];
+  CTR(2);
 
-  const int grp = tid >> 4, ln = tid & 15;
-  const float* ob = p.o + prow * p.o_row_stride + slice * 64 + ln * 4;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (uint32_t s0 = grp; s0 < ns; s0 += 64) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint32_t s = grp + 16 * u;
+    const float wgt = s < ns ? s_w[s] : 0.f;
+    acc.x += x8[u].x * wgt; acc.y += x8[u].y * wgt; acc.z += x8[u].z * wgt; acc.w += x8[u].w * wgt;
+  }
+  for (uint32_t s0 = grp + 128; s0 < ns; s0 += 64) {
     float4 x[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -480,6 +586,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   }
   s_acc[grp][ln] = acc;
   __syncthreads();
+  CTR(3);
   __shared__ float s_xm[8], s_xl[8];
   __shared__ unsigned int s_epoch;
   float t = 0.f;
@@ -489,7 +596,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
 #pragma unroll
     for (int i = 1; i < 16; ++i) t += sa[i * 64 + tid];
   }
-  const uint32_t d = slice * 64 + tid;
   if (p.exchange) {
     // ---- publish this rank's record slice to every rank, wait for theirs, merge across ranks ----
     const ExchangeView& x = p.xc;
@@ -552,15 +658,12 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
       return;
     }
     float rv = t / Lsum;
-    if (p.gate) {
-      const uint64_t go = (uint64_t)col * p.gate_col_stride + (uint64_t)h * p.gate_head_stride + d;
-      const float gv = p.act_f16 ? __half2float(reinterpret_cast<const __half*>(p.gate)[go]) : reinterpret_cast<const float*>(p.gate)[go];
-      rv *= 1.0f / (1.0f + __expf(-gv));
-    }
+    if (gated) rv *= 1.0f / (1.0f + __expf(-gv));
     const uint64_t oo = (uint64_t)col * p.out_col_stride + (uint64_t)h * HD + d;
     if (p.act_f16) reinterpret_cast<__half*>(p.out)[oo] = __float2half_rn(rv);
     else reinterpret_cast<float*>(p.out)[oo] = rv;
   }
+  CTR(4);
 }
 
 // ------------------------------------------------------------------------------ launchers --

@@ -12,7 +12,14 @@ struct DecodeParams {
   float* part_ml;           // [rows][n_splits][2]   (m in natural-log units, l)
   uint32_t n_splits;
   uint32_t n_heads, G, max_seq, n_stages;
+  // fused front (one token, partial RoPE over 64 dims, head_dim 256): q arrives unrotated and the consumers rotate
+  // it; the CTA that walks the sequence's last tile also rotates k, converts v and appends the token's row
+  uint32_t fused, append;       // append: this cache holds the new row (false on another rank's shard)
+  const void* k_new; const void* v_new;               // the token's k / v row, [n_kv * hd], dtype as q
+  __half* k_cache; __half* v_cache;                   // caches of the layer
+  double rope_cs[64];       // cos (first 32) and sin of pos * theta^(-2i/64), evaluated by the host in float64
   uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends
+  uint32_t pre_stages;         // ... but only this many per CTA before the q loads are in flight
   float scale_log2;         // log2(e) / sqrt(head_dim)
   uint32_t* err;
   unsigned long long* trace;   // development builds only (PA_TRACE): per-CTA timestamps; nullptr otherwise
@@ -20,6 +27,7 @@ struct DecodeParams {
 };
 
 struct CombineParams {
+  unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
   const float* o;        // record s of row prow: o + prow * o_row_stride + s * o_part_stride, HD floats
   const float* ml;       // (m, l) of it:        ml + prow * ml_row_stride + s * ml_part_stride
   uint64_t o_row_stride, o_part_stride, ml_row_stride, ml_part_stride;
@@ -38,6 +46,7 @@ struct CombineParams {
 };
 
 struct RopeParams {
+  unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
   void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
   const void* k; const void* v; uint64_t kv_col_stride; uint32_t kv_heads;  // k == nullptr: skip
