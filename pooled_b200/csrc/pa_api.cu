@@ -364,9 +364,10 @@ static unsigned long long* trace_region(unsigned call) {
 
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
                             uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
-                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0) {
+                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false) {
   RopeParams p{};
   p.q_out_f16 = q_out_f16;
+  p.trigger_early = in_layer_call ? 1u : 0u;
   p.q = q; p.q_col_stride = qcs; p.q_head_stride = qhs; p.q_heads = q_heads; p.q_out = q_out; p.q_out_col_stride = q_out_cs;
   p.k = k; p.v = v; p.kv_col_stride = kvcs; p.kv_heads = ctx->cfg.n_kv_heads;
   if (L) { p.k_cache = L->k; p.v_cache = L->v; p.cache_row0 = (uint64_t)seq * L->max_seq + (pos - L->origin); }
@@ -378,6 +379,11 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
 #endif
   CU_TRY(ctx, launch_rope_append(p, n_cols, st));
   ctx->stats.kernel_launches++;
+  if (L && k) {
+    uint32_t r0 = pos - L->origin;
+    if (ctx->inflight_layer == L && ctx->inflight_row0 < r0) r0 = ctx->inflight_row0;
+    ctx->inflight_layer = L; ctx->inflight_row0 = r0;
+  }
   return PA_OK;
 }
 
@@ -470,6 +476,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   // after this library's own RoPE/append kernel the only rows in flux are the call's new ones: older rows may be
   // fetched while that kernel still runs
   p.prefetch_old_rows = after_own_append ? 1u : 0u;
+  p.early_limit = (after_own_append && ctx->inflight_layer == L) ? ctx->inflight_row0 : 0xffffffffu;
   {
     static const int env_pre = getenv("POOLED_ATTN_PRE_STAGES") ? atoi(getenv("POOLED_ATTN_PRE_STAGES")) : -1;
     p.pre_stages = env_pre >= 0 ? (uint32_t)env_pre : 2u;
@@ -498,7 +505,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs;
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
-    vp.prefetch_old_rows = after_own_append ? 1u : 0u;
+    vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit;
     vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);
@@ -525,6 +532,9 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   c.items = p.items; c.n_items = n_items;
   if (!ctx->core_only) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
   ctx->stats.kernel_launches += ctx->core_only ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
+  // this call's kernel waited for everything before it; what it appends itself is what may still be in flight
+  if (fz && fz->append) { ctx->inflight_layer = L; ctx->inflight_row0 = max_rows ? max_rows - 1 : 0; }
+  else ctx->inflight_layer = nullptr;
   return PA_OK;
 }
 
@@ -602,6 +612,7 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   timing_mark(ctx, st, 1);
   ctx->stats.kernel_launches++; ctx->stats.calls++;
   ctx->stats.kv_bytes_streamed += 2ull * (pos + n_cols) * ctx->kv_dim * 2;
+  ctx->inflight_layer = nullptr;   // the prefill kernel waits for its RoPE/append kernel before it lets anything follow
   return PA_OK;
 }
 
@@ -653,7 +664,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
       return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true, &fz);
     }
     if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
-                                  owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st))
+                                  owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, 0, true))
       return rc;
     pa_item it{seq, pos, n_cols, 0};
     return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true);
@@ -669,7 +680,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic)
   if (!ctx->core_only)
     if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
-                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : 0))
+                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : 0, true))
       return rc;
   if (prefill)
     return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);

@@ -185,6 +185,11 @@ struct pa_ctx {
   uint32_t G = 1, q_dim = 0, kv_dim = 0;
   double* inv_freq = nullptr;  // device: theta^(-2i/n_rot), i < n_rot/2, evaluated on the host in float64
   double inv_freq_host[128] = {};   // the same table on the host
+  // The one call whose cache writes may still be in flight when the kernels of the next call start ahead of their
+  // own wait: a fused one-token decode (its kernel appends the row) or a stand-alone append.  The next call on the
+  // same layer fetches early only below inflight_row0 (row within the layer's shard).
+  const pa_layer* inflight_layer = nullptr;
+  uint32_t inflight_row0 = 0;
   float* q_rot = nullptr;      // device: rotated q of the current call, f32 [max_cols][q_dim]
   float* part_o = nullptr;     // device: split partials, f32 [rows][splits][head_dim] of the current call
   float* part_ml = nullptr;    // device: f32 [rows][splits][2]

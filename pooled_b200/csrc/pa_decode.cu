@@ -101,8 +101,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   constexpr bool Q_IN_REGS = QLD <= 16;
   float2 qreg[Q_IN_REGS ? QLD : 1];
   const uint32_t G = p.G, live_rows = n_cols * G;
-  auto q_load = [&](int idx) {
-    const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+  auto q_load_rd = [&](int row, int d) {
     float2 x = make_float2(0.f, 0.f);
     if ((uint32_t)row < live_rows) {
       const uint32_t c = row / G, hh = row % G;
@@ -112,23 +111,26 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     return x;   // f16 input: the two halves, unconverted, in x.x -- nothing here waits for the load to land
   };
+  auto q_load = [&](int idx) { return q_load_rd(idx / (HD / 2), (idx % (HD / 2)) * 2); };
   auto act_cvt = [&](float2 raw) {
     if (!p.q_f16) return raw;
     const uint32_t u = __float_as_uint(raw.x);
     return __half22float2(*reinterpret_cast<const __half2*>(&u));
   };
-  auto q_store = [&](int idx, float2 x) {
-    const int row = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+  auto q_store_rd = [&](int row, int d, float2 x) {
     __half h0, l0, h1, l1;
     split_h(x.x, h0, l0); split_h(x.y, h1, l1);
     *reinterpret_cast<__half2*>(q_hi + row * QP + d * 2) = __halves2half2(h0, h1);
     if (PRECISE) *reinterpret_cast<__half2*>(q_lo + row * QP + d * 2) = __halves2half2(l0, l1);
   };
-  // Fused front (one token, 64 rotated dims, head_dim 256): q arrives unrotated.  Thread t holds dims (2t, 2t + 1) of
-  // every row, so the rotary pairs (d, d + 32) of the first 64 dims sit in lanes l and l ^ 16 of warp 0: one shuffle
-  // brings the partner, and cos / sin of the float64 angle come with the launch parameters.  In the CTA that walks the
-  // sequence's last tile the same threads also carry the token's own k / v row: rotated, rounded to f16, stored to
-  // the cache, and kept in two registers to be placed into the tile the TMA fetched before (or while) it was stored.
+  auto q_store = [&](int idx, float2 x) { q_store_rd(idx / (HD / 2), (idx % (HD / 2)) * 2, x); };
+  // Fused front (one token, 64 rotated dims, head_dim 256): q arrives unrotated; cos / sin of the float64 angle come
+  // with the launch parameters.  The rotation is spread over all 128 consumer threads: thread t takes row t / 16 and
+  // the dims (2b, 2b + 1) with their partners (2b + 32, 2b + 33), b = t % 16 (four outputs), and six of the 768
+  // unrotated pairs.  In the CTA that walks the sequence's last tile thread t also carries dims (2t, 2t + 1) of the
+  // token's own k / v row (rotary partners sit in lanes l and l ^ 16 of warp 0: one shuffle): rotated, rounded to f16,
+  // stored to the cache, and kept in two registers to be placed into the tile the TMA fetched before (or while) it
+  // was stored.
   constexpr bool CAN_FUSE = NT == 1 && HD == 256;
   const bool fused = CAN_FUSE && p.fused;
   const bool own_new = fused && p.append && tile1 == tiles;
@@ -150,8 +152,18 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     pdl_trigger();
     TR(4);
     if (Q_IN_REGS) {
+      if (fused) {
+        qreg[0] = q_load_rd(tid >> 4, 2 * (tid & 15));
+        qreg[1 % (Q_IN_REGS ? QLD : 1)] = q_load_rd(tid >> 4, 2 * (tid & 15) + 32);
 #pragma unroll
-      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = q_load(tid + it * kConsumers);
+        for (int it = 2; it < (Q_IN_REGS ? QLD : 1); ++it) {
+          const int idx = tid + (it - 2) * kConsumers;
+          qreg[it] = q_load_rd(idx / 96, 64 + 2 * (idx % 96));
+        }
+      } else {
+#pragma unroll
+        for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = q_load(tid + it * kConsumers);
+      }
       if (own_new) {
         const uint64_t so = (uint64_t)g * HD + 2 * tid;
         if (p.q_f16) {
@@ -197,7 +209,8 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const uint32_t pre = p.prefetch_old_rows ? p.pre_stages : 0u;
     const int y0 = (int)(p.items.seq[item] * p.max_seq + tile0 * kT);
     const int z = (int)(g * CH);
-    const uint32_t old_rows = n_rows - min(n_rows, n_cols);   // rows below the ones this call's columns added
+    // rows below the ones this call's columns added, and below whatever the call before may still be writing
+    const uint32_t old_rows = min(n_rows - min(n_rows, n_cols), p.early_limit);
     bool waited = !p.prefetch_old_rows;
     if (lane == 0) {
       prefetch_tmap(&tm_k);
@@ -245,13 +258,27 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
     for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = act_cvt(qreg[it]);
     if (own_new) { kx = act_cvt(kx); vx = act_cvt(vx); }
-    if (fused && w == 0) {
+    if (fused) {
+      const int row = tid >> 4, b2 = 2 * (tid & 15);
+      const double c0 = p.rope_cs[b2], c1 = p.rope_cs[b2 + 1], s0 = p.rope_cs[32 + b2], s1 = p.rope_cs[33 + b2];
+      const float2 a = qreg[0], b = qreg[1 % (Q_IN_REGS ? QLD : 1)];
+      float2 ra, rb;   // products rounded one by one, as the stand-alone RoPE kernel does
+      ra.x = (float)__dsub_rn(__dmul_rn((double)a.x, c0), __dmul_rn((double)b.x, s0));
+      ra.y = (float)__dsub_rn(__dmul_rn((double)a.y, c1), __dmul_rn((double)b.y, s1));
+      rb.x = (float)__dadd_rn(__dmul_rn((double)b.x, c0), __dmul_rn((double)a.x, s0));
+      rb.y = (float)__dadd_rn(__dmul_rn((double)b.y, c1), __dmul_rn((double)a.y, s1));
+      q_store_rd(row, b2, ra);
+      q_store_rd(row, b2 + 32, rb);
 #pragma unroll
-      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = rotate(qreg[it]);
-      if (own_new) kx = rotate(kx);
+      for (int it = 2; it < (Q_IN_REGS ? QLD : 1); ++it) {
+        const int idx = tid + (it - 2) * kConsumers;
+        q_store_rd(idx / 96, 64 + 2 * (idx % 96), qreg[it]);
+      }
+      if (own_new && w == 0) kx = rotate(kx);
+    } else {
+#pragma unroll
+      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) q_store(tid + it * kConsumers, qreg[it]);
     }
-#pragma unroll
-    for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) q_store(tid + it * kConsumers, qreg[it]);
     if (own_new) {
       auto h16 = [](float x) -> uint32_t {   // round to nearest even; NaN -> sign | 0x7e00, as the append kernel
         return x != x ? (((__float_as_uint(x) >> 16) & 0x8000u) | 0x7e00u) : (uint32_t)__half_as_ushort(__float2half_rn(x));
@@ -315,6 +342,43 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       *reinterpret_cast<uint32_t*>(k_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = k_new2;
       named_bar_sync(1, kConsumers);
     }
+    if constexpr (NT <= 2) {
+      // Software-pipelined: the fragments of step k2 + 1 are requested before the MMAs of step k2 are issued, so
+      // the shared-memory latency of one step hides behind the tensor work of the other (one warp per scheduler:
+      // nothing else would hide it).
+      const uint32_t krow = 16 * w + (lane & 7) + ((lane >> 3) & 1) * 8;
+      uint32_t a[2][2][4], bh[2][NT][4], bl[2][NT][4];
+      auto load_step = [&](int k2, int buf) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t c16g = (2 * k2 + e) * 2 + (lane >> 4);
+          const uint32_t addr = ks_base + (c16g >> 3) * (kT * 128) + krow * 128 + (((c16g & 7) ^ (krow & 7)) << 4);
+          ldsm_x4(addr, a[buf][e][0], a[buf][e][1], a[buf][e][2], a[buf][e][3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t qoff = (nt * 8 + (lane & 7)) * QP + (4 * k2 + (lane >> 3)) * 16;
+          ldsm_x4(q_hi_s + qoff, bh[buf][nt][0], bh[buf][nt][1], bh[buf][nt][2], bh[buf][nt][3]);
+          if (PRECISE) ldsm_x4(q_lo_s + qoff, bl[buf][nt][0], bl[buf][nt][1], bl[buf][nt][2], bl[buf][nt][3]);
+        }
+      };
+      load_step(0, 0);
+#pragma unroll
+      for (int k2 = 0; k2 < HD / 32; ++k2) {
+        const int cur = k2 & 1;
+        if (k2 + 1 < HD / 32) load_step(k2 + 1, cur ^ 1);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_16816(sacc[nt], a[cur][0][0], a[cur][0][1], a[cur][0][2], a[cur][0][3], bh[cur][nt][0], bh[cur][nt][1]);
+          mma_16816(NA >= 2 ? sacc_x[nt][0] : sacc[nt], a[cur][1][0], a[cur][1][1], a[cur][1][2], a[cur][1][3], bh[cur][nt][2], bh[cur][nt][3]);
+          if (PRECISE) {
+            mma_16816(NA >= 4 ? sacc_x[nt][1] : sacc[nt], a[cur][0][0], a[cur][0][1], a[cur][0][2], a[cur][0][3], bl[cur][nt][0], bl[cur][nt][1]);
+            mma_16816(NA >= 4 ? sacc_x[nt][2] : (NA >= 2 ? sacc_x[nt][0] : sacc[nt]), a[cur][1][0], a[cur][1][1], a[cur][1][2], a[cur][1][3],
+                      bl[cur][nt][2], bl[cur][nt][3]);
+          }
+        }
+      }
+    } else
     {
       const uint32_t krow = 16 * w + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll 4
@@ -430,6 +494,43 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (i < 15) TR(13 + 8 * i);
 
     // ---- O^T += V^T . P^T, dims (w*MT + mt)*16 .. +15 ----
+    if constexpr (NT <= 2) {
+      // pipelined like the score product: step t = (ks, mt); V fragments of step t + 1 and the P fragments of the
+      // next ks are requested before the MMAs of step t
+      constexpr int STEPS = (kT / 16) * MT;
+      uint32_t av[2][4], pbh[2][NT][2], pbl[2][NT][2];
+      auto load_p = [&](int ks, int buf) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t poff = (ks * 16 + (lane & 15)) * PP + nt * 16;
+          ldsm_x2_t(p_hi_s + poff, pbh[buf][nt][0], pbh[buf][nt][1]);
+          if (PRECISE) ldsm_x2_t(p_lo_s + poff, pbl[buf][nt][0], pbl[buf][nt][1]);
+        }
+      };
+      auto load_v = [&](int t, int buf) {
+        const int ks = t / MT, mt = t % MT;
+        const uint32_t qd = lane >> 3;
+        const uint32_t vrow = ks * 16 + (lane & 7) + (qd >> 1) * 8;
+        const uint32_t c16g = (w * MT + mt) * 2 + (qd & 1);
+        const uint32_t addr = vs_base + (c16g >> 3) * (kT * 128) + vrow * 128 + (((c16g & 7) ^ (vrow & 7)) << 4);
+        ldsm_x4_t(addr, av[buf][0], av[buf][1], av[buf][2], av[buf][3]);
+      };
+      load_p(0, 0);
+      load_v(0, 0);
+#pragma unroll
+      for (int t = 0; t < STEPS; ++t) {
+        const int ks = t / MT, mt = t % MT, cur = t & 1, pc = ks & 1;
+        if (t + 1 < STEPS) {
+          if ((t + 1) % MT == 0) load_p(ks + 1, pc ^ 1);
+          load_v(t + 1, cur ^ 1);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_16816(oacc[mt][nt], av[cur][0], av[cur][1], av[cur][2], av[cur][3], pbh[pc][nt][0], pbh[pc][nt][1]);
+          if (PRECISE) mma_16816(oacc[mt][nt], av[cur][0], av[cur][1], av[cur][2], av[cur][3], pbl[pc][nt][0], pbl[pc][nt][1]);
+        }
+      }
+    } else
 #pragma unroll
     for (int ks = 0; ks < kT / 16; ++ks) {
       uint32_t bh[NT][2], bl[NT][2];

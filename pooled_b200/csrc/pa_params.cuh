@@ -20,6 +20,7 @@ struct DecodeParams {
   double rope_cs[64];       // cos (first 32) and sin of pos * theta^(-2i/64), evaluated by the host in float64
   uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends
   uint32_t pre_stages;         // ... but only this many per CTA before the q loads are in flight
+  uint32_t early_limit;        // ... and only rows below this one (the call before may still be writing its own row)
   float scale_log2;         // log2(e) / sqrt(head_dim)
   uint32_t* err;
   unsigned long long* trace;   // development builds only (PA_TRACE): per-CTA timestamps; nullptr otherwise
@@ -47,6 +48,7 @@ struct CombineParams {
 
 struct RopeParams {
   unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
+  uint32_t trigger_early;      // 1: the dependent kernel may start before this one's own wait (inside a layer call only)
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
   void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
   const void* k; const void* v; uint64_t kv_col_stride; uint32_t kv_heads;  // k == nullptr: skip
@@ -72,6 +74,7 @@ struct PrefillParams {
   // split-K form (k-token verify on the tensor cores): one CTA per (split, kv head), rows = columns x heads of the group
   float* part_o; float* part_ml; uint32_t n_splits; int32_t lim0; uint32_t n_rows, col0;
   uint32_t prefetch_old_rows;   // split-K form: K/V tiles wholly below the call's new rows may be fetched before the predecessor ends
+  uint32_t early_limit;         // ... and below this row (the call before may still be writing its own row)
   unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
 };
 

@@ -235,7 +235,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   // q, and the rows the RoPE/append kernel before this one writes, may only be touched after pdl_wait(); in the
   // split-K form the producers may fetch older K/V tiles ahead of it when the caller allows
   const bool early = SK && p.prefetch_old_rows;
-  const uint32_t old_rows = SK ? p.n_rows - min(p.n_rows, p.n_cols) : 0u;
+  const uint32_t old_rows = SK ? min(p.n_rows - min(p.n_rows, p.n_cols), p.early_limit) : 0u;
   if (!early) pdl_wait();
   __syncthreads();
   tc_fence_after();

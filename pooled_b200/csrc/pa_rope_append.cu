@@ -39,8 +39,9 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
 #define RTR(slot) do {} while (0)
 #endif
   RTR(0);
-  pdl_trigger();
+  if (p.trigger_early) pdl_trigger();
   pdl_wait();
+  if (!p.trigger_early) pdl_trigger();
   RTR(1);
   if (pr >= hd / 2) return;
   const uint32_t nq = p.q ? p.q_heads : 0, nk = p.k ? p.kv_heads : 0;
@@ -95,8 +96,9 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
 __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopeParams p) {
   __shared__ double s_c[128], s_s[128];
   const uint32_t col = blockIdx.x, half = p.n_rot / 2, hd = p.hd, pairs = hd / 2;
-  pdl_trigger();
+  if (p.trigger_early) pdl_trigger();
   pdl_wait();
+  if (!p.trigger_early) pdl_trigger();
   if (p.mode == PA_ROPE_F64) {
     for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
       double sv, cv;
