@@ -17,6 +17,7 @@ cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, i
 cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, cudaStream_t st);
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
+cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
 cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
@@ -167,6 +168,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
     if ((e = cudaMalloc(&ctx->inv_freq, half * sizeof(double))) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(inv_freq)", e);
     if ((e = cudaMemcpy(ctx->inv_freq, host, half * sizeof(double), cudaMemcpyHostToDevice)) != cudaSuccess) return bail(PA_ECUDA, "cudaMemcpy(inv_freq)", e);
   }
+  if (half && (e = cudaMalloc(&ctx->angles, (size_t)cfg->max_cols * half * sizeof(Angle))) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(angles)", e);
   if ((e = cudaMalloc(&ctx->q_rot, (size_t)cfg->max_cols * cfg->n_heads * cfg->head_dim * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(q_rot)", e);
   // split partials: one (o, m, l) record per (query row, split).  A call uses rows * splits of them, about
   // 64 rows x one CTA per SM; the split planner keeps every call inside this capacity.
@@ -184,7 +186,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
 extern "C" int pa_destroy(pa_ctx* ctx) {
   if (!ctx) return PA_OK;
   cudaSetDevice(ctx->device);
-  cudaFree(ctx->inv_freq); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err);
+  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err);
   cudaFree(ctx->stage_dev);
   for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
@@ -362,6 +364,41 @@ static unsigned long long* trace_region(unsigned call) {
 }
 #endif
 
+// cos / sin of a call of at most 64 angles, evaluated by the host's libm and kept while the position repeats (every
+// layer of a step asks for the same ones)
+static const Angle* host_angles(pa_ctx* ctx, uint32_t pos, uint32_t n_cols) {
+  const uint32_t half = ctx->cfg.n_rot / 2;
+  if (ctx->host_ang_n != n_cols * half || ctx->host_ang_pos != pos) {
+    for (uint32_t c = 0; c < n_cols; ++c)
+      for (uint32_t i = 0; i < half; ++i) {
+        const double ang = (double)(pos + c) * ctx->inv_freq_host[i];
+        ctx->host_ang[c * half + i] = make_angle(cos(ang), sin(ang));
+      }
+    ctx->host_ang_n = n_cols * half; ctx->host_ang_pos = pos;
+  }
+  return ctx->host_ang;
+}
+
+// Makes ctx->angles hold cos / sin for columns pos .. pos + n_cols - 1, launching pa_angles_kernel unless the table
+// already does (same position and width, same capture, and no graph replay can have rewritten it since).
+static int ensure_angles(pa_ctx* ctx, uint32_t pos, uint32_t n_cols, cudaStream_t st) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  unsigned long long cap = 0;
+  if (cudaStreamGetCaptureInfo(st, &cs, &cap) != cudaSuccess) { cudaGetLastError(); cs = cudaStreamCaptureStatusNone; }
+  if (cs != cudaStreamCaptureStatusActive) cap = 0;
+  else ctx->ever_captured = true;
+  const bool same = ctx->angles_valid && ctx->angles_pos0 == pos && ctx->angles_n == n_cols && ctx->angles_capture == cap;
+  const bool trusted = cap != 0 || !ctx->ever_captured || (ctx->scope_active && ctx->scope_fresh);
+  if (same && trusted) return PA_OK;
+  AnglesParams a{};
+  a.out = ctx->angles; a.inv_freq = ctx->inv_freq; a.pos0 = pos; a.n_cols = n_cols; a.half = ctx->cfg.n_rot / 2;
+  CU_TRY(ctx, launch_angles(a, st));
+  ctx->stats.kernel_launches++;
+  ctx->angles_valid = true; ctx->angles_pos0 = pos; ctx->angles_n = n_cols; ctx->angles_capture = cap;
+  if (ctx->scope_active) ctx->scope_fresh = true;
+  return PA_OK;
+}
+
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
                             uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
                             uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false) {
@@ -374,6 +411,17 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
   p.hd = ctx->cfg.head_dim; p.n_rot = ctx->cfg.n_rot; p.pos = pos; p.mode = mode; p.in_f16 = in_f16;
   p.inv_freq = ctx->inv_freq; p.cs_table = cs_table;
   if (mode == PA_ROPE_TABLE && !cs_table) return fail(ctx, PA_EINVAL, "rope: PA_ROPE_TABLE needs a cos/sin table");
+  const uint32_t half = ctx->cfg.n_rot / 2;
+  if (mode == PA_ROPE_F64 && half && (q || k)) {
+    if (n_cols * half <= 64) {
+      // few angles: the host's libm evaluates them (the very values the CPU reference uses) and they travel by value
+      p.n_ang = n_cols * half;
+      memcpy(p.ang, host_angles(ctx, pos, n_cols), (size_t)p.n_ang * sizeof(Angle));
+    } else if (ctx->angles && n_cols <= ctx->cfg.max_cols) {
+      if (int rc = ensure_angles(ctx, pos, n_cols, st)) return rc;
+      p.angles = ctx->angles;
+    }
+  }
 #ifdef PA_TRACE
   if (n_cols == 1) p.trace = trace_region(g_trace_call);   // the decode call that follows takes the same region
 #endif
@@ -484,10 +532,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   if (fz) {
     p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
     p.k_cache = L->k; p.v_cache = L->v;
-    for (uint32_t i = 0; i < 32; ++i) {
-      const double ang = (double)fz->pos * ctx->inv_freq_host[i];
-      p.rope_cs[i] = cos(ang); p.rope_cs[32 + i] = sin(ang);
-    }
+    memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), 32 * sizeof(Angle));
   }
 #ifdef PA_TRACE
   p.trace = trace_region(g_trace_call++);
@@ -505,7 +550,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs;
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
-    vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit;
+    vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit; vp.pre_stages = p.pre_stages;
     vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);
@@ -780,12 +825,16 @@ extern "C" int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uin
   const uint8_t* dgate = nullptr;
   if (gate_in_q) dgate = dq + (gh - qh);
   else if (gate) { CU_TRY(ctx, cudaMemcpyAsync(dg, gate, (size_t)n_layers * gate_layer_stride * es, cudaMemcpyHostToDevice, st)); dgate = dg; }
+  ctx->scope_active = true; ctx->scope_fresh = false;   // all layers of this call may share one cos / sin table
   for (uint32_t l = 0; l < n_layers; ++l) {
     if (int rc = layer_impl(layers[l], seq, pos, n_cols, mode, dq + l * q_layer_stride * es, qcs, qhs, dk + l * kv_layer_stride * es,
                             dv + l * kv_layer_stride * es, kvcs, dgate ? dgate + l * gate_layer_stride * es : nullptr, gcs, ghs, nullptr,
-                            dout + l * out_layer_stride * es, ocs, st))
+                            dout + l * out_layer_stride * es, ocs, st)) {
+      ctx->scope_active = false;
       return rc;
+    }
   }
+  ctx->scope_active = false;
   CU_TRY(ctx, cudaMemcpyAsync(out, dout, (size_t)n_layers * out_layer_stride * es, cudaMemcpyDeviceToHost, st));
   return pa_sync(ctx, stream);
 }

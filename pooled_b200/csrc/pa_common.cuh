@@ -102,6 +102,46 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// cos / sin of one rotary angle: the float64 values and each split into an f32 pair (hi = fl32(v), lo = fl32(v - hi))
+struct Angle { double c, s; float c_hi, c_lo, s_hi, s_lo; };
+__host__ __device__ inline Angle make_angle(double c, double s) {
+  Angle g; g.c = c; g.s = s;
+  g.c_hi = (float)c; g.c_lo = (float)(c - (double)g.c_hi);
+  g.s_hi = (float)s; g.s_lo = (float)(s - (double)g.s_hi);
+  // a nonzero value so small that its low half would underflow in f32: poison the pair, which sends every use of
+  // this angle to the float64 instructions
+  const double tiny = 8.0e-28;   // ~2^-90
+  if ((c != 0.0 && fabs(c) < tiny) || (s != 0.0 && fabs(s) < tiny)) g.c_hi = __builtin_nanf("");
+  return g;
+}
+
+// One output of a float64 rotation, rounded to f32:  fl32( fl64( fl64(x * cos) -/+ fl64(y * sin) ) ), bit for bit,
+// at f32 cost.  (Plain FP64 instructions run at a small fraction of the FP32 rate on this GPU, and a prefill chunk
+// rotates millions of elements.)  x*cos_hi and y*sin_hi are split exactly into product + error by FMA, the low
+// halves of cos / sin are folded in, and the sum is kept as an unevaluated f32 pair hi + lo that is within
+// 2^-44 (|x cos| + |y sin|) of the exact value; the float64 expression is within 2^-51 of it.  fl32 of both is the
+// same number unless the value lies within that distance of a rounding boundary of f32 (hi +- ulp/2, or hi - ulp/4
+// below a power of two): only then (about one output in 2^17, and for zero, tiny, huge or non-finite operands) the
+// float64 instructions run.
+__device__ __forceinline__ float rot_exact(float x, float y, const Angle& g, bool minus) {
+  const float ys = minus ? -y : y;
+  const float p1 = __fmul_rn(x, g.c_hi), e1 = __fmaf_rn(x, g.c_hi, -p1), t1 = __fmaf_rn(x, g.c_lo, e1);
+  const float p2 = __fmul_rn(ys, g.s_hi), e2 = __fmaf_rn(ys, g.s_hi, -p2), t2 = __fmaf_rn(ys, g.s_lo, e2);
+  const float sh = __fadd_rn(p1, p2), z = __fsub_rn(sh, p1);
+  const float se = __fadd_rn(__fsub_rn(p1, __fsub_rn(sh, z)), __fsub_rn(p2, z));   // p1 + p2 = sh + se exactly
+  const float l0 = __fadd_rn(se, __fadd_rn(t1, t2));
+  const float hi = __fadd_rn(sh, l0), lo = __fsub_rn(l0, __fsub_rn(hi, sh));
+  const float M = __fadd_rn(fabsf(p1), fabsf(p2));
+  const float delta = __fmul_rn(M, 2.2737368e-13f);   // 2^-42 M: well above both error bounds
+  const float ah = fabsf(hi), al = fabsf(lo);
+  const float u = __fmul_rn(__uint_as_float(__float_as_uint(ah) & 0x7f800000u), 1.1920929e-7f);   // ulp(hi) = 2^(e-23)
+  const bool safe = M > 7.8886091e-31f && M < 1.2676506e30f && ah > 7.8886091e-31f &&      // 2^-100 .. 2^100
+                    fabsf(__fsub_rn(al, 0.5f * u)) > delta && fabsf(__fsub_rn(al, 0.25f * u)) > delta && al <= 0.5f * u;
+  if (safe) return hi;
+  const double a = __dmul_rn((double)x, g.c), b = __dmul_rn((double)y, g.s);
+  return (float)(minus ? __dsub_rn(a, b) : __dadd_rn(a, b));
+}
+
 // hi + lo f16 pair of an f32: x ~= hi + lo with about 22 significant bits
 __device__ __forceinline__ void split_h(float x, __half& hi, __half& lo) {
   hi = __float2half_rn(x);
@@ -188,6 +228,15 @@ struct pa_ctx {
   // The one call whose cache writes may still be in flight when the kernels of the next call start ahead of their
   // own wait: a fused one-token decode (its kernel appends the row) or a stand-alone append.  The next call on the
   // same layer fetches early only below inflight_row0 (row within the layer's shard).
+  // cos / sin table of the current step's columns (PA_ROPE_F64), filled by pa_angles_kernel.  Valid for calls with
+  // the same position and width in the same capture (or, outside captures, until a graph that rewrites it may have
+  // been replayed: once a capture has been seen, stand-alone calls refill it, except inside one multi-layer call).
+  pa::Angle host_ang[64];            // the last small call's angles (host libm), reused while the position repeats
+  uint32_t host_ang_pos = 0, host_ang_n = 0;
+  pa::Angle* angles = nullptr;
+  uint32_t angles_pos0 = 0, angles_n = 0;
+  unsigned long long angles_capture = 0;
+  bool angles_valid = false, ever_captured = false, scope_active = false, scope_fresh = false;
   const pa_layer* inflight_layer = nullptr;
   uint32_t inflight_row0 = 0;
   float* q_rot = nullptr;      // device: rotated q of the current call, f32 [max_cols][q_dim]

@@ -47,7 +47,7 @@ struct DecSmem {
   static constexpr int PP = ROWS * 2;                // P^T row pitch (bytes)
   static constexpr int Q_BYTES = ROWS * QP * (PRECISE ? 2 : 1);
   static constexpr int P_BYTES = kT * PP * (PRECISE ? 2 : 1);
-  static constexpr int MISC = 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64;
+  static constexpr int MISC = 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 1024;   // + the fused front's angles
   static constexpr int fixed_bytes() { return Q_BYTES + P_BYTES + MISC; }
   static int stages_for(int smem_limit) {
     int s = (smem_limit - 1024 - fixed_bytes()) / (2 * SLOT);
@@ -87,6 +87,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   float* s_l = s_max + 4 * ROWS;                                // [4][ROWS]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_l + 4 * ROWS); // kfull, kempty, vfull, vempty [kMaxStages] each
   volatile uint32_t* s_err = reinterpret_cast<volatile uint32_t*>(bars + 4 * kMaxStages);
+  Angle* s_ang = reinterpret_cast<Angle*>(bars + 4 * kMaxStages + 8);   // [32], fused front only
 
   const uint32_t kfull = smem_u32(bars), kempty = kfull + kMaxStages * 8, vfull = kempty + kMaxStages * 8,
                  vempty = vfull + kMaxStages * 8;
@@ -139,15 +140,16 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   auto rotate = [&](float2 x) {   // warp 0 only, all lanes
     const float2 y = make_float2(__shfl_xor_sync(0xffffffffu, x.x, 16), __shfl_xor_sync(0xffffffffu, x.y, 16));
     const int i = 2 * (lane & 15);
-    const double c0 = p.rope_cs[i], c1 = p.rope_cs[i + 1], s0 = p.rope_cs[32 + i], s1 = p.rope_cs[33 + i];
     // first element of a pair (lanes 0-15): a cos - b sin; second: b cos + a sin -- own * cos -/+ partner * sin
-    const double sg = lane < 16 ? -1.0 : 1.0;
     float2 o;
-    o.x = (float)__dadd_rn(__dmul_rn((double)x.x, c0), sg * __dmul_rn((double)y.x, s0));
-    o.y = (float)__dadd_rn(__dmul_rn((double)x.y, c1), sg * __dmul_rn((double)y.y, s1));
+    o.x = rot_exact(x.x, y.x, s_ang[i], lane < 16);
+    o.y = rot_exact(x.y, y.y, s_ang[i + 1], lane < 16);
     return o;
   };
   if (warp < 4) {
+    // Threads that index launch parameters differently are served one address at a time, each a miss of the constant
+    // cache: far too slow for the critical path.  The angles go to shared memory while the predecessor still runs.
+    if (fused) reinterpret_cast<uint2*>(s_ang)[tid] = reinterpret_cast<const uint2*>(p.rope_ang)[tid];
     pdl_wait();      // q (and the partial buffers written at the end) belong to earlier kernels until here
     pdl_trigger();
     TR(4);
@@ -260,13 +262,12 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (own_new) { kx = act_cvt(kx); vx = act_cvt(vx); }
     if (fused) {
       const int row = tid >> 4, b2 = 2 * (tid & 15);
-      const double c0 = p.rope_cs[b2], c1 = p.rope_cs[b2 + 1], s0 = p.rope_cs[32 + b2], s1 = p.rope_cs[33 + b2];
       const float2 a = qreg[0], b = qreg[1 % (Q_IN_REGS ? QLD : 1)];
-      float2 ra, rb;   // products rounded one by one, as the stand-alone RoPE kernel does
-      ra.x = (float)__dsub_rn(__dmul_rn((double)a.x, c0), __dmul_rn((double)b.x, s0));
-      ra.y = (float)__dsub_rn(__dmul_rn((double)a.y, c1), __dmul_rn((double)b.y, s1));
-      rb.x = (float)__dadd_rn(__dmul_rn((double)b.x, c0), __dmul_rn((double)a.x, s0));
-      rb.y = (float)__dadd_rn(__dmul_rn((double)b.y, c1), __dmul_rn((double)a.y, s1));
+      float2 ra, rb;   // the bits of the float64 expression the stand-alone RoPE kernel evaluates
+      ra.x = rot_exact(a.x, b.x, s_ang[b2], true);
+      ra.y = rot_exact(a.y, b.y, s_ang[b2 + 1], true);
+      rb.x = rot_exact(b.x, a.x, s_ang[b2], false);
+      rb.y = rot_exact(b.y, a.y, s_ang[b2 + 1], false);
       q_store_rd(row, b2, ra);
       q_store_rd(row, b2 + 32, rb);
 #pragma unroll

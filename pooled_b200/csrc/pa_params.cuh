@@ -17,7 +17,7 @@ struct DecodeParams {
   uint32_t fused, append;       // append: this cache holds the new row (false on another rank's shard)
   const void* k_new; const void* v_new;               // the token's k / v row, [n_kv * hd], dtype as q
   __half* k_cache; __half* v_cache;                   // caches of the layer
-  double rope_cs[64];       // cos (first 32) and sin of pos * theta^(-2i/64), evaluated by the host in float64
+  Angle rope_ang[32];       // cos / sin of pos * theta^(-2i/64), evaluated by the host in float64
   uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends
   uint32_t pre_stages;         // ... but only this many per CTA before the q loads are in flight
   uint32_t early_limit;        // ... and only rows below this one (the call before may still be writing its own row)
@@ -57,6 +57,15 @@ struct RopeParams {
   int in_f16;
   const double* inv_freq;
   const float* cs_table;   // [n_cols][n_rot] (cos, sin) per pair
+  const Angle* angles;     // PA_ROPE_F64: [n_cols][n_rot/2] cos / sin of the call's columns (nullptr: evaluate here)
+  uint32_t n_ang;          // > 0: a call of at most 64 angles carries them here, evaluated by the host's libm
+  Angle ang[64];
+};
+
+struct AnglesParams {
+  Angle* out;              // [n_cols][half]
+  const double* inv_freq;
+  uint32_t pos0, n_cols, half;
 };
 
 struct SigmoidParams {
@@ -75,6 +84,7 @@ struct PrefillParams {
   float* part_o; float* part_ml; uint32_t n_splits; int32_t lim0; uint32_t n_rows, col0;
   uint32_t prefetch_old_rows;   // split-K form: K/V tiles wholly below the call's new rows may be fetched before the predecessor ends
   uint32_t early_limit;         // ... and below this row (the call before may still be writing its own row)
+  uint32_t pre_stages;          // ... and only this many K tiles (one fewer V tiles) before the q loads are in flight
   unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
 };
 

@@ -198,7 +198,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 24);
   volatile uint32_t* s_err = s_tmem + 1;
   const uint32_t bar0 = smem_u32(bars);
-  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22 };
+  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23 };
   uint8_t* q_s = base + L::OFF_Q;
   auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
@@ -225,6 +225,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     for (int i = 0; i < kSBuf; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
     mbar_init(BAR(Q_FULL, 0), 128);
+    mbar_init(BAR(Q_ISSUED, 0), 128);
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -250,6 +251,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NK, u = j / NK;
         if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
+        // ahead of the wait only a few tiles go out: a long burst would queue in front of the q loads that follow it
+        if (early && j == p.pre_stages) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
@@ -265,6 +268,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NV, u = j / NV;
         if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
+        if (early && j + 1 == p.pre_stages) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
@@ -373,6 +377,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
+        if (c2 == HD / 128 - 1) mbar_arrive(BAR(Q_ISSUED, 0));   // every q load of this thread has been issued
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
           const int c = 2 * c2 + hc;

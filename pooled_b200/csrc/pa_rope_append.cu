@@ -1,10 +1,12 @@
 // RoPE (full or partial, NeoX pairing), the f16 KV-cache append and the standalone sigmoid gate.
 //
-// One small CTA per (column, head).  The cos / sin of an angle is evaluated by the thread that rotates the pair:
+// One small CTA per (column, head), or one CTA per column for prefill chunks.
 //   PA_ROPE_F64    angle = pos * inv_freq[i] in float64 (inv_freq = theta^(-2i/n_rot) comes from the host's
 //                  libm), cos / sin in float64, the two products and their difference / sum rounded one by
 //                  one in float64, the result rounded to f32 — the arithmetic of pooled's CPU reference
-//                  (tests/reference/ref_q38.mjs:67-79).
+//                  (tests/reference/ref_q38.mjs:67-79).  cos / sin come from a table that pa_angles_kernel fills
+//                  once per (position, width) and every layer of the step reuses; the rotation itself is
+//                  rot_exact(): the same bits as the float64 expression at f32 cost.
 //   PA_ROPE_TABLE  cos / sin read from the caller's f32 table, products and sums rounded one by one in f32
 //                  (the Flash engine's host table, engine/qwen4exp.js:549-553).
 // K is rotated, rounded to f32 and then to f16 (round to nearest even) into row pos + col of the K cache;
@@ -39,7 +41,14 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
 #define RTR(slot) do {} while (0)
 #endif
   RTR(0);
+  // by-value angles go through shared memory: launch parameters indexed differently by every thread are served one
+  // address at a time.  Done ahead of the wait, while the predecessor still runs.
+  __shared__ Angle s_ang[64];
   if (p.trigger_early) pdl_trigger();
+  if (p.n_ang) {
+    if (threadIdx.x < p.n_ang * 2) reinterpret_cast<uint4*>(s_ang)[threadIdx.x] = reinterpret_cast<const uint4*>(p.ang)[threadIdx.x];
+    __syncthreads();
+  }
   pdl_wait();
   if (!p.trigger_early) pdl_trigger();
   RTR(1);
@@ -67,12 +76,16 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
   float ra = a, rb = b;
   if (rot) {
     if (p.mode == PA_ROPE_F64) {
-      const double ang = __dmul_rn((double)(p.pos + col), p.inv_freq[pr]);
-      double s, c;
-      sincos(ang, &s, &c);
-      const double ad = (double)a, bd = (double)b;
-      ra = (float)__dsub_rn(__dmul_rn(ad, c), __dmul_rn(bd, s));
-      rb = (float)__dadd_rn(__dmul_rn(bd, c), __dmul_rn(ad, s));
+      Angle g;
+      if (p.n_ang) g = s_ang[col * half + pr];
+      else if (p.angles) g = p.angles[(uint64_t)col * half + pr];
+      else {
+        double s, c;
+        sincos(__dmul_rn((double)(p.pos + col), p.inv_freq[pr]), &s, &c);
+        g = make_angle(c, s);
+      }
+      ra = rot_exact(a, b, g, true);     // a cos - b sin
+      rb = rot_exact(b, a, g, false);    // b cos + a sin
     } else {
       const float c = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr], s = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr + 1];
       ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
@@ -94,16 +107,20 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
 // shared by every head through shared memory; each thread then takes (head, pair) items four at a time so that its
 // loads overlap.  Same arithmetic, element for element, as the per-head kernel above.
 __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopeParams p) {
-  __shared__ double s_c[128], s_s[128];
+  __shared__ Angle s_g[128];
   const uint32_t col = blockIdx.x, half = p.n_rot / 2, hd = p.hd, pairs = hd / 2;
   if (p.trigger_early) pdl_trigger();
   pdl_wait();
   if (!p.trigger_early) pdl_trigger();
   if (p.mode == PA_ROPE_F64) {
     for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
-      double sv, cv;
-      sincos(__dmul_rn((double)(p.pos + col), p.inv_freq[i]), &sv, &cv);
-      s_c[i] = cv; s_s[i] = sv;
+      if (p.n_ang) s_g[i] = p.ang[col * half + i];
+      else if (p.angles) s_g[i] = p.angles[(uint64_t)col * half + i];
+      else {
+        double sv, cv;
+        sincos(__dmul_rn((double)(p.pos + col), p.inv_freq[i]), &sv, &cv);
+        s_g[i] = make_angle(cv, sv);
+      }
     }
   }
   __syncthreads();
@@ -142,9 +159,9 @@ __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopePara
       float ra = a[u], rb = b[u];
       if (p.mode != PA_ROPE_NONE && pr < half) {
         if (p.mode == PA_ROPE_F64) {
-          const double c = s_c[pr], sn = s_s[pr], ad = (double)a[u], bd = (double)b[u];
-          ra = (float)__dsub_rn(__dmul_rn(ad, c), __dmul_rn(bd, sn));
-          rb = (float)__dadd_rn(__dmul_rn(bd, c), __dmul_rn(ad, sn));
+          const Angle g = s_g[pr];
+          ra = rot_exact(a[u], b[u], g, true);
+          rb = rot_exact(b[u], a[u], g, false);
         } else {
           const float c = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr], sn = p.cs_table[(uint64_t)col * p.n_rot + 2 * pr + 1];
           ra = __fsub_rn(__fmul_rn(a[u], c), __fmul_rn(b[u], sn));
@@ -163,6 +180,104 @@ __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopePara
   }
 }
 
+
+// Prefill chunks of f16 activations with the rotated q stored as f16 (what the prefill kernel consumes): the same
+// arithmetic as the kernels above, eight elements per access.  One CTA per column; an item is a 16-byte vector of the
+// unrotated dims (copied; NaNs take the pattern the scalar path produces) or a pair of vectors (d .. d+7, d+half ..
+// d+half+7) of the rotated dims.  Four items per thread are in flight.
+__device__ __forceinline__ uint32_t fix_nan2(uint32_t w, bool cache) {
+  // per half: NaN -> 0x7fff (q, cvt.rn.f16.f32 of a NaN) or sign | 0x7e00 (cache, f16_rne)
+  uint32_t out = w;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const uint32_t h = (w >> (16 * e)) & 0xffffu;
+    if ((h & 0x7c00u) == 0x7c00u && (h & 0x03ffu)) {
+      const uint32_t r = cache ? ((h & 0x8000u) | 0x7e00u) : 0x7fffu;
+      out = (out & ~(0xffffu << (16 * e))) | (r << (16 * e));
+    }
+  }
+  return out;
+}
+__global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParams p) {
+  __shared__ Angle s_g[128];
+  const uint32_t col = blockIdx.x, half = p.n_rot / 2, hd = p.hd;
+  if (p.trigger_early) pdl_trigger();
+  pdl_wait();
+  if (!p.trigger_early) pdl_trigger();
+  for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) s_g[i] = p.n_ang ? p.ang[col * half + i] : p.angles[(uint64_t)col * half + i];
+  __syncthreads();
+  const uint32_t rv = half / 8, cv = (hd - p.n_rot) / 8, per_head = rv + cv, vv = hd / 8;
+  const uint32_t nq = p.q ? p.q_heads * per_head : 0, nk = p.k ? p.kv_heads * per_head : 0, nv = p.v ? p.kv_heads * vv : 0;
+  const uint32_t total = nq + nk + nv, kvd = p.kv_heads * hd;
+  const __half* qs = reinterpret_cast<const __half*>(p.q) + (uint64_t)col * p.q_col_stride;
+  const __half* ks = reinterpret_cast<const __half*>(p.k) + (uint64_t)col * p.kv_col_stride;
+  const __half* vs = reinterpret_cast<const __half*>(p.v) + (uint64_t)col * p.kv_col_stride;
+  __half* qd = reinterpret_cast<__half*>(p.q_out) + (uint64_t)col * p.q_out_col_stride;
+  __half* kd = p.k_cache + (p.cache_row0 + col) * (uint64_t)kvd;
+  __half* vd = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd;
+  for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * blockDim.x) {
+    uint4 A[4], B[4];
+    const __half* src[4]; __half* dst[4]; uint32_t jj[4]; int kind[4];   // kind 0: q, 1: k, 2: v
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t w = w0 + u * blockDim.x;
+      kind[u] = -1;
+      if (w >= total) continue;
+      if (w >= nq + nk) {
+        const uint32_t x = w - nq - nk;
+        kind[u] = 2; jj[u] = rv; src[u] = vs + 8 * x; dst[u] = vd + 8 * x;
+      } else {
+        const bool is_q = w < nq;
+        const uint32_t ww = is_q ? w : w - nq, head = ww / per_head, j = ww % per_head;
+        const uint32_t d = j < rv ? 8 * j : p.n_rot + 8 * (j - rv);
+        kind[u] = is_q ? 0 : 1; jj[u] = j;
+        src[u] = (is_q ? qs + (uint64_t)head * p.q_head_stride : ks + (uint64_t)head * hd) + d;
+        dst[u] = (is_q ? qd + (uint64_t)head * hd : kd + (uint64_t)head * hd) + d;
+      }
+      A[u] = *reinterpret_cast<const uint4*>(src[u]);
+      if (jj[u] < rv) B[u] = *reinterpret_cast<const uint4*>(src[u] + half);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (kind[u] < 0) continue;
+      const bool cache = kind[u] != 0;
+      if (jj[u] >= rv) {
+        uint4 o = A[u];
+        o.x = fix_nan2(o.x, cache); o.y = fix_nan2(o.y, cache); o.z = fix_nan2(o.z, cache); o.w = fix_nan2(o.w, cache);
+        *reinterpret_cast<uint4*>(dst[u]) = o;
+        continue;
+      }
+      const __half* ah = reinterpret_cast<const __half*>(&A[u]);
+      const __half* bh = reinterpret_cast<const __half*>(&B[u]);
+      uint4 oa, ob;
+      unsigned short* oah = reinterpret_cast<unsigned short*>(&oa);
+      unsigned short* obh = reinterpret_cast<unsigned short*>(&ob);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float a = __half2float(ah[e]), b = __half2float(bh[e]);
+        const Angle g = s_g[8 * jj[u] + e];
+        const float ra = rot_exact(a, b, g, true), rb = rot_exact(b, a, g, false);
+        oah[e] = cache ? __half_as_ushort(f16_rne(ra)) : __half_as_ushort(__float2half_rn(ra));
+        obh[e] = cache ? __half_as_ushort(f16_rne(rb)) : __half_as_ushort(__float2half_rn(rb));
+      }
+      *reinterpret_cast<uint4*>(dst[u]) = oa;
+      *reinterpret_cast<uint4*>(dst[u] + half) = ob;
+    }
+  }
+}
+
+// cos / sin of every (column, rotary pair) of a call, evaluated once in float64 and shared by all layers of the step
+// (the host keeps the table while position and width stay the same)
+__global__ void __launch_bounds__(128) pa_angles_kernel(const AnglesParams p) {
+  pdl_wait();        // an earlier kernel may still be reading the table
+  pdl_trigger();
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= p.n_cols * p.half) return;
+  double s, c;
+  sincos(__dmul_rn((double)(p.pos0 + i / p.half), p.inv_freq[i % p.half]), &s, &c);
+  p.out[i] = make_angle(c, s);
+}
+
 __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams p) {
   const uint32_t col = blockIdx.x, n = p.n_heads * p.hd;
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -176,9 +291,17 @@ __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams
 }
 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
+  auto al16 = [](const void* x) { return ((uintptr_t)x & 15) == 0; };
+  const bool vec = n_cols >= 16 && p.mode == PA_ROPE_F64 && (p.angles || p.n_ang) && p.in_f16 && p.n_rot % 16 == 0 && p.n_rot <= 256 && p.hd % 8 == 0 &&
+                   (!p.q || (p.q_out_f16 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
+                   (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0));
+  if (vec) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
   if (n_cols >= 16) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
   const uint32_t slots = (p.q ? p.q_heads : 0) + (p.k ? p.kv_heads : 0) + (p.v ? p.kv_heads : 0);
   return launch_pdl(pa_rope_append_kernel, dim3(n_cols, slots), dim3(128), 0, st, p);
+}
+cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st) {
+  return launch_pdl(pa_angles_kernel, dim3((p.n_cols * p.half + 127) / 128), dim3(128), 0, st, p);
 }
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st) {
   pa_sigmoid_mul_kernel<<<n_cols, 256, 0, st>>>(p);

@@ -76,6 +76,75 @@ def test_rope_append_matches_oracle_bit_for_bit(hd, n_rot, theta, nH, nKV, pos, 
         assert not np.any(util.read_cache(eng, 0, 0, pos - 1, 1)[0] != util.read_cache(eng, 0, 0, pos - 1, 1)[0])
 
 
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_one_token_rope_is_the_float64_expression_bit_for_bit(dtype):
+    # One-token calls take cos / sin from the host's libm (as the oracle does) and rotate with f32-pair arithmetic that
+    # must reproduce fl32(fl64(fl64(a cos) -/+ fl64(b sin))) exactly, falling back to float64 instructions near a
+    # rounding boundary (about one output in 2^17): 2.4M rotated values per dtype, no differing bit allowed.
+    import torch
+    td = torch.float16 if dtype == "f16" else torch.float32
+    nH, nKV, hd, n_rot, theta = 16, 8, 128, 128, 1e6
+    eng = _engine(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=n_rot, rope_theta=theta, max_seq=40000, act_dtype=td)
+    qd, kvd = nH * hd, nKV * hd
+    rng = np.random.default_rng(5)
+    n_calls = 800
+    scales = [1.0, 20.0, 1e-3, 300.0]
+    bad_q = bad_k = 0
+    for it in range(n_calls):
+        pos = int(rng.integers(0, 39000))
+        sc = scales[it % len(scales)]
+        q = (rng.standard_normal(qd) * sc).astype(np.float32); k = (rng.standard_normal(kvd) * sc).astype(np.float32)
+        v = rng.standard_normal(kvd).astype(np.float32)
+        if dtype == "f16":
+            q, k, v = (po.h2f(po.f16_rne(x)) for x in (q, k, v))
+        if it % 7 == 0:
+            q[rng.integers(0, qd, 64)] = 0.0; k[rng.integers(0, kvd, 64)] = 0.0
+        q_rot = eng.rope_append(0, 0, pos, util.torch_dev(q[None], td), util.torch_dev(k[None], td), util.torch_dev(v[None], td))
+        gq = q_rot.cpu().numpy()[0]
+        gk, _ = util.read_cache(eng, 0, 0, pos, 1)
+        wq = po.rope_neox_f64(q, nH, hd, n_rot, pos, theta)
+        wk = po.rope_neox_f64(k, nKV, hd, n_rot, pos, theta)
+        bad_q += int(np.count_nonzero(gq.view(np.uint32) != wq.view(np.uint32)))
+        bad_k += int(np.count_nonzero(gk[0] != po.f16_rne(wk)))
+    assert bad_q == 0 and bad_k == 0, f"{bad_q} rotated q values and {bad_k} cache halves differ"
+
+
+def test_angle_table_is_refilled_when_a_graph_replay_may_have_rewritten_it():
+    # Wide calls (more than 64 angles) read cos / sin from a device table that the library fills once per (position,
+    # width) and reuses across layers.  A captured graph refills it on replay, so a stand-alone call that follows must
+    # not trust what it wrote there before the replay.
+    import torch
+    nH, nKV, hd, n_rot, theta, n_cols = 4, 2, 128, 128, 1e6, 32
+    eng = _engine(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=n_rot, rope_theta=theta, max_seq=4096, act_dtype=torch.float32, max_cols=n_cols)
+    qd, kvd = nH * hd, nKV * hd
+    q = po.normal(3, n_cols * qd).astype(np.float32).reshape(n_cols, qd)
+    k = po.normal(4, n_cols * kvd).astype(np.float32).reshape(n_cols, kvd)
+    dq, dk, dv = (util.torch_dev(x) for x in (q, k, k))
+    want = lambda pos: np.stack([po.rope_neox_f64(q[c], nH, hd, n_rot, pos + c, theta) for c in range(n_cols)])
+    close = lambda got, pos: int(np.count_nonzero(got.view(np.uint32) != want(pos).view(np.uint32))) <= 4   # device vs host sin/cos, last place
+    pos_a, pos_b = 1000, 2000
+    eng.rope_append(0, 0, pos_a, dq, dk, dv)
+    torch.cuda.synchronize()
+    cs = torch.cuda.Stream()
+    cs.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(cs):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=cs):
+            out_a = eng.rope_append(0, 0, pos_a, dq, dk, dv)
+            out_a2 = eng.rope_append(0, 0, pos_a, dq, dk, dv)      # same capture, same columns: shares the table
+    torch.cuda.current_stream().wait_stream(cs)
+    out_b = eng.rope_append(0, 0, pos_b, dq, dk, dv).cpu().numpy()
+    assert close(out_b, pos_b)
+    g.replay()                                                     # rewrites the table for pos_a
+    torch.cuda.synchronize()
+    assert close(out_a.cpu().numpy(), pos_a) and close(out_a2.cpu().numpy(), pos_a)
+    out_b2 = eng.rope_append(0, 0, pos_b, dq, dk, dv).cpu().numpy()   # same key as before the replay
+    assert close(out_b2, pos_b)
+    g.replay()
+    torch.cuda.synchronize()
+    assert close(out_a.cpu().numpy(), pos_a)
+
+
 def test_rope_table_mode_matches_ggml_recurrence_bit_for_bit():
     # the Flash engine's host-computed table: engine/qwen4exp.js:549-553, tests/reference/qsa_ref.mjs:99-110
     import torch
