@@ -423,7 +423,7 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
     }
   }
 #ifdef PA_TRACE
-  if (n_cols == 1) p.trace = trace_region(g_trace_call);   // the decode call that follows takes the same region
+  if (n_cols <= 15) p.trace = trace_region(g_trace_call);   // the decode call that follows takes the same region
 #endif
   CU_TRY(ctx, launch_rope_append(p, n_cols, st));
   ctx->stats.kernel_launches++;
@@ -551,6 +551,9 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
     vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit; vp.pre_stages = p.pre_stages;
+#ifdef PA_TRACE
+    vp.trace = p.trace;
+#endif
     vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);

@@ -28,7 +28,12 @@ namespace pa {
 
 #ifdef PA_TRACE   // development builds: per-CTA timestamps of the pipeline stages
 __device__ __forceinline__ unsigned long long pf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define PTR(slot) do { if (p.trace && lane == 0 && (slot) < 256) p.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + (slot)] = pf_gtime(); } while (0)
+// A predicated store, not a branch: the marks sit between .sync.aligned tensor instructions, which want the warp
+// converged.
+#define PTR(slot) do { if (p.trace) { \
+    unsigned long long* a_ = p.trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + ((slot) < 256 ? (slot) : 255); \
+    const unsigned long long t_ = pf_gtime(); \
+    asm volatile("{\n\t.reg .pred pq;\n\tsetp.eq.u32 pq, %0, 0;\n\t@pq st.global.u64 [%1], %2;\n\t}" :: "r"((unsigned)lane), "l"(a_), "l"(t_) : "memory"); } } while (0)
 #else
 #define PTR(slot) do {} while (0)
 #endif
@@ -341,6 +346,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // split-K: rows 0..63 are (column, head-of-group) pairs; with MODE 2 rows 64..127 repeat them for the low parts
     if (early) pdl_wait();
     pdl_trigger();
+    if (warp == 4) PTR(4);
     const bool is_lo = SK && row >= 64;
     const uint32_t lr = SK ? (row & 63u) : row;
     const uint32_t sk_c = lr / p.G, sk_hh = lr % p.G;
@@ -378,6 +384,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           }
         }
         if (c2 == HD / 128 - 1) mbar_arrive(BAR(Q_ISSUED, 0));   // every q load of this thread has been issued
+        if (warp == 4 && c2 == HD / 128 - 1) PTR(5);
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
           const int c = 2 * c2 + hc;

@@ -182,9 +182,9 @@ __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopePara
 
 
 // Prefill chunks of f16 activations with the rotated q stored as f16 (what the prefill kernel consumes): the same
-// arithmetic as the kernels above, eight elements per access.  One CTA per column; an item is a 16-byte vector of the
-// unrotated dims (copied; NaNs take the pattern the scalar path produces) or a pair of vectors (d .. d+7, d+half ..
-// d+half+7) of the rotated dims.  Four items per thread are in flight.
+// arithmetic as the kernels above.  One CTA per column, two passes: the rotated dims two at a time (every lane of
+// a warp does the same four rotations: mixed with copies, the few rotating lanes would hold their warps up), then
+// 16-byte vectors of everything that is only copied (NaNs take the pattern the scalar path produces).
 __device__ __forceinline__ uint32_t fix_nan2(uint32_t w, bool cache) {
   // per half: NaN -> 0x7fff (q, cvt.rn.f16.f32 of a NaN) or sign | 0x7e00 (cache, f16_rne)
   uint32_t out = w;
@@ -206,62 +206,80 @@ __global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParam
   if (!p.trigger_early) pdl_trigger();
   for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) s_g[i] = p.n_ang ? p.ang[col * half + i] : p.angles[(uint64_t)col * half + i];
   __syncthreads();
-  const uint32_t rv = half / 8, cv = (hd - p.n_rot) / 8, per_head = rv + cv, vv = hd / 8;
-  const uint32_t nq = p.q ? p.q_heads * per_head : 0, nk = p.k ? p.kv_heads * per_head : 0, nv = p.v ? p.kv_heads * vv : 0;
-  const uint32_t total = nq + nk + nv, kvd = p.kv_heads * hd;
+  const uint32_t kvd = p.kv_heads * hd;
   const __half* qs = reinterpret_cast<const __half*>(p.q) + (uint64_t)col * p.q_col_stride;
   const __half* ks = reinterpret_cast<const __half*>(p.k) + (uint64_t)col * p.kv_col_stride;
   const __half* vs = reinterpret_cast<const __half*>(p.v) + (uint64_t)col * p.kv_col_stride;
   __half* qd = reinterpret_cast<__half*>(p.q_out) + (uint64_t)col * p.q_out_col_stride;
   __half* kd = p.k_cache + (p.cache_row0 + col) * (uint64_t)kvd;
   __half* vd = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd;
-  for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * blockDim.x) {
-    uint4 A[4], B[4];
-    const __half* src[4]; __half* dst[4]; uint32_t jj[4]; int kind[4];   // kind 0: q, 1: k, 2: v
+  const uint32_t nqh = p.q ? p.q_heads : 0, nkh = p.k ? p.kv_heads : 0;
+
+  // ---- rotated dims: an item is two adjacent dims (d, d + 1) with their partners (d + half, d + half + 1) of one
+  //      head, so every lane of a warp carries the same four rotations ----
+  {
+    const uint32_t per = half / 2, total = (nqh + nkh) * per;
+    for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 2 * blockDim.x) {
+      uint32_t A[2], B[2]; const __half* src[2]; __half* dst[2]; uint32_t dd[2]; int kind[2];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const uint32_t w = w0 + u * blockDim.x;
-      kind[u] = -1;
-      if (w >= total) continue;
-      if (w >= nq + nk) {
-        const uint32_t x = w - nq - nk;
-        kind[u] = 2; jj[u] = rv; src[u] = vs + 8 * x; dst[u] = vd + 8 * x;
-      } else {
-        const bool is_q = w < nq;
-        const uint32_t ww = is_q ? w : w - nq, head = ww / per_head, j = ww % per_head;
-        const uint32_t d = j < rv ? 8 * j : p.n_rot + 8 * (j - rv);
-        kind[u] = is_q ? 0 : 1; jj[u] = j;
-        src[u] = (is_q ? qs + (uint64_t)head * p.q_head_stride : ks + (uint64_t)head * hd) + d;
-        dst[u] = (is_q ? qd + (uint64_t)head * hd : kd + (uint64_t)head * hd) + d;
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t w = w0 + u * blockDim.x;
+        kind[u] = -1;
+        if (w >= total) continue;
+        const uint32_t head = w / per, d = 2 * (w % per);
+        const bool is_q = head < nqh;
+        kind[u] = is_q ? 0 : 1; dd[u] = d;
+        src[u] = (is_q ? qs + (uint64_t)head * p.q_head_stride : ks + (uint64_t)(head - nqh) * hd) + d;
+        dst[u] = (is_q ? qd + (uint64_t)head * hd : kd + (uint64_t)(head - nqh) * hd) + d;
+        A[u] = *reinterpret_cast<const uint32_t*>(src[u]);
+        B[u] = *reinterpret_cast<const uint32_t*>(src[u] + half);
       }
-      A[u] = *reinterpret_cast<const uint4*>(src[u]);
-      if (jj[u] < rv) B[u] = *reinterpret_cast<const uint4*>(src[u] + half);
-    }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (kind[u] < 0) continue;
-      const bool cache = kind[u] != 0;
-      if (jj[u] >= rv) {
+      for (int u = 0; u < 2; ++u) {
+        if (kind[u] < 0) continue;
+        const bool cache = kind[u] != 0;
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&A[u])), b = __half22float2(*reinterpret_cast<const __half2*>(&B[u]));
+        const Angle g0 = s_g[dd[u]], g1 = s_g[dd[u] + 1];
+        const float ra0 = rot_exact(a.x, b.x, g0, true), ra1 = rot_exact(a.y, b.y, g1, true);
+        const float rb0 = rot_exact(b.x, a.x, g0, false), rb1 = rot_exact(b.y, a.y, g1, false);
+        auto h = [&](float x) -> uint32_t { return cache ? __half_as_ushort(f16_rne(x)) : __half_as_ushort(__float2half_rn(x)); };
+        *reinterpret_cast<uint32_t*>(dst[u]) = h(ra0) | (h(ra1) << 16);
+        *reinterpret_cast<uint32_t*>(dst[u] + half) = h(rb0) | (h(rb1) << 16);
+      }
+    }
+  }
+  // ---- everything else: 16-byte vectors of the unrotated dims of q and k, and all of v ----
+  {
+    const uint32_t cv = (hd - p.n_rot) / 8, vv = hd / 8;
+    const uint32_t nq = nqh * cv, nk = nkh * cv, nv = p.v ? p.kv_heads * vv : 0, total = nq + nk + nv;
+    for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * blockDim.x) {
+      uint4 A[4]; __half* dst[4]; int kind[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t w = w0 + u * blockDim.x;
+        kind[u] = -1;
+        if (w >= total) continue;
+        const __half* src;
+        if (w >= nq + nk) {
+          const uint32_t x = w - nq - nk;
+          kind[u] = 1; src = vs + 8 * x; dst[u] = vd + 8 * x;
+        } else {
+          const bool is_q = w < nq;
+          const uint32_t ww = is_q ? w : w - nq, head = ww / cv, d = p.n_rot + 8 * (ww % cv);
+          kind[u] = is_q ? 0 : 1;
+          src = (is_q ? qs + (uint64_t)head * p.q_head_stride : ks + (uint64_t)head * hd) + d;
+          dst[u] = (is_q ? qd + (uint64_t)head * hd : kd + (uint64_t)head * hd) + d;
+        }
+        A[u] = *reinterpret_cast<const uint4*>(src);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (kind[u] < 0) continue;
+        const bool cache = kind[u] != 0;
         uint4 o = A[u];
         o.x = fix_nan2(o.x, cache); o.y = fix_nan2(o.y, cache); o.z = fix_nan2(o.z, cache); o.w = fix_nan2(o.w, cache);
         *reinterpret_cast<uint4*>(dst[u]) = o;
-        continue;
       }
-      const __half* ah = reinterpret_cast<const __half*>(&A[u]);
-      const __half* bh = reinterpret_cast<const __half*>(&B[u]);
-      uint4 oa, ob;
-      unsigned short* oah = reinterpret_cast<unsigned short*>(&oa);
-      unsigned short* obh = reinterpret_cast<unsigned short*>(&ob);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float a = __half2float(ah[e]), b = __half2float(bh[e]);
-        const Angle g = s_g[8 * jj[u] + e];
-        const float ra = rot_exact(a, b, g, true), rb = rot_exact(b, a, g, false);
-        oah[e] = cache ? __half_as_ushort(f16_rne(ra)) : __half_as_ushort(__float2half_rn(ra));
-        obh[e] = cache ? __half_as_ushort(f16_rne(rb)) : __half_as_ushort(__float2half_rn(rb));
-      }
-      *reinterpret_cast<uint4*>(dst[u]) = oa;
-      *reinterpret_cast<uint4*>(dst[u] + half) = ob;
     }
   }
 }
