@@ -404,6 +404,7 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
                             uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false) {
   RopeParams p{};
   p.q_out_f16 = q_out_f16;
+  if (q_out_f16 == 2) p.q_lo_offset = (uint64_t)ctx->cfg.max_cols * ctx->q_dim;   // second half of the f32-sized q_rot buffer
   p.trigger_early = in_layer_call ? 1u : 0u;
   p.q = q; p.q_col_stride = qcs; p.q_head_stride = qhs; p.q_heads = q_heads; p.q_out = q_out; p.q_out_col_stride = q_out_cs;
   p.k = k; p.v = v; p.kv_col_stride = kvcs; p.kv_heads = ctx->cfg.n_kv_heads;
@@ -500,7 +501,7 @@ struct FusedFront { const void* k; const void* v; bool append; uint32_t pos; };
 
 static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false,
-                       bool exchange = false, const FusedFront* fz = nullptr) {
+                       bool exchange = false, const FusedFront* fz = nullptr, const void* q_lo = nullptr) {
   pa_ctx* ctx = L->ctx;
   if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
   if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
@@ -547,7 +548,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     const uint64_t seq_off = (uint64_t)items[0].seq * L->max_seq * ctx->kv_dim;
     if (int rc = make_cache_map(ctx, &tm_k, L->k + seq_off, max_rows, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
     if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, max_rows, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
-    vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs;
+    vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs; vp.q_lo = q_lo;
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
     vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit; vp.pre_stages = p.pre_stages;
@@ -567,7 +568,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
 #ifdef PA_TRACE
   c.trace = p.trace;
 #endif
-  const bool lo_rec = verify_tc && !(ctx->cfg.flags & PA_FLAG_FAST);   // the hi/lo verify kernel writes two records per split
+  const bool lo_rec = false;
   const uint32_t rs = lo_rec ? 2 * ns : ns;
   c.lo_records = lo_rec ? 1 : 0;
   c.o_row_stride = (uint64_t)rs * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
@@ -703,6 +704,10 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer: null q, k, v or out");
   if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer", !sharded)) return rc;
   cudaSetDevice(ctx->device);
+  // A k-token block on the tensor-core split-K kernel in its hi/lo form takes q as two f16 planes (high and low parts),
+  // which the RoPE kernel writes directly: nothing is left to convert in the attention kernel's prologue.
+  const bool planes = mode != PA_MODE_PREFILL && n_cols * ctx->G > 8 && n_cols * ctx->G <= (uint32_t)kMaxRows && !(ctx->cfg.flags & PA_FLAG_FAST) &&
+                      !getenv("POOLED_ATTN_VERIFY_MMA_SYNC");
   if (sharded) {
     // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
     const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
@@ -712,9 +717,12 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
       return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true, &fz);
     }
     if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
-                                  owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, 0, true))
+                                  owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, planes ? 2 : 0, true))
       return rc;
     pa_item it{seq, pos, n_cols, 0};
+    if (planes)
+      return decode_impl(L, &it, 1, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true,
+                         nullptr, reinterpret_cast<const __half*>(ctx->q_rot) + (size_t)ctx->cfg.max_cols * ctx->q_dim);
     return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true);
   }
   // the decode / verify kernel carries at most 64 query rows per kv head; wider passes are prefill chunks
@@ -728,11 +736,14 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic)
   if (!ctx->core_only)
     if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
-                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : 0, true))
+                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : (planes ? 2 : 0), true))
       return rc;
   if (prefill)
     return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
   pa_item it{seq, pos, n_cols, 0};
+  if (planes)
+    return decode_impl(L, &it, 1, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", !ctx->core_only, false, nullptr,
+                       reinterpret_cast<const __half*>(ctx->q_rot) + (size_t)ctx->cfg.max_cols * ctx->q_dim);
   return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", !ctx->core_only);
 }
 

@@ -51,6 +51,7 @@ struct RopeParams {
   uint32_t trigger_early;      // 1: the dependent kernel may start before this one's own wait (inside a layer call only)
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
   void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
+  uint64_t q_lo_offset;    // q_out_f16 == 2: f16 high parts at q_out, f16 low parts (x - fl16(x)) this many halves later
   const void* k; const void* v; uint64_t kv_col_stride; uint32_t kv_heads;  // k == nullptr: skip
   __half* k_cache; __half* v_cache; uint64_t cache_row0;                    // row of column 0
   uint32_t hd, n_rot, pos, mode;
@@ -75,6 +76,7 @@ struct SigmoidParams {
 
 struct PrefillParams {
   const void* q; int q_f16; uint64_t q_col_stride, q_head_stride;
+  const void* q_lo;             // split-K, f16 q: the low parts as a second f16 array of the same shape (nullptr: none)
   const void* gate; uint64_t gate_col_stride, gate_head_stride;
   void* out; uint64_t out_col_stride; int act_f16;
   uint32_t seq, pos, n_cols, n_heads, G, max_seq;

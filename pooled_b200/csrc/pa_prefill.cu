@@ -172,16 +172,17 @@ constexpr int kSBuf = 3;     // S / P tiles in tensor memory: S(j+2) is formed w
 // MODE 1 / 2: split-K form for a k-token verify block: one CTA per (split of the KV sequence, kv head); the rows of the
 //   tile are (column, head of the GQA group) pairs, at most 64 of them, and the CTA writes an unnormalised (o, m, l)
 //   partial per row for the LSE combine.  MODE 2 keeps about 22 bits of q and of the softmax weights at no extra
-//   tensor work: rows 0..63 carry the f16 high parts (q_hi, P_hi), rows 64..127 the low parts (q_lo, P_lo) of the same
-//   query rows; S_hi + S_lo is formed in the softmax, O_hi + O_lo in the epilogue.
-constexpr int kXStride = 65;   // floats per row of the hi/lo exchange buffer (odd: no bank conflicts)
+//   tensor work: even rows carry the f16 high parts (q_hi, P_hi), odd rows the low parts (q_lo, P_lo) of the same
+//   query row, so the two sit in neighbouring lanes of one warp: S_hi + S_lo is one shuffle per score in the
+//   softmax, O_hi + O_lo one per output in the epilogue, and the split writes a single record per query row.
 
 template <int HD, int MODE>
 struct PfSmem {
-  static constexpr int NK = 3, NV = MODE == 2 ? 2 : 3;   // K ring and V ring depth (the scores run two tiles ahead)
+  static constexpr int NK = 3, NV = MODE == 0 ? 3 : 2;   // K ring and V ring depth (the scores run two tiles ahead); split-K
+                                                         // leaves 32 KB free so that its CTAs can join SMs that still run a small kernel
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
   static constexpr int QS_BYTES = HD * 128;         // upper half of the head dims of Q: [HD/128][128 rows][128 B]
-  static constexpr int X_BYTES = MODE == 2 ? kBM * kXStride * 4 : 0;   // S rows swapped between the hi and lo halves
+  static constexpr int X_BYTES = 0;
   static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
   static constexpr int TOTAL = 1024 + OFF_BAR + 256;
   // tensor memory columns: lower half of Q (HD/4: f16 pairs) | S0 S1 S2 (64 each; P overwrites the first 32 of
@@ -200,10 +201,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 24);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 25);
   volatile uint32_t* s_err = s_tmem + 1;
   const uint32_t bar0 = smem_u32(bars);
-  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23 };
+  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23, Q_SENT = 24 };
   uint8_t* q_s = base + L::OFF_Q;
   auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
@@ -231,6 +232,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     mbar_init(BAR(O_DONE, 0), 1);
     mbar_init(BAR(Q_FULL, 0), 128);
     mbar_init(BAR(Q_ISSUED, 0), 128);
+    mbar_init(BAR(Q_SENT, 0), 128);
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -256,8 +258,11 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NK, u = j / NK;
         if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
-        // ahead of the wait only a few tiles go out: a long burst would queue in front of the q loads that follow it
-        if (early && j == p.pre_stages) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
+        // split-K: tile 0 may go out at once (ahead of the wait if the caller allows); the next one only when the
+        // requests for the query rows are on their way (a burst of tiles would queue in front of them), and the
+        // third, whose slot stages the query rows, when those have been consumed
+        if (SK && j == ((early && p.pre_stages == 0) ? 0u : 1u)) mbar_wait(BAR(Q_SENT, 0), 0, s_err, WAIT_QFULL);
+        if (SK && j == 2) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
@@ -273,7 +278,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NV, u = j / NV;
         if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
-        if (early && j + 1 == p.pre_stages) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
+        if (SK && j == 1) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);   // slot 1 stages query rows until then
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
@@ -343,16 +348,48 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ softmax + epilogue ----
     const uint32_t qd = warp - 4, row = qd * 32 + lane;
     const uint32_t lane_addr = (qd * 32) << 16;
-    // split-K: rows 0..63 are (column, head-of-group) pairs; with MODE 2 rows 64..127 repeat them for the low parts
-    if (early) pdl_wait();
-    pdl_trigger();
-    if (warp == 4) PTR(4);
-    const bool is_lo = SK && row >= 64;
-    const uint32_t lr = SK ? (row & 63u) : row;
+    // split-K: a (column, head-of-group) pair per row; MODE 2: per two rows (even: high parts, odd: low parts)
+    const bool is_lo = SK && (PREC ? (row & 1u) != 0 : row >= 64);
+    const uint32_t lr = SK ? (PREC ? row >> 1 : (row & 63u)) : row;
     const uint32_t sk_c = lr / p.G, sk_hh = lr % p.G;
     const uint32_t head = SK ? g * p.G + sk_hh : h;
     const bool live = SK ? (lr < p.n_cols * p.G && (PREC || !is_lo)) : row < rows_valid;
-    float* x_s = reinterpret_cast<float*>(base + L::OFF_X);
+    // ---- split-K: the few query rows are fetched by all 128 threads at once, 16 bytes per request, straight into
+    //      shared memory (cp.async: no registers held, every request in flight together), into the K and the V slot
+    //      the producers leave alone until Q_ISSUED (32 rows each); a row's chunks are XOR-swizzled so that the
+    //      per-row reads below do not all hit one bank.  (One thread loading its own 1 KB row needs the loads in register-sized batches,
+    //      a memory round trip each: 4.8 us between the wait and the first MMA.) ----
+    auto stage_row = [&](uint32_t pr) {
+      return (pr < 32 ? base + L::OFF_K + 2 * L::KV_BYTES : base + L::OFF_V + L::KV_BYTES - (size_t)32 * (HD * 4)) + (size_t)pr * (HD * 4);
+    };
+    // q as f32 (this kernel splits it), as f16 (no low part), or as two f16 planes, high and low parts, which the
+    // RoPE kernel of a layer call writes: then a staged row is [high HD halves][low HD halves] and nothing is left
+    // to convert here (the f32 -> f16 conversions of 128 x HD elements took 3 us on four warps)
+    const bool planes = SK && p.q_f16 && p.q_lo != nullptr;
+    const uint32_t q_es = p.q_f16 ? 2u : 4u, q_ch = planes ? HD * 4 / 16 : HD * q_es / 16;     // 16-byte chunks per staged row
+    if (early) pdl_wait();
+    pdl_trigger();
+    if (warp == 4) PTR(4);
+    if (SK) {
+      const uint32_t pairs = p.n_cols * p.G, st_tid = tid - 128, total = pairs * q_ch;
+      for (uint32_t idx = st_tid; idx < total; idx += 128) {
+        const uint32_t pr = idx / q_ch, c = idx % q_ch;
+        const uint32_t half_ch = HD * 2 / 16;
+        const bool lo_plane = planes && c >= half_ch;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(lo_plane ? p.q_lo : p.q) +
+                             ((uint64_t)(p.col0 + pr / p.G) * p.q_col_stride + (uint64_t)(g * p.G + pr % p.G) * p.q_head_stride) * q_es +
+                             (uint64_t)(lo_plane ? c - half_ch : c) * 16;
+        const uint32_t dst = smem_u32(stage_row(pr) + ((c ^ (pr & 7u)) << 4));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      mbar_arrive(BAR(Q_SENT, 0));
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      named_bar_sync(1, 128);
+      if (warp == 4) PTR(5);
+    }
+    const uint8_t* my_stage = stage_row(lr & 63u);
+    auto stage_ld = [&](uint32_t c) { return *reinterpret_cast<const uint4*>(my_stage + ((c ^ (lr & 7u)) << 4)); };
     // ---- this thread's Q row -> f16 pairs: lower half of the dims to tensor memory, upper half to shared memory ----
     {
       const uint64_t off = (uint64_t)(SK ? p.col0 + (live ? sk_c : 0) : c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)head * p.q_head_stride;
@@ -365,14 +402,18 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c2 * 128);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const uint4 x = (live && !is_lo) ? src[i] : make_uint4(0, 0, 0, 0);     // f16 q has no low part
+            const uint32_t cb = (planes && is_lo) ? HD * 2 / 16 : 0;
+            const uint4 x = (live && (planes || !is_lo)) ? (SK ? stage_ld(cb + c2 * 16 + i) : src[i]) : make_uint4(0, 0, 0, 0);   // plain f16 q has no low part
             w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
           }
         } else {
           const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c2 * 128);
           float4 xs[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) xs[i] = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int i = 0; i < 32; ++i) {
+            if (SK) { const uint4 r4 = live ? stage_ld(c2 * 32 + i) : make_uint4(0, 0, 0, 0); xs[i] = *reinterpret_cast<const float4*>(&r4); }
+            else xs[i] = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float4 x = xs[i];
@@ -383,8 +424,12 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
-        if (c2 == HD / 128 - 1) mbar_arrive(BAR(Q_ISSUED, 0));   // every q load of this thread has been issued
-        if (warp == 4 && c2 == HD / 128 - 1) PTR(5);
+        if (c2 == HD / 128 - 1) {
+          // this thread is done with the staging area: the producers may fetch into it (and may send the tiles they
+          // held back so that the early burst would not queue in front of the q requests)
+          fence_proxy_async();
+          mbar_arrive(BAR(Q_ISSUED, 0));
+        }
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
           const int c = 2 * c2 + hc;
@@ -424,14 +469,9 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
       }
       if (PREC) {
-        // S = S_hi + S_lo: the two halves of a query row swap their score rows through shared memory
+        // S = S_hi + S_lo: the two rows of a query row are neighbouring lanes
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) x_s[row * kXStride + i] = s[i];
-        named_bar_sync(1, 128);
-        const float* xp = x_s + (row ^ 64u) * kXStride;
-#pragma unroll
-        for (int i = 0; i < kBN; ++i) s[i] += xp[i];
-        named_bar_sync(1, 128);   // everyone has read before the next tile's rows are written
+        for (int i = 0; i < kBN; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 1);
       }
       if (warp == 4 && j < 10) PTR(9 + 6 * j);
       // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
@@ -487,24 +527,26 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const float inv_l = 1.f / l_sum;
     const uint32_t col = c0 + row;
     if (SK) {
-      // unnormalised partial (o, m, l) of this split for the LSE combine.  MODE 2: the low-part rows write a record of
-      // their own right after the used splits' records, with the same m and l = 0: the combine adds its o with the
-      // same weight and nothing to the denominator, which is exactly O_hi + O_lo.
+      // unnormalised partial (o, m, l) of this split for the LSE combine.  MODE 2: O = O_hi + O_lo, the odd lane's
+      // row added to the even lane's, which writes the record (m and l are the same in both)
       const uint64_t prow = (uint64_t)(p.col0 + sk_c) * p.n_heads + head;
-      const uint32_t tiles_all = (p.n_rows + kBN - 1) / kBN, tps_all = (tiles_all + p.n_splits - 1) / p.n_splits;
-      const uint32_t used = (tiles_all + tps_all - 1) / tps_all;
-      const uint64_t slot = prow * (PREC ? 2 * p.n_splits : p.n_splits) + (is_lo ? used : 0) + blockIdx.x;
+      const uint64_t slot = prow * p.n_splits + blockIdx.x;
+      const bool writer = live && !is_lo;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         float o[32];
         tmem_ld32(t_o + c * 32 + lane_addr, o);
-        if (live) {
+        if (PREC) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], 1);
+        }
+        if (writer) {
           float4* dst = reinterpret_cast<float4*>(p.part_o + slot * HD + c * 32);
 #pragma unroll
           for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
       }
-      if (live) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = is_lo ? 0.f : l_sum; }
+      if (writer) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
     } else {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {

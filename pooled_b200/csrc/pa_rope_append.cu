@@ -94,7 +94,12 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
   }
   if (is_q) {
     const uint64_t o = (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
-    if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
+    if (p.q_out_f16 == 2) {   // high and low f16 parts for the verify kernel's hi / lo rows
+      __half* dst = reinterpret_cast<__half*>(p.q_out) + o;
+      const __half ha = __float2half_rn(ra), hb = __float2half_rn(rb);
+      dst[d0] = ha; dst[d1] = hb;
+      dst[p.q_lo_offset + d0] = __float2half_rn(ra - __half2float(ha)); dst[p.q_lo_offset + d1] = __float2half_rn(rb - __half2float(hb));
+    } else if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
     else { float* dst = reinterpret_cast<float*>(p.q_out) + o; dst[d0] = ra; dst[d1] = rb; }
   } else {
     __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
@@ -170,7 +175,12 @@ __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopePara
       }
       if (is_q) {
         const uint64_t o = (uint64_t)col * p.q_out_col_stride + (uint64_t)head * hd;
-        if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
+        if (p.q_out_f16 == 2) {   // high and low f16 parts for the verify kernel's hi / lo rows
+      __half* dst = reinterpret_cast<__half*>(p.q_out) + o;
+      const __half ha = __float2half_rn(ra), hb = __float2half_rn(rb);
+      dst[d0] = ha; dst[d1] = hb;
+      dst[p.q_lo_offset + d0] = __float2half_rn(ra - __half2float(ha)); dst[p.q_lo_offset + d1] = __float2half_rn(rb - __half2float(hb));
+    } else if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
         else { float* dst = reinterpret_cast<float*>(p.q_out) + o; dst[d0] = ra; dst[d1] = rb; }
       } else {
         __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)kvd + (uint64_t)head * hd;
@@ -311,7 +321,7 @@ __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
   auto al16 = [](const void* x) { return ((uintptr_t)x & 15) == 0; };
   const bool vec = n_cols >= 16 && p.mode == PA_ROPE_F64 && (p.angles || p.n_ang) && p.in_f16 && p.n_rot % 16 == 0 && p.n_rot <= 256 && p.hd % 8 == 0 &&
-                   (!p.q || (p.q_out_f16 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
+                   (!p.q || (p.q_out_f16 == 1 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
                    (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0));
   if (vec) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
   if (n_cols >= 16) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
