@@ -858,8 +858,8 @@ extern "C" int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uin
 extern "C" size_t pa_exchange_bytes(pa_ctx* ctx, uint32_t world, uint32_t max_rows) {
   if (!ctx || world < 1 || world > 8 || max_rows < 1) return 0;
   const size_t n_slices = ctx->cfg.head_dim / 64;
-  const size_t blk = (size_t)max_rows * (ctx->cfg.head_dim + 2 * n_slices) * 4;   // o rows + (m, l) per (row, slice)
-  return 2 * (size_t)world * blk + 2 * (size_t)world * max_rows * n_slices * 4;    // + one flag per (parity, rank, row, slice)
+  const size_t blk = (size_t)max_rows * (ctx->cfg.head_dim + 2 * n_slices) * 8;   // {value, tag} entries: o rows + (m, l) per (row, slice)
+  return 2 * (size_t)world * blk;                                                  // two parities x world source ranks
 }
 
 extern "C" int pa_shared_alloc(pa_ctx* ctx, size_t bytes, void** dev_ptr, void* ipc_handle_out) {

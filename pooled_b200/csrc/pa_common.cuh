@@ -205,10 +205,10 @@ struct ItemList {
 };
 
 // Peer exchange of merged (o, m, l) records between the GPUs of one box.  Every rank owns one buffer that all ranks
-// (itself included) write into with plain stores over NVLink; peer[r] is rank r's buffer as seen from this GPU.
-// Layout of a buffer, in floats, for parity p in {0,1} and source rank s: block (p * world + s) of max_rows * (hd +
-// 2 * hd/64) floats (o rows first, then (m, l) per (row, 64-dim slice)); after all blocks, one uint32 flag per
-// (p, s, row, slice).
+// (itself included) write into with plain 8-byte stores over NVLink; peer[r] is rank r's buffer as seen from this
+// GPU.  Layout of a buffer, in 8-byte entries {f32 value, u32 tag}, for parity p in {0,1} and source rank s: block
+// (p * world + s) of max_rows * (hd + 2 * hd/64) entries (o rows first, then (m, l) per (row, 64-dim slice)).  The
+// tag is the call counter + 1: a receiver spins on an entry until it carries the current call's tag.
 struct ExchangeView {
   float* peer[8];
   uint32_t world, rank, max_rows, hd;

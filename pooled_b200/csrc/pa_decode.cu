@@ -689,7 +689,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   s_acc[grp][ln] = acc;
   __syncthreads();
   CTR(3);
-  __shared__ float s_xm[8], s_xl[8];
   __shared__ unsigned int s_epoch;
   float t = 0.f;
   if (tid < 64) {
@@ -700,47 +699,61 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   }
   if (p.exchange) {
     // ---- publish this rank's record slice to every rank, wait for theirs, merge across ranks ----
+    // Every value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands whole, so
+    // the receiver spins on the words themselves and no flag, fence or second round trip is needed.
     const ExchangeView& x = p.xc;
     const uint32_t n_slices = HD / 64;
     if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(x.ctr);
     __syncthreads();
     const uint32_t epoch = s_epoch, parity = epoch & 1u, tag = epoch + 1u;
-    const size_t blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // o rows, then (m, l) per (row, slice)
-    const size_t flags_off = (size_t)2 * x.world * blk;            // in floats (= uint32 words)
-    const size_t ml_off = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + slice) * 2;
+    const size_t blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // entries of 8 bytes: o rows, then (m, l) per (row, slice)
+    const size_t o_idx = (size_t)prow * HD + d;
+    const size_t ml_idx = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + slice) * 2;
+    auto put = [&](uint2* dst, float v) {
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    };
     for (uint32_t r = 0; r < x.world; ++r) {
-      float* dst = x.peer[r] + (size_t)(parity * x.world + x.rank) * blk;
-      if (tid < 64) dst[(size_t)prow * HD + d] = t;
-      if (tid == 64) { dst[ml_off] = M; dst[ml_off + 1] = Lsum; }
+      uint2* dst = reinterpret_cast<uint2*>(x.peer[r]) + (size_t)(parity * x.world + x.rank) * blk;
+      if (tid < 64) put(dst + o_idx, t);
+      if (tid == 64) { put(dst + ml_idx, M); put(dst + ml_idx + 1, Lsum); }
     }
-    __syncthreads();
-    if (tid < x.world) {
-      // one flag per (source rank, row, slice) in the destination's buffer.  The release store at system scope orders
-      // the CTA's record stores (which this thread observed through the barrier) before the flag.
-      unsigned int* f = reinterpret_cast<unsigned int*>(x.peer[tid] + flags_off) + ((size_t)(parity * x.world + x.rank) * x.max_rows + prow) * n_slices + slice;
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tag) : "memory");
-      // wait (bounded) for source rank `tid`'s slice of this row
-      const unsigned int* fl = reinterpret_cast<const unsigned int*>(x.peer[x.rank] + flags_off) + ((size_t)(parity * x.world + tid) * x.max_rows + prow) * n_slices + slice;
-      bool ok = false;
-      for (uint32_t it = 0; it < (1u << 22); ++it) {
-        unsigned int a;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(a) : "l"(fl) : "memory");
-        if (a == tag) { ok = true; break; }
-        if (it > 4096) __nanosleep(64);
-      }
-      if (!ok) atomicMax(p.err, 7u);   // a peer never published: report and carry on
-      const float* src = x.peer[x.rank] + (size_t)(parity * x.world + tid) * blk + ml_off;
-      s_xm[tid] = __ldcg(src); s_xl[tid] = __ldcg(src + 1);
-    }
-    __syncthreads();
     if (tid < 64) {
+      // every sweep requests all entries still missing at once (m, l and this thread's o of every source rank) and
+      // keeps those that carry the call's tag; bounded
+      const uint2* mine = reinterpret_cast<const uint2*>(x.peer[x.rank]);
+      float mr[8], lr[8], orr[8];
+      uint32_t pending = (1u << x.world) - 1u;
+      for (uint32_t it = 0; it < (1u << 20) && pending; ++it) {
+        uint32_t v[8][3], tg[8][3];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (!((pending >> r) & 1u)) continue;
+          const uint2* src = mine + (size_t)(parity * x.world + r) * blk;
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][0]), "=r"(tg[r][0]) : "l"(src + ml_idx) : "memory");
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][1]), "=r"(tg[r][1]) : "l"(src + ml_idx + 1) : "memory");
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][2]), "=r"(tg[r][2]) : "l"(src + o_idx) : "memory");
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (!((pending >> r) & 1u)) continue;
+          if (tg[r][0] == tag && tg[r][1] == tag && tg[r][2] == tag) {
+            mr[r] = __uint_as_float(v[r][0]); lr[r] = __uint_as_float(v[r][1]); orr[r] = __uint_as_float(v[r][2]);
+            pending &= ~(1u << r);
+          }
+        }
+        if (pending && it > 1024) __nanosleep(64);
+      }
+      if (pending) atomicMax(p.err, 7u);   // a peer never published: report and carry on
       float Mg = -3.0e38f;
-      for (uint32_t r = 0; r < x.world; ++r) Mg = fmaxf(Mg, s_xm[r]);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) if ((uint32_t)r < x.world && !((pending >> r) & 1u)) Mg = fmaxf(Mg, mr[r]);
       float Lg = 0.f, og = 0.f;
-      for (uint32_t r = 0; r < x.world; ++r) {
-        const float w = __expf(s_xm[r] - Mg);
-        Lg += s_xl[r] * w;
-        og += __ldcg(x.peer[x.rank] + (size_t)(parity * x.world + r) * blk + (size_t)prow * HD + d) * w;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if ((uint32_t)r >= x.world || ((pending >> r) & 1u)) continue;
+        const float w = __expf(mr[r] - Mg);
+        Lg += lr[r] * w;
+        og += orr[r] * w;
       }
       t = og; Lsum = Lg;
     }
