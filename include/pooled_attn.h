@@ -129,6 +129,16 @@ PA_API uint32_t pa_plan_splits(pa_ctx* ctx, uint32_t n_rows, uint32_t n_items);
 
 /* ---- the path, step by step ------------------------------------------------------------------------ */
 
+/* QK head-norm, the step before RoPE in the reference's attention glue.  Replaces the head_norm part of attn_glue /
+ * attn_glue_kv (engine/wgsl/qwen35.js:1112-1122, engine/wgsl/layer_fuse.js:112-125) with the arithmetic of its CPU
+ * twin (tests/reference/ref_q38.mjs:50-57, :163-164): per head, y = f32((x * inv) * w[d]), inv = 1/sqrt(mean(x^2) + eps),
+ * the mean accumulated in float64 in index order.  x, y: act_dtype [n_cols][col_stride], head h at h * head_stride
+ * (x == y allowed); w: f32 [head_dim] on the device (the q-norm or the k-norm weight).  A separate pass today: call it
+ * on q and on k before pa_attn_layer / pa_rope_append. */
+PA_API int pa_head_norm(pa_ctx* ctx, const void* x, uint64_t col_stride, uint64_t head_stride, uint32_t n_heads_x,
+                        uint32_t n_cols, const float* w, double eps, void* y, uint64_t y_col_stride,
+                        uint64_t y_head_stride, void* stream);
+
 /* RoPE.  Replaces rope_part / rope_part_mc (engine/wgsl/qwen35.js:386-404, :858-875), the full-head rope
  * (engine/wgsl/base.js:154-172) and the rotation inside attn_glue (engine/wgsl/qwen35.js:1124-1131).
  * x: act_dtype [n_cols][col_stride], head h at h * head_stride; y: f32 [n_cols][y_col_stride] with heads
@@ -190,10 +200,10 @@ PA_API int pa_shared_open(pa_ctx* ctx, const void* ipc_handle, void** dev_ptr);
 PA_API int pa_shared_close(pa_ctx* ctx, void* dev_ptr);
 PA_API int pa_exchange_init(pa_ctx* ctx, uint32_t rank, uint32_t world, void* const* bufs, uint32_t max_rows);
 /* pa_decode over this rank's shard with the cross-GPU merge inside the combine kernel: each CTA stores its merged
- * (o, m, l) slice into every rank's exchange buffer with plain stores over NVLink, raises a per-(row, slice) flag,
- * waits (bounded) for the other ranks' flags, merges and writes the gated output.  Every rank must make the same
- * call in the same order; every rank ends with the full result.  The arithmetic is attn_dec_combine(_g)'s
- * (engine/wgsl/attn_dec.js:215-287) applied to per-GPU records. */
+ * (o, m, l) slice into every rank's exchange buffer over NVLink, each value as one 8-byte {value, call tag} store,
+ * spins (bounded) on its own buffer until the other ranks' entries carry the call's tag, merges and writes the gated
+ * output.  Every rank must make the same call in the same order; every rank ends with the full result.  The
+ * arithmetic is attn_dec_combine(_g)'s (engine/wgsl/attn_dec.js:215-287) applied to per-GPU records. */
 PA_API int pa_decode_exchange(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q, int q_dtype,
                               uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
                               uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);

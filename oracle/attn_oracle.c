@@ -103,6 +103,23 @@ PO_API float po_h2f(uint16_t h) {
 PO_API void po_f16_rne_array(const float* x, uint16_t* h, size_t n) { for (size_t i = 0; i < n; i++) h[i] = po_f16_rne(x[i]); }
 PO_API void po_h2f_array(const uint16_t* h, float* x, size_t n) { for (size_t i = 0; i < n; i++) x[i] = po_h2f(h[i]); }
 
+/* ------------------------------------------------------------ head norm -- */
+
+/* QK head-norm, the step before RoPE in the reference's attention glue: per head,
+ * the sum of squares accumulated serially in double, inv = 1/sqrt(ss/n + eps),
+ * out[i] = f32((x[i] * inv) * w[i]).  tests/reference/ref_q38.mjs:50-57 (rmsnorm)
+ * as applied to the q and k heads at :163-164; the shader form (f32, thread 0
+ * serial) is engine/wgsl/qwen35.js:1112-1122. */
+PO_API void po_head_norm_f64(float* vec, uint32_t heads, uint32_t hd, const float* w, double eps) {
+  for (uint32_t h = 0; h < heads; h++) {
+    float* p = vec + (size_t)h * hd;
+    double ss = 0.0;
+    for (uint32_t i = 0; i < hd; i++) ss += (double)p[i] * (double)p[i];
+    double inv = 1.0 / sqrt(ss / (double)hd + eps);
+    for (uint32_t i = 0; i < hd; i++) p[i] = (float)(((double)p[i] * inv) * (double)w[i]);
+  }
+}
+
 /* ----------------------------------------------------------------- RoPE -- */
 
 /* NeoX rotation of the first n_rot dims of every head, pairs (i, i + n_rot/2),

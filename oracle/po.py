@@ -40,6 +40,7 @@ def lib():
         L.po_f16_rne_array.argtypes = [f32p, u16p, C.c_size_t]
         L.po_h2f_array.argtypes = [u16p, f32p, C.c_size_t]
         L.po_rope_neox_f64.argtypes = [f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_double, C.c_double]
+        L.po_head_norm_f64.argtypes = [f32p, C.c_uint32, C.c_uint32, f32p, C.c_double]
         L.po_rope_ggml_f32.argtypes = [f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_double, C.c_double]
         L.po_rope_table_f32.argtypes = [f32p, C.c_uint32, C.c_double, C.c_double]
         L.po_kv_append.argtypes = [f32p, f32p, C.c_uint32, C.c_uint64, u16p, u16p]
@@ -75,6 +76,22 @@ def h2f(h: np.ndarray) -> np.ndarray:
     x = np.empty(h.shape, dtype=np.float32)
     lib().po_h2f_array(_p(h, C.c_uint16), _p(x, C.c_float), h.size)
     return x
+
+
+def head_norm_f64(vec: np.ndarray, heads: int, hd: int, w: np.ndarray, eps: float) -> np.ndarray:
+    """QK head-norm on a copy: float32 [heads*hd], weight float32 [hd]."""
+    v = np.ascontiguousarray(vec, dtype=np.float32).copy()
+    ww = np.ascontiguousarray(w, dtype=np.float32)
+    lib().po_head_norm_f64(_p(v, C.c_float), heads, hd, _p(ww, C.c_float), float(eps))
+    return v
+
+
+def np_head_norm(vec: np.ndarray, heads: int, hd: int, w: np.ndarray, eps: float) -> np.ndarray:
+    """NumPy twin of head_norm_f64 (cumsum adds in index order, as the serial loop does)."""
+    x = np.asarray(vec, dtype=np.float32).reshape(heads, hd).astype(np.float64)
+    ss = np.cumsum(x * x, axis=1)[:, -1]
+    inv = 1.0 / np.sqrt(ss / hd + eps)
+    return ((x * inv[:, None]) * np.asarray(w, dtype=np.float32).astype(np.float64)[None, :]).astype(np.float32).reshape(-1)
 
 
 def rope_neox_f64(vec: np.ndarray, heads: int, hd: int, n_rot: int, pos: int, theta: float) -> np.ndarray:

@@ -265,6 +265,17 @@ class AttnEngine:
                                    gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
         return out
 
+    def head_norm(self, x: torch.Tensor, n_heads_x: int, w: torch.Tensor, eps: float, head_stride: int | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+        """QK head-norm of q or k before RoPE (the head_norm step of attn_glue, engine/wgsl/qwen35.js:1112-1122):
+        x [n_cols, stride] of act_dtype, w float32 [head_dim] on the device; in place unless `out` is given."""
+        assert w.dtype == torch.float32 and w.is_cuda and w.numel() == self.cfg.head_dim
+        y = x if out is None else out
+        hs = head_stride or self.cfg.head_dim
+        self._ck(self.L.pa_head_norm(self.ctx, self._p(x), x.stride(0), hs, n_heads_x, x.shape[0], self._p(w), float(eps), self._p(y), y.stride(0),
+                                     hs, self._st()))
+        return y
+
     def sigmoid_mul(self, a: torch.Tensor, g: torch.Tensor, g_head_stride: int | None = None):
         self._ck(self.L.pa_sigmoid_mul(self.ctx, self._p(a), a.stride(0), self._p(g), g.stride(0), g_head_stride or self.cfg.head_dim,
                                        a.shape[0], self._st()))

@@ -18,6 +18,7 @@ cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st);
+cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t n_heads, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
 cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
@@ -533,7 +534,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   if (fz) {
     p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
     p.k_cache = L->k; p.v_cache = L->v;
-    memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), 32 * sizeof(Angle));
+    memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), (size_t)(ctx->cfg.n_rot / 2) * sizeof(Angle));
   }
 #ifdef PA_TRACE
   p.trace = trace_region(g_trace_call++);
@@ -674,6 +675,23 @@ extern "C" int pa_prefill(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_co
                       (cudaStream_t)stream);
 }
 
+extern "C" int pa_head_norm(pa_ctx* ctx, const void* x, uint64_t col_stride, uint64_t head_stride, uint32_t n_heads_x, uint32_t n_cols, const float* w,
+                            double eps, void* y, uint64_t y_col_stride, uint64_t y_head_stride, void* stream) {
+  GUARD(ctx);
+  if (!x || !y || !w) return fail(ctx, PA_EINVAL, "pa_head_norm: null x, y or w");
+  if (n_cols == 0 || n_heads_x == 0) return PA_OK;
+  if (n_heads_x > 65535) return fail(ctx, PA_EINVAL, "pa_head_norm: at most 65535 heads per call");
+  if (ctx->cfg.head_dim > 512) return fail(ctx, PA_EUNSUPPORTED, "pa_head_norm: head_dim above 512");
+  if (!(eps >= 0.0)) return fail(ctx, PA_EINVAL, "pa_head_norm: eps must be a non-negative number");
+  cudaSetDevice(ctx->device);
+  HeadNormParams p{};
+  p.x = x; p.x_col_stride = col_stride; p.x_head_stride = head_stride; p.y = y; p.y_col_stride = y_col_stride; p.y_head_stride = y_head_stride;
+  p.w = w; p.eps = eps; p.hd = ctx->cfg.head_dim; p.f16 = ctx->cfg.act_dtype == PA_F16;
+  CU_TRY(ctx, launch_head_norm(p, n_cols, n_heads_x, (cudaStream_t)stream));
+  ctx->stats.kernel_launches++;
+  return PA_OK;
+}
+
 extern "C" int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const void* g, uint64_t g_col_stride, uint64_t g_head_stride, uint32_t n_cols,
                               void* stream) {
   GUARD(ctx);
@@ -689,11 +707,12 @@ extern "C" int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const
 
 // ------------------------------------------------------------------------------ one call --
 
-// One token of a partial-RoPE model (64 rotated dims, head_dim 256, at most 8 heads per kv head): the rotation of
-// q and k and the append ride inside the decode kernel (attn_glue_kv folded into attn_dec, in the reference's terms).
+// One token of a model with head_dim 256 and 64 rotary dims, or head_dim 128 rotated in full (at most 8 heads per kv
+// head): the rotation of q and k and the append ride inside the decode kernel (attn_glue_kv folded into attn_dec, in
+// the reference's terms).
 static bool can_fuse_front(const pa_ctx* ctx, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs, const void* k, const void* v) {
-  const uint32_t nr = ctx->cfg.n_rot;
-  return !ctx->core_only && n_cols == 1 && ctx->cfg.rope_mode == PA_ROPE_F64 && ctx->cfg.head_dim == 256 && ctx->G <= 8 && nr == 64 &&
+  const uint32_t nr = ctx->cfg.n_rot, hd = ctx->cfg.head_dim;
+  return !ctx->core_only && n_cols == 1 && ctx->cfg.rope_mode == PA_ROPE_F64 && ((hd == 256 && nr == 64) || (hd == 128 && nr == 128)) && ctx->G <= 8 &&
          !(qcs & 1) && !(qhs & 1) && !((uintptr_t)q & 7) && !((uintptr_t)k & 7) && !((uintptr_t)v & 7) && !getenv("POOLED_ATTN_NO_FUSE");
 }
 

@@ -47,7 +47,7 @@ struct DecSmem {
   static constexpr int PP = ROWS * 2;                // P^T row pitch (bytes)
   static constexpr int Q_BYTES = ROWS * QP * (PRECISE ? 2 : 1);
   static constexpr int P_BYTES = kT * PP * (PRECISE ? 2 : 1);
-  static constexpr int MISC = 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 1024;   // + the fused front's angles
+  static constexpr int MISC = 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 2048;   // + the fused front's angles
   static constexpr int fixed_bytes() { return Q_BYTES + P_BYTES + MISC; }
   static int stages_for(int smem_limit) {
     int s = (smem_limit - 1024 - fixed_bytes()) / (2 * SLOT);
@@ -87,7 +87,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   float* s_l = s_max + 4 * ROWS;                                // [4][ROWS]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_l + 4 * ROWS); // kfull, kempty, vfull, vempty [kMaxStages] each
   volatile uint32_t* s_err = reinterpret_cast<volatile uint32_t*>(bars + 4 * kMaxStages);
-  Angle* s_ang = reinterpret_cast<Angle*>(bars + 4 * kMaxStages + 8);   // [32], fused front only
+  Angle* s_ang = reinterpret_cast<Angle*>(bars + 4 * kMaxStages + 8);   // [64], fused front only
 
   const uint32_t kfull = smem_u32(bars), kempty = kfull + kMaxStages * 8, vfull = kempty + kMaxStages * 8,
                  vempty = vfull + kMaxStages * 8;
@@ -113,6 +113,14 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     return x;   // f16 input: the two halves, unconverted, in x.x -- nothing here waits for the load to land
   };
   auto q_load = [&](int idx) { return q_load_rd(idx / (HD / 2), (idx % (HD / 2)) * 2); };
+  // a hint only (L2 is the point of coherence: a line the predecessor rewrites afterwards is simply updated there)
+  auto q_pref_rd = [&](int row, int d) {
+    if ((uint32_t)row >= live_rows) return;
+    const uint32_t c = row / G, hh = row % G;
+    const uint64_t off = (uint64_t)(p.items.col0[item] + c) * p.q_col_stride + (uint64_t)(g * G + hh) * p.q_head_stride + d;
+    const void* a = p.q_f16 ? (const void*)(reinterpret_cast<const __half*>(p.q) + off) : (const void*)(reinterpret_cast<const float*>(p.q) + off);
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+  };
   auto act_cvt = [&](float2 raw) {
     if (!p.q_f16) return raw;
     const uint32_t u = __float_as_uint(raw.x);
@@ -132,11 +140,17 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   // token's own k / v row (rotary partners sit in lanes l and l ^ 16 of warp 0: one shuffle): rotated, rounded to f16,
   // stored to the cache, and kept in two registers to be placed into the tile the TMA fetched before (or while) it
   // was stored.
-  constexpr bool CAN_FUSE = NT == 1 && HD == 256;
+  // The two fused shapes: head_dim 256 with 64 rotary dims (the rest of a row is copied), and head_dim 128 rotated
+  // in full.  An item is two adjacent dims with their rotary partners; thread t takes items t, t + 128, ...
+  constexpr bool CAN_FUSE = NT == 1 && (HD == 256 || HD == 128);
+  constexpr int NRD = HD == 256 ? 64 : HD;            // rotated dims
+  constexpr int RHALF = NRD / 2, IPR = RHALF / 2;     // partner distance; items per row
+  constexpr int RIT = CAN_FUSE ? ROWS * IPR / kConsumers : 1;   // rotated items per thread (1 or 2)
+  constexpr int PPR = (HD - NRD) / 2;                 // unrotated pairs per row (96 or 0)
   const bool fused = CAN_FUSE && p.fused;
   const bool own_new = fused && p.append && tile1 == tiles;
-  float2 kx = make_float2(0.f, 0.f), vx = make_float2(0.f, 0.f);
-  uint32_t k_new2 = 0, v_new2 = 0;
+  float2 kx = make_float2(0.f, 0.f), vx = make_float2(0.f, 0.f), kxb = make_float2(0.f, 0.f);
+  uint32_t k_new2 = 0, v_new2 = 0, k_new2b = 0;       // head_dim 128: lanes of warp 0 carry K words t and t + 32
   auto rotate = [&](float2 x) {   // warp 0 only, all lanes
     const float2 y = make_float2(__shfl_xor_sync(0xffffffffu, x.x, 16), __shfl_xor_sync(0xffffffffu, x.y, 16));
     const int i = 2 * (lane & 15);
@@ -149,31 +163,55 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   if (warp < 4) {
     // Threads that index launch parameters differently are served one address at a time, each a miss of the constant
     // cache: far too slow for the critical path.  The angles go to shared memory while the predecessor still runs.
-    if (fused) reinterpret_cast<uint2*>(s_ang)[tid] = reinterpret_cast<const uint2*>(p.rope_ang)[tid];
+    if (fused) {
+#pragma unroll
+      for (int u = 0; u < RHALF / 32; ++u) reinterpret_cast<uint2*>(s_ang)[tid + u * kConsumers] = reinterpret_cast<const uint2*>(p.rope_ang)[tid + u * kConsumers];
+    }
+    if (Q_IN_REGS && p.prefetch_old_rows) {   // the CTA is ahead of its predecessor: bring the q lines to L2 meanwhile
+      if (fused) {
+#pragma unroll
+        for (int u = 0; u < RIT; ++u) { const int i = tid + u * kConsumers; q_pref_rd(i / IPR, 2 * (i % IPR)); }
+        if (PPR > 0) {
+#pragma unroll
+          for (int it = 2 * RIT; it < (Q_IN_REGS ? QLD : 1); it += 2) { const int idx = tid + (it - 2 * RIT) * kConsumers; q_pref_rd(idx / (PPR ? PPR : 1), NRD + 2 * (idx % (PPR ? PPR : 1))); }
+        }
+      } else {
+#pragma unroll
+        for (int it = 0; it < (Q_IN_REGS ? QLD : 1); it += 2) { const int idx = tid + it * kConsumers; q_pref_rd(idx / (HD / 2), (idx % (HD / 2)) * 2); }
+      }
+    }
     pdl_wait();      // q (and the partial buffers written at the end) belong to earlier kernels until here
     pdl_trigger();
     TR(4);
     if (Q_IN_REGS) {
       if (fused) {
-        qreg[0] = q_load_rd(tid >> 4, 2 * (tid & 15));
-        qreg[1 % (Q_IN_REGS ? QLD : 1)] = q_load_rd(tid >> 4, 2 * (tid & 15) + 32);
 #pragma unroll
-        for (int it = 2; it < (Q_IN_REGS ? QLD : 1); ++it) {
-          const int idx = tid + (it - 2) * kConsumers;
-          qreg[it] = q_load_rd(idx / 96, 64 + 2 * (idx % 96));
+        for (int u = 0; u < RIT; ++u) {
+          const int i = tid + u * kConsumers;
+          qreg[(2 * u) % (Q_IN_REGS ? QLD : 1)] = q_load_rd(i / IPR, 2 * (i % IPR));
+          qreg[(2 * u + 1) % (Q_IN_REGS ? QLD : 1)] = q_load_rd(i / IPR, 2 * (i % IPR) + RHALF);
+        }
+#pragma unroll
+        for (int it = 2 * RIT; it < (Q_IN_REGS ? QLD : 1); ++it) {
+          const int idx = tid + (it - 2 * RIT) * kConsumers;
+          qreg[it] = q_load_rd(idx / (PPR ? PPR : 1), NRD + 2 * (idx % (PPR ? PPR : 1)));
         }
       } else {
 #pragma unroll
         for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = q_load(tid + it * kConsumers);
       }
       if (own_new) {
+        auto ld2 = [&](const void* src, uint64_t off) {
+          float2 x = make_float2(0.f, 0.f);
+          if (p.q_f16) x.x = __uint_as_float(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(src) + off));
+          else x = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(src) + off);
+          return x;
+        };
         const uint64_t so = (uint64_t)g * HD + 2 * tid;
-        if (p.q_f16) {
-          kx.x = __uint_as_float(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(p.k_new) + so));
-          vx.x = __uint_as_float(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(p.v_new) + so));
-        } else {
-          kx = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.k_new) + so);
-          vx = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p.v_new) + so);
+        if (HD == 256) { kx = ld2(p.k_new, so); vx = ld2(p.v_new, so); }
+        else {
+          if (tid < 32) { kx = ld2(p.k_new, so); kxb = ld2(p.k_new, so + RHALF); }
+          if (tid < HD / 2) vx = ld2(p.v_new, so);
         }
       }
     } else {
@@ -257,38 +295,62 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   const int w = warp, r = lane >> 2, j = lane & 3;
 
   if (Q_IN_REGS) {
-#pragma unroll
-    for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) qreg[it] = act_cvt(qreg[it]);
-    if (own_new) { kx = act_cvt(kx); vx = act_cvt(vx); }
+    if (own_new) { kx = act_cvt(kx); vx = act_cvt(vx); kxb = act_cvt(kxb); }
     if (fused) {
-      const int row = tid >> 4, b2 = 2 * (tid & 15);
-      const float2 a = qreg[0], b = qreg[1 % (Q_IN_REGS ? QLD : 1)];
-      float2 ra, rb;   // the bits of the float64 expression the stand-alone RoPE kernel evaluates
-      ra.x = rot_exact(a.x, b.x, s_ang[b2], true);
-      ra.y = rot_exact(a.y, b.y, s_ang[b2 + 1], true);
-      rb.x = rot_exact(b.x, a.x, s_ang[b2], false);
-      rb.y = rot_exact(b.y, a.y, s_ang[b2 + 1], false);
-      q_store_rd(row, b2, ra);
-      q_store_rd(row, b2 + 32, rb);
 #pragma unroll
-      for (int it = 2; it < (Q_IN_REGS ? QLD : 1); ++it) {
-        const int idx = tid + (it - 2) * kConsumers;
-        q_store_rd(idx / 96, 64 + 2 * (idx % 96), qreg[it]);
+      for (int u = 0; u < RIT; ++u) {
+        const int i = tid + u * kConsumers, row = i / IPR, b2 = 2 * (i % IPR);
+        if ((uint32_t)row >= live_rows) {   // padding rows of the tile: zeros, no arithmetic
+          q_store_rd(row, b2, make_float2(0.f, 0.f)); q_store_rd(row, b2 + RHALF, make_float2(0.f, 0.f));
+          continue;
+        }
+        const float2 a = act_cvt(qreg[(2 * u) % (Q_IN_REGS ? QLD : 1)]), b = act_cvt(qreg[(2 * u + 1) % (Q_IN_REGS ? QLD : 1)]);
+        float2 ra, rb;   // the bits of the float64 expression the stand-alone RoPE kernel evaluates
+        ra.x = rot_exact(a.x, b.x, s_ang[b2], true);
+        ra.y = rot_exact(a.y, b.y, s_ang[b2 + 1], true);
+        rb.x = rot_exact(b.x, a.x, s_ang[b2], false);
+        rb.y = rot_exact(b.y, a.y, s_ang[b2 + 1], false);
+        q_store_rd(row, b2, ra);
+        q_store_rd(row, b2 + RHALF, rb);
       }
-      if (own_new && w == 0) kx = rotate(kx);
+#pragma unroll
+      for (int it = 2 * RIT; it < (Q_IN_REGS ? QLD : 1); ++it) {
+        const int idx = tid + (it - 2 * RIT) * kConsumers, rr = idx / (PPR ? PPR : 1), d = NRD + 2 * (idx % (PPR ? PPR : 1));
+        if (p.q_f16) {   // unrotated f16 values are their own high parts: the loaded bits go in as they are
+          *reinterpret_cast<uint32_t*>(q_hi + rr * QP + d * 2) = __float_as_uint(qreg[it].x);
+          if (PRECISE) *reinterpret_cast<uint32_t*>(q_lo + rr * QP + d * 2) = 0u;
+        } else {
+          q_store_rd(rr, d, qreg[it]);
+        }
+      }
+      if (own_new && w == 0) {
+        if (HD == 256) kx = rotate(kx);
+        else {
+          const int b2 = 2 * lane;
+          const float2 a = kx, b = kxb;
+          kx.x = rot_exact(a.x, b.x, s_ang[b2], true);   kx.y = rot_exact(a.y, b.y, s_ang[b2 + 1], true);
+          kxb.x = rot_exact(b.x, a.x, s_ang[b2], false); kxb.y = rot_exact(b.y, a.y, s_ang[b2 + 1], false);
+        }
+      }
     } else {
 #pragma unroll
-      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) q_store(tid + it * kConsumers, qreg[it]);
+      for (int it = 0; it < (Q_IN_REGS ? QLD : 1); ++it) q_store(tid + it * kConsumers, act_cvt(qreg[it]));
     }
     if (own_new) {
       auto h16 = [](float x) -> uint32_t {   // round to nearest even; NaN -> sign | 0x7e00, as the append kernel
         return x != x ? (((__float_as_uint(x) >> 16) & 0x8000u) | 0x7e00u) : (uint32_t)__half_as_ushort(__float2half_rn(x));
       };
       k_new2 = h16(kx.x) | (h16(kx.y) << 16);
+      k_new2b = h16(kxb.x) | (h16(kxb.y) << 16);
       v_new2 = h16(vx.x) | (h16(vx.y) << 16);
       const uint64_t ro = ((uint64_t)p.items.seq[item] * p.max_seq + (n_rows - 1)) * ((uint64_t)gridDim.y * HD) + (uint64_t)g * HD + 2 * tid;
-      *reinterpret_cast<uint32_t*>(p.k_cache + ro) = k_new2;
-      *reinterpret_cast<uint32_t*>(p.v_cache + ro) = v_new2;
+      if (HD == 256) {
+        *reinterpret_cast<uint32_t*>(p.k_cache + ro) = k_new2;
+        *reinterpret_cast<uint32_t*>(p.v_cache + ro) = v_new2;
+      } else {
+        if (tid < 32) { *reinterpret_cast<uint32_t*>(p.k_cache + ro) = k_new2; *reinterpret_cast<uint32_t*>(p.k_cache + ro + RHALF) = k_new2b; }
+        if (tid < HD / 2) *reinterpret_cast<uint32_t*>(p.v_cache + ro) = v_new2;
+      }
     }
   }
 
@@ -339,8 +401,13 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     mbar_wait(kfull + 8 * s, ph, s_err, WAIT_KFULL);
     if (i < 15) TR(8 + 8 * i);
     if (own_new && i == n_tiles - 1) {
-      const uint32_t rr = n_rows - 1 - tile_pos, c16g = tid >> 2;
-      *reinterpret_cast<uint32_t*>(k_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = k_new2;
+      const uint32_t rr = n_rows - 1 - tile_pos;
+      auto word_at = [&](uint8_t* slots, uint32_t wi) {   // 32-bit word wi of row rr in the swizzled tile
+        const uint32_t c16g = wi >> 2;
+        return reinterpret_cast<uint32_t*>(slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (wi & 3) * 4);
+      };
+      if (HD == 256) *word_at(k_slots, tid) = k_new2;
+      else if (tid < 32) { *word_at(k_slots, tid) = k_new2; *word_at(k_slots, tid + 32) = k_new2b; }
       named_bar_sync(1, kConsumers);
     }
     if constexpr (NT <= 2) {
@@ -478,7 +545,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (i < 15) TR(11 + 8 * i);
     mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
     if (i < 15) TR(12 + 8 * i);
-    if (own_new && i == n_tiles - 1) {   // made visible by the barrier below
+    if (own_new && i == n_tiles - 1 && tid < HD / 2) {   // made visible by the barrier below
       const uint32_t rr = n_rows - 1 - tile_pos, c16g = tid >> 2;
       *reinterpret_cast<uint32_t*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = v_new2;
     }

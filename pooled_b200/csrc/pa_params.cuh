@@ -12,12 +12,12 @@ struct DecodeParams {
   float* part_ml;           // [rows][n_splits][2]   (m in natural-log units, l)
   uint32_t n_splits;
   uint32_t n_heads, G, max_seq, n_stages;
-  // fused front (one token, partial RoPE over 64 dims, head_dim 256): q arrives unrotated and the consumers rotate
+  // fused front (one token; head_dim 256 with 64 rotary dims, or head_dim 128 rotated in full): q arrives unrotated and the consumers rotate
   // it; the CTA that walks the sequence's last tile also rotates k, converts v and appends the token's row
   uint32_t fused, append;       // append: this cache holds the new row (false on another rank's shard)
   const void* k_new; const void* v_new;               // the token's k / v row, [n_kv * hd], dtype as q
   __half* k_cache; __half* v_cache;                   // caches of the layer
-  Angle rope_ang[32];       // cos / sin of pos * theta^(-2i/64), evaluated by the host in float64
+  Angle rope_ang[64];       // cos / sin of pos * theta^(-2i/n_rot), i < n_rot/2, evaluated by the host in float64
   uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends
   uint32_t pre_stages;         // ... but only this many per CTA before the q loads are in flight
   uint32_t early_limit;        // ... and only rows below this one (the call before may still be writing its own row)
@@ -67,6 +67,14 @@ struct AnglesParams {
   Angle* out;              // [n_cols][half]
   const double* inv_freq;
   uint32_t pos0, n_cols, half;
+};
+
+struct HeadNormParams {
+  const void* x; uint64_t x_col_stride, x_head_stride;
+  void* y; uint64_t y_col_stride, y_head_stride;
+  const float* w;          // [hd]
+  double eps;
+  uint32_t hd; int f16;
 };
 
 struct SigmoidParams {

@@ -306,6 +306,34 @@ __global__ void __launch_bounds__(128) pa_angles_kernel(const AnglesParams p) {
   p.out[i] = make_angle(c, s);
 }
 
+// QK head-norm (the step before RoPE in attn_glue, engine/wgsl/qwen35.js:1112-1122), with the arithmetic of the CPU
+// reference (tests/reference/ref_q38.mjs:50-57): the sum of squares is accumulated in float64 in index order by one
+// thread -- that order is part of the result -- then out = f32((x * inv) * w) with inv = 1 / sqrt(ss / hd + eps).
+// grid (columns, heads), 64 threads.
+__global__ void __launch_bounds__(64) pa_head_norm_kernel(const HeadNormParams p) {
+  __shared__ float s_x[512];
+  __shared__ double s_inv;
+  const uint32_t col = blockIdx.x, head = blockIdx.y, hd = p.hd;
+  pdl_wait();
+  pdl_trigger();
+  const uint64_t xo = (uint64_t)col * p.x_col_stride + (uint64_t)head * p.x_head_stride;
+  for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) s_x[i] = ld_act(p.x, xo + i, p.f16);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double ss = 0.0;
+    for (uint32_t i = 0; i < hd; ++i) { const double v = (double)s_x[i]; ss = __dadd_rn(ss, __dmul_rn(v, v)); }
+    s_inv = __ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(__ddiv_rn(ss, (double)hd), p.eps)));
+  }
+  __syncthreads();
+  const double inv = s_inv;
+  const uint64_t yo = (uint64_t)col * p.y_col_stride + (uint64_t)head * p.y_head_stride;
+  for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) {
+    const float r = (float)__dmul_rn(__dmul_rn((double)s_x[i], inv), (double)p.w[i]);
+    if (p.f16) reinterpret_cast<__half*>(p.y)[yo + i] = __float2half_rn(r);
+    else reinterpret_cast<float*>(p.y)[yo + i] = r;
+  }
+}
+
 __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams p) {
   const uint32_t col = blockIdx.x, n = p.n_heads * p.hd;
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -330,6 +358,9 @@ cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_
 }
 cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st) {
   return launch_pdl(pa_angles_kernel, dim3((p.n_cols * p.half + 127) / 128), dim3(128), 0, st, p);
+}
+cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t n_heads, cudaStream_t st) {
+  return launch_pdl(pa_head_norm_kernel, dim3(n_cols, n_heads), dim3(64), 0, st, p);
 }
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st) {
   pa_sigmoid_mul_kernel<<<n_cols, 256, 0, st>>>(p);

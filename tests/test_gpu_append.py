@@ -191,3 +191,35 @@ def test_arguments_are_checked():
         eng.kv_append(0, 0, 0, torch.zeros((5, eng.cfg.kv_dim), device="cuda"), torch.zeros((5, eng.cfg.kv_dim), device="cuda"))
     eng.kv_append(0, 0, 126, k, k)               # still usable after argument errors
     eng.sync()
+
+
+@pytest.mark.parametrize("hd,heads,n_cols,dtype", [(256, 16, 1, "f32"), (256, 2, 5, "f32"), (128, 24, 33, "f32"), (256, 6, 4, "f16")])
+def test_head_norm_matches_the_reference_arithmetic_bit_for_bit(hd, heads, n_cols, dtype):
+    # tests/reference/ref_q38.mjs:50-57, :163-164: serial float64 sum of squares, inv = 1/sqrt(ss/n + eps), f32((x*inv)*w);
+    # padded column stride and interleaved heads (q_full layout: head stride 2*hd) as the engine hands them over
+    import torch
+    td = torch.float16 if dtype == "f16" else torch.float32
+    eng = _engine(n_heads=heads, n_kv_heads=1 if heads % 2 else 2, head_dim=hd, n_rot=64, act_dtype=td)
+    hs, cs = 2 * hd, heads * 2 * hd + 12
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((n_cols, cs)) * 3).astype(np.float32)
+    x[0, :hd] *= 1e-3; x[-1, hd * 2:hd * 3] *= 40
+    if dtype == "f16":
+        x = po.h2f(po.f16_rne(x))
+    w = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    dx = util.torch_dev(x, td)
+    out = torch.zeros_like(dx)
+    eng.head_norm(dx, heads, util.torch_dev(w), 1e-6, head_stride=hs, out=out)
+    got = out.float().cpu().numpy()
+    for c in range(n_cols):
+        for h in range(heads):
+            want = po.head_norm_f64(x[c, h * hs:h * hs + hd], 1, hd, w, 1e-6)
+            g = got[c, h * hs:h * hs + hd]
+            if dtype == "f16":
+                assert np.array_equal(po.f16_rne(g), po.f16_rne(want))
+            else:
+                assert np.array_equal(g.view(np.uint32), want.view(np.uint32)), (c, h)
+            assert not got[c, h * hs + hd:(h + 1) * hs].any()      # the gate half of q_full is not touched
+    # in place
+    eng.head_norm(dx, heads, util.torch_dev(w), 1e-6, head_stride=hs)
+    assert torch.equal(dx[:, :heads * hs].view(n_cols, heads, hs)[:, :, :hd], out[:, :heads * hs].view(n_cols, heads, hs)[:, :, :hd])

@@ -298,14 +298,15 @@ def test_exchange_merge_with_one_rank_matches_decode_over_many_calls():
         eng.decode_exchange(0, [(0, 100, 8)], torch.zeros((8, nH * hd), device="cuda"))   # 128 rows > max_rows 64
 
 
+@pytest.mark.parametrize("nH,nKV,hd,n_rot,theta", [(16, 2, 256, 64, 1e7), (16, 8, 128, 128, 1e6), (8, 2, 128, 128, 1e6)])
 @pytest.mark.parametrize("act", ["f16", "f32"])
-def test_fused_front_equals_the_three_kernel_chain_bit_for_bit(act, monkeypatch):
+def test_fused_front_equals_the_three_kernel_chain_bit_for_bit(act, nH, nKV, hd, n_rot, theta, monkeypatch):
     # One-token calls of the 64-rotary-dim / head_dim 256 shape rotate q and k and append inside the decode kernel.
     # Same cos / sin (host libm), same rotation arithmetic, same decode kernel: the cache rows and the outputs must
     # carry the same bits as the RoPE/append -> decode -> combine chain (POOLED_ATTN_NO_FUSE=1), token after token on
     # ONE layer, where each call's early K/V fetch must stay clear of the row the call before may still be writing.
     import torch
-    nH, nKV, hd, ctx0, steps = 16, 2, 256, 700, 40
+    ctx0, steps = 700, 40
     td = torch.float16 if act == "f16" else torch.float32
     rng = np.random.default_rng(11)
     K0 = util.normal_f16(21, (ctx0, nKV * hd)); V0 = util.normal_f16(22, (ctx0, nKV * hd))
@@ -319,7 +320,7 @@ def test_fused_front_equals_the_three_kernel_chain_bit_for_bit(act, monkeypatch)
             monkeypatch.setenv("POOLED_ATTN_NO_FUSE", "1")
         else:
             monkeypatch.delenv("POOLED_ATTN_NO_FUSE", raising=False)
-        eng = _engine(nH, nKV, hd, ctx0 + steps + 8, act=act)
+        eng = _engine(nH, nKV, hd, ctx0 + steps + 8, act=act, n_rot=n_rot, theta=theta)
         util.load_cache(eng, 0, 0, po.f16_rne(K0), po.f16_rne(V0))
         dq, dk, dv, dg = (util.torch_dev(x, td) for x in (q, k, v, g))
         out = torch.empty((steps, nH * hd), dtype=td, device="cuda")
@@ -331,5 +332,5 @@ def test_fused_front_equals_the_three_kernel_chain_bit_for_bit(act, monkeypatch)
     assert np.array_equal(caches["fused"][0], caches["chain"][0]) and np.array_equal(caches["fused"][1], caches["chain"][1])
     assert np.array_equal(outs["fused"].view(np.uint32), outs["chain"].view(np.uint32))
     # and against the oracle: the appended rows bit for bit
-    wk = np.stack([po.f16_rne(po.rope_neox_f64(k[t], nKV, hd, 64, ctx0 + t, 1e7)) for t in range(steps)])
+    wk = np.stack([po.f16_rne(po.rope_neox_f64(k[t], nKV, hd, n_rot, ctx0 + t, theta)) for t in range(steps)])
     assert np.array_equal(caches["fused"][0], wk) and np.array_equal(caches["fused"][1], po.f16_rne(v))

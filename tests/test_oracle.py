@@ -165,3 +165,16 @@ def test_normal_generator_is_counter_based():
     assert abs(b.mean()) < 0.01 and abs(b.std() - 1) < 0.01
     ch = po.outlier_channels(3, 256)
     assert len(set(ch)) == 4 and all(0 <= c < 256 for c in ch) and ch == po.outlier_channels(3, 256)
+
+
+def test_head_norm_c_and_numpy_twins_agree_and_normalise():
+    # tests/reference/ref_q38.mjs:50-57: with unit weights the output has mean square 1 (up to eps)
+    rng = np.random.default_rng(4)
+    for hd, heads in ((128, 8), (256, 16)):
+        x = (rng.standard_normal(heads * hd) * 5).astype(np.float32)
+        w = (1 + 0.2 * rng.standard_normal(hd)).astype(np.float32)
+        a = po.head_norm_f64(x, heads, hd, w, 1e-6)
+        b = po.np_head_norm(x, heads, hd, w, 1e-6)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        u = po.head_norm_f64(x, heads, hd, np.ones(hd, np.float32), 1e-6).reshape(heads, hd).astype(np.float64)
+        assert np.allclose((u * u).mean(axis=1), 1.0, atol=1e-5)
