@@ -671,7 +671,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 // grid (query rows, HD / 64): one CTA per (column, head, 64-dim slice).  Every thread fetches the (m, l) of up to two
 // splits while 16 groups of 16 lanes (a float4 each) fetch the o records, splits 16 apart, eight loads in flight per
 // lane; the weights are applied when both have arrived.  Every sum has a fixed order.
-template <int HD>
+template <int HD, bool XCH>
 __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) {
   __shared__ float s_w[512];
   __shared__ float s_red[8], s_red2[8];
@@ -764,7 +764,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
 #pragma unroll
     for (int i = 1; i < 16; ++i) t += sa[i * 64 + tid];
   }
-  if (p.exchange) {
+  if constexpr (XCH) {
     // ---- publish this rank's record slice to every rank, wait for theirs, merge across ranks ----
     // Every value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands whole, so
     // the receiver spins on the words themselves and no flag, fence or second round trip is needed.
@@ -887,8 +887,11 @@ cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, i
 }
 
 cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, cudaStream_t st) {
-  if (head_dim == 256) return launch_pdl(pa_combine_kernel<256>, dim3(rows, 4), dim3(256), 0, st, p);
-  if (head_dim == 128) return launch_pdl(pa_combine_kernel<128>, dim3(rows, 2), dim3(256), 0, st, p);
+  // the cross-GPU exchange is its own instantiation: its registers would halve the occupancy of the plain merge
+  if (head_dim == 256) return p.exchange ? launch_pdl(pa_combine_kernel<256, true>, dim3(rows, 4), dim3(256), 0, st, p)
+                                         : launch_pdl(pa_combine_kernel<256, false>, dim3(rows, 4), dim3(256), 0, st, p);
+  if (head_dim == 128) return p.exchange ? launch_pdl(pa_combine_kernel<128, true>, dim3(rows, 2), dim3(256), 0, st, p)
+                                         : launch_pdl(pa_combine_kernel<128, false>, dim3(rows, 2), dim3(256), 0, st, p);
   return cudaErrorInvalidValue;
 }
 
