@@ -569,9 +569,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
 #ifdef PA_TRACE
   c.trace = p.trace;
 #endif
-  const bool lo_rec = false;
-  const uint32_t rs = lo_rec ? 2 * ns : ns;
-  c.lo_records = lo_rec ? 1 : 0;
+  const uint32_t rs = ns;
   c.o_row_stride = (uint64_t)rs * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
   c.ml_row_stride = (uint64_t)rs * 2; c.ml_part_stride = 2;
   c.n_heads = ctx->cfg.n_heads; c.fixed_parts = 0; c.n_splits = ns;

@@ -165,28 +165,8 @@ __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) 
 constexpr int kMaxItems = 32;     // items of one batched decode call
 constexpr int kMaxRows = 64;      // query rows (columns x heads of one kv head) one decode CTA carries
 
-// The small kernels of a layer ask for the largest shared-memory carveout although they need little of it: an SM
-// changes its carveout only when idle, so a decode CTA (about 205 KB) launched ahead of its predecessor's end could
-// otherwise not join an SM that still runs one of their CTAs.  Asked once per kernel and device.
-static inline void prefer_max_carveout(const void* fn) {
-  static std::atomic<const void*> seen[16][16];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return;
-  for (int i = 0; i < 16; ++i) {
-    const void* cur = seen[dev][i].load(std::memory_order_acquire);
-    if (cur == fn) return;
-    if (cur == nullptr) {
-      static const bool off = getenv("POOLED_ATTN_NO_CARVEOUT") != nullptr;
-      if (!off) cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-      seen[dev][i].store(fn, std::memory_order_release);
-      return;
-    }
-  }
-}
-
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-  if (smem == 0) prefer_max_carveout(reinterpret_cast<const void*>(kern));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];

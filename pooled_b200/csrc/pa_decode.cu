@@ -689,7 +689,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     const uint32_t n_rows = p.items.n_rows[it];
     const uint32_t tiles = (n_rows + kT - 1) / kT, tps = (tiles + p.n_splits - 1) / p.n_splits;
     ns = tiles ? (tiles + tps - 1) / tps : 0;   // a shard that holds no row of the item: an empty record
-    if (p.lo_records) ns *= 2;
   }
   // Everything the CTA reads is requested before the first use: the (m, l) pairs, the o records of the first 128
   // splits (eight float4 per lane, splits 16 apart) and the gate value.  One memory round trip instead of three.

@@ -40,7 +40,6 @@ struct CombineParams {
   float* partial_out;    // != nullptr: write the merged record (o unnormalised, m, l) instead of out
   uint64_t partial_rows; // rows in partial_out (o block first, then the (m, l) block)
   ItemList items; uint32_t n_items;
-  int lo_records;        // != 0: each used split is followed (after all used splits) by a low-part record (same m, l = 0)
   int exchange;          // != 0: publish the merged record to every rank, wait for theirs, merge across ranks, then out
   ExchangeView xc;
   uint32_t* err;
