@@ -138,6 +138,12 @@ PA_API uint32_t pa_plan_splits(pa_ctx* ctx, uint32_t n_rows, uint32_t n_items);
 PA_API int pa_head_norm(pa_ctx* ctx, const void* x, uint64_t col_stride, uint64_t head_stride, uint32_t n_heads_x,
                         uint32_t n_cols, const float* w, double eps, void* y, uint64_t y_col_stride,
                         uint64_t y_head_stride, void* stream);
+/* Gives a layer its QK head-norm weights (device, f32 [head_dim] each; both or neither; they stay the caller's).  From
+ * then on pa_attn_layer / pa_attn_layer_host / pa_attn_step_host / pa_attn_layer_sharded on this layer apply
+ * pa_head_norm to q and k first (one extra kernel per call, into scratch of the context), which makes the call the
+ * whole of attn_glue_kv + attn core + gate (engine/wgsl/layer_fuse.js:87-146): q_full, k and v go in as the GEMVs
+ * leave them.  Passing null weights turns it off. */
+PA_API int pa_layer_set_head_norm(pa_layer* layer, const float* q_w, const float* k_w, double eps);
 
 /* RoPE.  Replaces rope_part / rope_part_mc (engine/wgsl/qwen35.js:386-404, :858-875), the full-head rope
  * (engine/wgsl/base.js:154-172) and the rotation inside attn_glue (engine/wgsl/qwen35.js:1124-1131).

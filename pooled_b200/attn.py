@@ -265,6 +265,16 @@ class AttnEngine:
                                    gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
         return out
 
+    def set_head_norm(self, li: int, q_w: torch.Tensor | None, k_w: torch.Tensor | None, eps: float = 1e-6):
+        """Layer li applies the QK head-norm inside encode_layer* from now on (weights: float32 [head_dim] on the device,
+        kept alive here); None turns it off."""
+        if q_w is not None:
+            assert q_w.dtype == torch.float32 and k_w.dtype == torch.float32 and q_w.is_cuda and k_w.is_cuda
+            assert q_w.numel() == self.cfg.head_dim and k_w.numel() == self.cfg.head_dim
+        self._norm_w = getattr(self, "_norm_w", {})
+        self._norm_w[li] = (q_w, k_w)
+        self._ck(self.L.pa_layer_set_head_norm(self.layers[li], self._p(q_w), self._p(k_w), float(eps)))
+
     def head_norm(self, x: torch.Tensor, n_heads_x: int, w: torch.Tensor, eps: float, head_stride: int | None = None,
                   out: torch.Tensor | None = None) -> torch.Tensor:
         """QK head-norm of q or k before RoPE (the head_norm step of attn_glue, engine/wgsl/qwen35.js:1112-1122):

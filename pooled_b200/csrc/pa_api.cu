@@ -187,7 +187,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
 extern "C" int pa_destroy(pa_ctx* ctx) {
   if (!ctx) return PA_OK;
   cudaSetDevice(ctx->device);
-  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err);
+  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->norm_q); cudaFree(ctx->norm_k); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err);
   cudaFree(ctx->stage_dev);
   for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
@@ -234,6 +234,26 @@ extern "C" int pa_layer_destroy(pa_layer* L) {
 extern "C" int pa_layer_set_origin(pa_layer* L, uint32_t origin) {
   if (!L) return PA_EINVAL;
   L->origin = origin;
+  return PA_OK;
+}
+
+extern "C" int pa_layer_set_head_norm(pa_layer* L, const float* q_w, const float* k_w, double eps) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  if ((q_w == nullptr) != (k_w == nullptr)) return fail(ctx, PA_EINVAL, "pa_layer_set_head_norm: give both weights or neither");
+  if (q_w && !(eps >= 0.0)) return fail(ctx, PA_EINVAL, "pa_layer_set_head_norm: eps must be a non-negative number");
+  if (q_w && ctx->cfg.head_dim > 512) return fail(ctx, PA_EUNSUPPORTED, "pa_layer_set_head_norm: head_dim above 512");
+  if (q_w && !ctx->norm_q) {   // scratch for the normed q and k of one layer call, made once
+    cudaSetDevice(ctx->device);
+    const size_t es = ctx->cfg.act_dtype == PA_F16 ? 2 : 4;
+    if (cudaMalloc(&ctx->norm_q, (size_t)ctx->cfg.max_cols * ctx->q_dim * es) != cudaSuccess ||
+        cudaMalloc(&ctx->norm_k, (size_t)ctx->cfg.max_cols * ctx->kv_dim * es) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(ctx->norm_q); ctx->norm_q = nullptr;
+      return fail(ctx, PA_ENOMEM, "pa_layer_set_head_norm: scratch for the normed q and k does not fit on the device");
+    }
+  }
+  L->qnorm_w = q_w; L->knorm_w = k_w; L->norm_eps = eps;
   return PA_OK;
 }
 
@@ -402,13 +422,13 @@ static int ensure_angles(pa_ctx* ctx, uint32_t pos, uint32_t n_cols, cudaStream_
 
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
                             uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
-                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false) {
+                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false, uint64_t vcs = 0) {
   RopeParams p{};
   p.q_out_f16 = q_out_f16;
   if (q_out_f16 == 2) p.q_lo_offset = (uint64_t)ctx->cfg.max_cols * ctx->q_dim;   // second half of the f32-sized q_rot buffer
   p.trigger_early = in_layer_call ? 1u : 0u;
   p.q = q; p.q_col_stride = qcs; p.q_head_stride = qhs; p.q_heads = q_heads; p.q_out = q_out; p.q_out_col_stride = q_out_cs;
-  p.k = k; p.v = v; p.kv_col_stride = kvcs; p.kv_heads = ctx->cfg.n_kv_heads;
+  p.k = k; p.v = v; p.kv_col_stride = kvcs; p.v_col_stride = vcs ? vcs : kvcs; p.kv_heads = ctx->cfg.n_kv_heads;
   if (L) { p.k_cache = L->k; p.v_cache = L->v; p.cache_row0 = (uint64_t)seq * L->max_seq + (pos - L->origin); }
   p.hd = ctx->cfg.head_dim; p.n_rot = ctx->cfg.n_rot; p.pos = pos; p.mode = mode; p.in_f16 = in_f16;
   p.inv_freq = ctx->inv_freq; p.cs_table = cs_table;
@@ -684,7 +704,7 @@ extern "C" int pa_head_norm(pa_ctx* ctx, const void* x, uint64_t col_stride, uin
   cudaSetDevice(ctx->device);
   HeadNormParams p{};
   p.x = x; p.x_col_stride = col_stride; p.x_head_stride = head_stride; p.y = y; p.y_col_stride = y_col_stride; p.y_head_stride = y_head_stride;
-  p.w = w; p.eps = eps; p.hd = ctx->cfg.head_dim; p.f16 = ctx->cfg.act_dtype == PA_F16;
+  p.w = w; p.eps = eps; p.hd = ctx->cfg.head_dim; p.f16 = ctx->cfg.act_dtype == PA_F16; p.n_first = n_heads_x;
   CU_TRY(ctx, launch_head_norm(p, n_cols, n_heads_x, (cudaStream_t)stream));
   ctx->stats.kernel_launches++;
   return PA_OK;
@@ -721,6 +741,23 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   if (!q || !k || !v || !out) return fail(ctx, PA_EINVAL, "pa_attn_layer: null q, k, v or out");
   if (int rc = check_cols(L, seq, pos, n_cols, "pa_attn_layer", !sharded)) return rc;
   cudaSetDevice(ctx->device);
+  // QK head-norm of the layer, if it has one: q and k in one launch into the context's scratch, which the rest of the
+  // call then reads (head_norm precedes RoPE in attn_glue, engine/wgsl/qwen35.js:1112-1131).  The gate keeps pointing
+  // into the caller's q_full.
+  uint64_t kcs = kvcs;   // k's column stride (v keeps the caller's)
+  if (L->qnorm_w && !ctx->core_only) {
+    if (n_cols > ctx->cfg.max_cols) return fail(ctx, PA_EINVAL, "pa_attn_layer: %u columns exceed max_cols %u", n_cols, ctx->cfg.max_cols);
+    HeadNormParams hp{};
+    hp.x = q; hp.x_col_stride = qcs; hp.x_head_stride = qhs; hp.y = ctx->norm_q; hp.y_col_stride = ctx->q_dim; hp.y_head_stride = ctx->cfg.head_dim;
+    hp.w = L->qnorm_w; hp.n_first = ctx->cfg.n_heads;
+    hp.x2 = k; hp.x2_col_stride = kvcs; hp.x2_head_stride = ctx->cfg.head_dim; hp.y2 = ctx->norm_k; hp.y2_col_stride = ctx->kv_dim;
+    hp.y2_head_stride = ctx->cfg.head_dim; hp.w2 = L->knorm_w;
+    hp.eps = L->norm_eps; hp.hd = ctx->cfg.head_dim; hp.f16 = ctx->cfg.act_dtype == PA_F16;
+    CU_TRY(ctx, launch_head_norm(hp, n_cols, ctx->cfg.n_heads + ctx->cfg.n_kv_heads, st));
+    ctx->stats.kernel_launches++;
+    q = ctx->norm_q; qcs = ctx->q_dim; qhs = ctx->cfg.head_dim;
+    k = ctx->norm_k; kcs = ctx->kv_dim;
+  }
   // A k-token block on the tensor-core split-K kernel in its hi/lo form takes q as two f16 planes (high and low parts),
   // which the RoPE kernel writes directly: nothing is left to convert in the attention kernel's prologue.
   const bool planes = mode != PA_MODE_PREFILL && n_cols * ctx->G > 8 && n_cols * ctx->G <= (uint32_t)kMaxRows && !(ctx->cfg.flags & PA_FLAG_FAST) &&
@@ -734,7 +771,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
       return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true, &fz);
     }
     if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
-                                  owns ? v : nullptr, kvcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, planes ? 2 : 0, true))
+                                  owns ? v : nullptr, kcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, planes ? 2 : 0, true, kvcs))
       return rc;
     pa_item it{seq, pos, n_cols, 0};
     if (planes)
@@ -752,8 +789,8 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   }
   // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic)
   if (!ctx->core_only)
-    if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kvcs, cs_table, ctx->cfg.rope_mode,
-                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : (planes ? 2 : 0), true))
+    if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kcs, cs_table, ctx->cfg.rope_mode,
+                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : (planes ? 2 : 0), true, kvcs))
       return rc;
   if (prefill)
     return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);

@@ -226,6 +226,8 @@ struct pa_ctx {
   size_t part_slots = 0;       // (query row, split) records the partial buffers hold
   uint32_t* dev_err = nullptr;   // device error word (bounded waits)
   uint32_t* host_err = nullptr;  // pinned mirror
+  void* norm_q = nullptr;        // normed q / k of the current layer call (act_dtype, [max_cols][q_dim] / [max_cols][kv_dim])
+  void* norm_k = nullptr;
   void* stage_dev = nullptr;     // device staging of the host-buffer entry point
   void* stage_host = nullptr;    // pinned staging
   size_t stage_bytes = 0;
@@ -246,4 +248,7 @@ struct pa_layer {
   __half* k = nullptr;
   __half* v = nullptr;
   CUtensorMap tm_k64, tm_v64;    // 64-row boxes over all sequences' rows, for the decode kernel
+  const float* qnorm_w = nullptr;   // QK head-norm weights of this layer (device, f32 [head_dim]); nullptr: the layer
+  const float* knorm_w = nullptr;   // call takes q and k as they come
+  double norm_eps = 0.0;
 };

@@ -51,7 +51,7 @@ struct RopeParams {
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
   void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
   uint64_t q_lo_offset;    // q_out_f16 == 2: f16 high parts at q_out, f16 low parts (x - fl16(x)) this many halves later
-  const void* k; const void* v; uint64_t kv_col_stride; uint32_t kv_heads;  // k == nullptr: skip
+  const void* k; const void* v; uint64_t kv_col_stride, v_col_stride; uint32_t kv_heads;  // k == nullptr: skip; kv_col_stride is k's
   __half* k_cache; __half* v_cache; uint64_t cache_row0;                    // row of column 0
   uint32_t hd, n_rot, pos, mode;
   int in_f16;
@@ -72,6 +72,11 @@ struct HeadNormParams {
   const void* x; uint64_t x_col_stride, x_head_stride;
   void* y; uint64_t y_col_stride, y_head_stride;
   const float* w;          // [hd]
+  // heads at or past n_first (blockIdx.y) belong to a second array with its own weight: q and k of a layer in one launch
+  uint32_t n_first;
+  const void* x2; uint64_t x2_col_stride, x2_head_stride;
+  void* y2; uint64_t y2_col_stride, y2_head_stride;
+  const float* w2;
   double eps;
   uint32_t hd; int f16;
 };

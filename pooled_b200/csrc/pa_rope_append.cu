@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
   if (slot >= nq + nk) {
     // V head: conversion only
     const uint32_t head = slot - nq - nk, kvd = p.kv_heads * hd;
-    const uint64_t so = (uint64_t)col * p.kv_col_stride + (uint64_t)head * hd + 2 * pr;
+    const uint64_t so = (uint64_t)col * p.v_col_stride + (uint64_t)head * hd + 2 * pr;
     __half* dst = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd + (uint64_t)head * hd + 2 * pr;
     dst[0] = f16_rne(ld_act(p.v, so, p.in_f16));
     dst[1] = f16_rne(ld_act(p.v, so + 1, p.in_f16));
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(256) pa_rope_append_cols_kernel(const RopePara
       a[u] = b[u] = 0.f;
       if (w >= total) continue;
       if (w >= nq + nk) {                      // V: elements 2i, 2i+1
-        const uint64_t so = (uint64_t)col * p.kv_col_stride + 2 * (w - nq - nk);
+        const uint64_t so = (uint64_t)col * p.v_col_stride + 2 * (w - nq - nk);
         a[u] = ld_act(p.v, so, p.in_f16); b[u] = ld_act(p.v, so + 1, p.in_f16);
       } else {
         const bool is_q = w < nq;
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParam
   const uint32_t kvd = p.kv_heads * hd;
   const __half* qs = reinterpret_cast<const __half*>(p.q) + (uint64_t)col * p.q_col_stride;
   const __half* ks = reinterpret_cast<const __half*>(p.k) + (uint64_t)col * p.kv_col_stride;
-  const __half* vs = reinterpret_cast<const __half*>(p.v) + (uint64_t)col * p.kv_col_stride;
+  const __half* vs = reinterpret_cast<const __half*>(p.v) + (uint64_t)col * p.v_col_stride;
   __half* qd = reinterpret_cast<__half*>(p.q_out) + (uint64_t)col * p.q_out_col_stride;
   __half* kd = p.k_cache + (p.cache_row0 + col) * (uint64_t)kvd;
   __half* vd = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd;
@@ -313,11 +313,16 @@ __global__ void __launch_bounds__(128) pa_angles_kernel(const AnglesParams p) {
 __global__ void __launch_bounds__(64) pa_head_norm_kernel(const HeadNormParams p) {
   __shared__ float s_x[512];
   __shared__ double s_inv;
-  const uint32_t col = blockIdx.x, head = blockIdx.y, hd = p.hd;
+  const uint32_t col = blockIdx.x, hd = p.hd;
+  const bool second = blockIdx.y >= p.n_first;
+  const uint32_t head = second ? blockIdx.y - p.n_first : blockIdx.y;
+  const void* x = second ? p.x2 : p.x;
+  void* y = second ? p.y2 : p.y;
+  const float* w = second ? p.w2 : p.w;
   pdl_wait();
   pdl_trigger();
-  const uint64_t xo = (uint64_t)col * p.x_col_stride + (uint64_t)head * p.x_head_stride;
-  for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) s_x[i] = ld_act(p.x, xo + i, p.f16);
+  const uint64_t xo = (uint64_t)col * (second ? p.x2_col_stride : p.x_col_stride) + (uint64_t)head * (second ? p.x2_head_stride : p.x_head_stride);
+  for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) s_x[i] = ld_act(x, xo + i, p.f16);
   __syncthreads();
   if (threadIdx.x == 0) {
     double ss = 0.0;
@@ -326,11 +331,11 @@ __global__ void __launch_bounds__(64) pa_head_norm_kernel(const HeadNormParams p
   }
   __syncthreads();
   const double inv = s_inv;
-  const uint64_t yo = (uint64_t)col * p.y_col_stride + (uint64_t)head * p.y_head_stride;
+  const uint64_t yo = (uint64_t)col * (second ? p.y2_col_stride : p.y_col_stride) + (uint64_t)head * (second ? p.y2_head_stride : p.y_head_stride);
   for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) {
-    const float r = (float)__dmul_rn(__dmul_rn((double)s_x[i], inv), (double)p.w[i]);
-    if (p.f16) reinterpret_cast<__half*>(p.y)[yo + i] = __float2half_rn(r);
-    else reinterpret_cast<float*>(p.y)[yo + i] = r;
+    const float r = (float)__dmul_rn(__dmul_rn((double)s_x[i], inv), (double)w[i]);
+    if (p.f16) reinterpret_cast<__half*>(y)[yo + i] = __float2half_rn(r);
+    else reinterpret_cast<float*>(y)[yo + i] = r;
   }
 }
 
@@ -350,7 +355,7 @@ cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_
   auto al16 = [](const void* x) { return ((uintptr_t)x & 15) == 0; };
   const bool vec = n_cols >= 16 && p.mode == PA_ROPE_F64 && (p.angles || p.n_ang) && p.in_f16 && p.n_rot % 16 == 0 && p.n_rot <= 256 && p.hd % 8 == 0 &&
                    (!p.q || (p.q_out_f16 == 1 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
-                   (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0));
+                   (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0 && p.v_col_stride % 8 == 0));
   if (vec) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
   if (n_cols >= 16) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
   const uint32_t slots = (p.q ? p.q_heads : 0) + (p.k ? p.kv_heads : 0) + (p.v ? p.kv_heads : 0);

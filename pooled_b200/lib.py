@@ -73,6 +73,7 @@ SYMBOLS = {
     "pa_attn_layer_sharded": (_i, [_vp, _u32, _u32, _u32, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
     "pa_prefill": (_i, [_vp, _u32, _u32, _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_sigmoid_mul": (_i, [_vp, _vp, _u64, _vp, _u64, _u64, _u32, _vp]),
+    "pa_layer_set_head_norm": (_i, [_vp, _vp, _vp, C.c_double]),
     "pa_head_norm": (_i, [_vp, _vp, _u64, _u64, _u32, _u32, _vp, C.c_double, _vp, _u64, _u64, _vp]),
     "pa_attn_layer": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
     "pa_attn_layer_host": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),

@@ -334,3 +334,44 @@ def test_fused_front_equals_the_three_kernel_chain_bit_for_bit(act, nH, nKV, hd,
     # and against the oracle: the appended rows bit for bit
     wk = np.stack([po.f16_rne(po.rope_neox_f64(k[t], nKV, hd, n_rot, ctx0 + t, theta)) for t in range(steps)])
     assert np.array_equal(caches["fused"][0], wk) and np.array_equal(caches["fused"][1], po.f16_rne(v))
+
+
+@pytest.mark.parametrize("n_cols,mode", [(1, "decode"), (5, "decode"), (160, "prefill")])
+def test_layer_call_with_head_norm_is_attn_glue_kv_plus_core_plus_gate(n_cols, mode):
+    # engine/wgsl/layer_fuse.js:87-146 + attn core + gate in one call: q_full (q and gate interleaved per head) and k go in
+    # un-normed; the library norms q and k (tests/reference/ref_q38.mjs:163-164), rotates, appends, attends, gates.
+    # f32 activations: the normed values are not f16 numbers, so the cache rows are checked bit for bit after the oracle's
+    # own norm -> rope -> f16 chain.
+    import torch
+    nH, nKV, hd, n_rot, theta, ctx0, eps = 16, 2, 256, 64, 1e7, 500, 1e-6
+    eng = _engine(nH, nKV, hd, ctx0 + n_cols + 8, act="f32", max_cols=max(8, n_cols))
+    rng = np.random.default_rng(17)
+    K0 = util.normal_f16(31, (ctx0, nKV * hd)); V0 = util.normal_f16(32, (ctx0, nKV * hd))
+    util.load_cache(eng, 0, 0, po.f16_rne(K0), po.f16_rne(V0))
+    q_full = (rng.standard_normal((n_cols, nH * 2 * hd)) * 2).astype(np.float32)      # [head][q hd | gate hd]
+    k = (rng.standard_normal((n_cols, nKV * hd)) * 3).astype(np.float32)
+    v = rng.standard_normal((n_cols, nKV * hd)).astype(np.float32)
+    qw = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32); kw = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    dqw, dkw = util.torch_dev(qw), util.torch_dev(kw)
+    eng.set_head_norm(0, dqw, dkw, eps)
+    dqf = util.torch_dev(q_full)
+    out = eng.encode_layer(0, ctx0, dqf, util.torch_dev(k), util.torch_dev(v), dqf[:, hd:], mode=mode, q_head_stride=2 * hd,
+                           gate_head_stride=2 * hd).cpu().numpy()
+    eng.sync()
+    qv = q_full.reshape(n_cols, nH, 2 * hd)
+    q_plain, g = np.ascontiguousarray(qv[:, :, :hd]).reshape(n_cols, -1), np.ascontiguousarray(qv[:, :, hd:]).reshape(n_cols, -1)
+    q_rot = np.stack([po.rope_neox_f64(po.head_norm_f64(q_plain[c], nH, hd, qw, eps), nH, hd, n_rot, ctx0 + c, theta) for c in range(n_cols)])
+    k_rot = np.stack([po.rope_neox_f64(po.head_norm_f64(k[c], nKV, hd, kw, eps), nKV, hd, n_rot, ctx0 + c, theta) for c in range(n_cols)])
+    Kf = np.concatenate([po.f16_rne(K0), po.f16_rne(k_rot)]); Vf = np.concatenate([po.f16_rne(V0), po.f16_rne(v)])
+    gk, gv = util.read_cache(eng, 0, 0, ctx0, n_cols)
+    bad = int(np.count_nonzero(gk != Kf[ctx0:]))
+    assert bad <= (0 if n_cols * (n_rot // 2) <= 64 else 2), f"{bad} cache halves differ"     # wide calls: device sin/cos, last place
+    assert np.array_equal(gv, Vf[ctx0:])
+    cols = range(n_cols) if n_cols <= 8 else [0, 1, 63, 64, 127, 159]
+    ref = np.stack([po.attn_f64(q_rot[c:c + 1], Kf, Vf, nH, nKV, hd, ctx0 + c, 1, g[c:c + 1])[0] for c in cols])
+    util.assert_close(out[list(cols)], ref, f"head-norm layer call, {n_cols} columns")
+    # switched off again: the same call without the norm differs
+    eng.set_head_norm(0, None, None)
+    out2 = eng.encode_layer(0, ctx0, dqf, util.torch_dev(k), util.torch_dev(v), dqf[:, hd:], mode=mode, q_head_stride=2 * hd,
+                            gate_head_stride=2 * hd).cpu().numpy()
+    assert np.abs(out2 - out).max() > 1e-3
