@@ -375,3 +375,36 @@ def test_layer_call_with_head_norm_is_attn_glue_kv_plus_core_plus_gate(n_cols, m
     out2 = eng.encode_layer(0, ctx0, dqf, util.torch_dev(k), util.torch_dev(v), dqf[:, hd:], mode=mode, q_head_stride=2 * hd,
                             gate_head_stride=2 * hd).cpu().numpy()
     assert np.abs(out2 - out).max() > 1e-3
+
+
+@pytest.mark.parametrize("n_cols,nH,nKV", [(5, 24, 4), (3, 16, 2), (8, 16, 2)])
+def test_token_blocks_back_to_back_on_one_layer(n_cols, nH, nKV):
+    # 30 k-token blocks of f16 activations, one after another without synchronisation on ONE layer: each block's early K/V
+    # fetch must stay clear of rows still being written, and the blocks' rows straddle tile and split boundaries somewhere
+    # along the way.  Cache rows against the oracle (device sin/cos for these wide calls: last-place slack), the last block's
+    # output against float64 attention over everything before it.
+    import torch
+    hd, ctx0, blocks = 256, 1000, 30
+    rng = np.random.default_rng(23)
+    T = n_cols * blocks
+    K0 = util.normal_f16(41, (ctx0, nKV * hd)); V0 = util.normal_f16(42, (ctx0, nKV * hd))
+    f16 = lambda x: po.h2f(po.f16_rne(x.astype(np.float32)))
+    q, g = f16(rng.standard_normal((T, nH * hd))), f16(rng.standard_normal((T, nH * hd)))
+    k, v = f16(rng.standard_normal((T, nKV * hd)) * 2), f16(rng.standard_normal((T, nKV * hd)))
+    eng = _engine(nH, nKV, hd, ctx0 + T + 8, act="f16", max_cols=8)
+    util.load_cache(eng, 0, 0, po.f16_rne(K0), po.f16_rne(V0))
+    dq, dk, dv, dg = (util.torch_dev(x, torch.float16) for x in (q, k, v, g))
+    out = torch.empty((T, nH * hd), dtype=torch.float16, device="cuda")
+    for b in range(blocks):
+        s = slice(b * n_cols, (b + 1) * n_cols)
+        eng.encode_layer(0, ctx0 + b * n_cols, dq[s], dk[s], dv[s], dg[s], out[s], mode="decode")
+    eng.sync()
+    o = out.float().cpu().numpy()
+    gk, gv = util.read_cache(eng, 0, 0, ctx0, T)
+    wk = np.stack([po.f16_rne(po.rope_neox_f64(k[t], nKV, hd, 64, ctx0 + t, 1e7)) for t in range(T)])
+    assert int(np.count_nonzero(gk != wk)) <= 2 and np.array_equal(gv, po.f16_rne(v))
+    Kf = np.concatenate([po.f16_rne(K0), gk]); Vf = np.concatenate([po.f16_rne(V0), gv])
+    p0 = ctx0 + T - n_cols
+    q_rot = np.stack([po.rope_neox_f64(q[T - n_cols + c], nH, hd, 64, p0 + c, 1e7) for c in range(n_cols)])
+    ref = po.attn_f64(q_rot, Kf, Vf, nH, nKV, hd, p0, n_cols, g[T - n_cols:])
+    util.assert_close(o[T - n_cols:], ref, "token blocks, last block")
