@@ -162,9 +162,8 @@ def run_ours(args, w):
 
             def step():
                 for li in range(layers):
-                    for s in range(n_seqs):
-                        eng.rope_append(li, s, pos, dq[li, s:s + 1], dk[li, s:s + 1], dv[li, s:s + 1])
-                    eng.decode(li, items, dq[li], gate(dg, li), dout[li])
+                    q_rot = eng.rope_append_items(li, [(s, pos) for s in range(n_seqs)], dq[li], dk[li], dv[li])   # all sequences, one launch
+                    eng.decode(li, items, q_rot, gate(dg, li), dout[li])
         kernel_bytes = 2 * (pos + n_cols) * kvd * 2 * n_seqs
         bytes_per_step = layers * kernel_bytes
 

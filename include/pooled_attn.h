@@ -166,6 +166,13 @@ PA_API int pa_kv_append(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_
 PA_API int pa_rope_append(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q,
                           uint64_t q_col_stride, uint64_t q_head_stride, const void* k, const void* v,
                           uint64_t kv_col_stride, const float* cs_table, float* q_rot, void* stream);
+/* The same for one token of each of several sequences in one launch (the batched engine's per-column positions,
+ * engine/wgsl/qwen4exp_batch.js:535-579): item i = (seq, pos, 1) owns row i of q, k, v and of q_rot.  Items whose
+ * position lies outside this layer's shard (pa_layer_set_origin) get their q rotated and nothing appended.
+ * At most 32 items; PA_ROPE_F64 or PA_ROPE_NONE. */
+PA_API int pa_rope_append_items(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q,
+                                uint64_t q_col_stride, uint64_t q_head_stride, const void* k, const void* v,
+                                uint64_t kv_col_stride, float* q_rot, void* stream);
 
 /* Decode / verify core + combine + gate.  Replaces attn_dec + attn_dec_combine(_g) + sigmoid_mul
  * (engine/wgsl/attn_dec.js:67-287, engine/wgsl/qwen35.js:406-416) as dispatched by _encodeLayerR

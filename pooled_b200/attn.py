@@ -215,6 +215,15 @@ class AttnEngine:
                                        self._p(v), k.stride(0), self._p(cs_table), self._p(q_rot), self._st()))
         return q_rot
 
+    def rope_append_items(self, li: int, seqs_pos, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_head_stride: int | None = None) -> torch.Tensor:
+        """One token of each of several sequences in one launch: seqs_pos = [(seq, pos)], row i of q / k / v belongs to
+        item i.  Returns the rotated q, float32 [n_items, q_dim]."""
+        n = len(seqs_pos)
+        q_rot = torch.empty((n, self.cfg.q_dim), dtype=torch.float32, device=q.device)
+        self._ck(self.L.pa_rope_append_items(self.layers[li], self._items([(s, p, 1) for s, p in seqs_pos]), n, self._p(q), q.stride(0),
+                                             q_head_stride or self.cfg.head_dim, self._p(k), self._p(v), k.stride(0), self._p(q_rot), self._st()))
+        return q_rot
+
     def _items(self, items):
         arr = (_l.PaItem * len(items))()
         for i, (seq, pos, n_cols) in enumerate(items):

@@ -490,6 +490,50 @@ extern "C" int pa_rope_append(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t 
                           kv_col_stride, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, (cudaStream_t)stream);
 }
 
+extern "C" int pa_rope_append_items(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, uint64_t q_col_stride, uint64_t q_head_stride,
+                                    const void* k, const void* v, uint64_t kv_col_stride, float* q_rot, void* stream) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (!q || !k || !v || !items) return fail(ctx, PA_EINVAL, "pa_rope_append_items: null q, k, v or items");
+  if (n_items < 1 || n_items > 32) return fail(ctx, PA_EINVAL, "pa_rope_append_items: 1 to 32 items per call");
+  if (n_items > ctx->cfg.max_cols && !q_rot) return fail(ctx, PA_EINVAL, "pa_rope_append_items: %u items exceed max_cols %u", n_items, ctx->cfg.max_cols);
+  if (ctx->cfg.rope_mode == PA_ROPE_TABLE) return fail(ctx, PA_EUNSUPPORTED, "pa_rope_append_items: PA_ROPE_TABLE takes one table per call; use pa_rope_append per sequence");
+  cudaSetDevice(ctx->device);
+  RopeParams p{};
+  p.q = q; p.q_col_stride = q_col_stride; p.q_head_stride = q_head_stride; p.q_heads = ctx->cfg.n_heads;
+  p.q_out = q_rot ? q_rot : ctx->q_rot; p.q_out_col_stride = ctx->q_dim;
+  p.k = k; p.v = v; p.kv_col_stride = kv_col_stride; p.v_col_stride = kv_col_stride; p.kv_heads = ctx->cfg.n_kv_heads;
+  p.k_cache = L->k; p.v_cache = L->v;
+  p.hd = ctx->cfg.head_dim; p.n_rot = ctx->cfg.n_rot; p.mode = ctx->cfg.rope_mode; p.in_f16 = ctx->cfg.act_dtype == PA_F16;
+  p.inv_freq = ctx->inv_freq;
+  p.n_items = n_items;
+  const uint32_t half = ctx->cfg.n_rot / 2;
+  uint32_t row0 = 0xffffffffu;
+  for (uint32_t i = 0; i < n_items; ++i) {
+    const pa_item& it = items[i];
+    if (it.n_cols != 1) return fail(ctx, PA_EINVAL, "pa_rope_append_items: item %u has %u columns; one token per item", i, it.n_cols);
+    if (it.seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "pa_rope_append_items: item %u: sequence %u of %u", i, it.seq, L->n_seqs);
+    p.item_pos[i] = it.pos;
+    const bool owns = it.pos >= L->origin && it.pos - L->origin < L->max_seq;
+    p.item_row[i] = owns ? (uint64_t)it.seq * L->max_seq + (it.pos - L->origin) : ~0ull;
+    if (owns && it.pos - L->origin < row0) row0 = it.pos - L->origin;
+    if (p.mode == PA_ROPE_F64 && n_items * half <= 64)
+      for (uint32_t j = 0; j < half; ++j) {
+        const double ang = (double)it.pos * ctx->inv_freq_host[j];
+        p.ang[i * half + j] = make_angle(cos(ang), sin(ang));
+      }
+  }
+  if (p.mode == PA_ROPE_F64 && n_items * half <= 64) p.n_ang = n_items * half;
+  CU_TRY(ctx, launch_rope_append(p, n_items, (cudaStream_t)stream));
+  ctx->stats.kernel_launches++;
+  if (row0 != 0xffffffffu) {
+    if (ctx->inflight_layer == L && ctx->inflight_row0 < row0) row0 = ctx->inflight_row0;
+    ctx->inflight_layer = L; ctx->inflight_row0 = row0;
+  }
+  return PA_OK;
+}
+
 static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, ItemList* il, uint32_t* total_cols, uint32_t* max_rows, uint32_t* max_cols,
                        uint64_t* kv_bytes, const char* who, bool sharded_ok) {
   pa_ctx* ctx = L->ctx;

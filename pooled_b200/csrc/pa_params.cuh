@@ -60,6 +60,10 @@ struct RopeParams {
   const Angle* angles;     // PA_ROPE_F64: [n_cols][n_rot/2] cos / sin of the call's columns (nullptr: evaluate here)
   uint32_t n_ang;          // > 0: a call of at most 64 angles carries them here, evaluated by the host's libm
   Angle ang[64];
+  // one token of each of several sequences in one launch (single-token kernel only): column c is item c
+  uint32_t n_items;
+  uint32_t item_pos[32];   // global position of the item's token
+  uint64_t item_row[32];   // its cache row (sequence * max_seq + position - origin), or ~0: not in this shard, no append
 };
 
 struct AnglesParams {

@@ -55,11 +55,14 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
   if (pr >= hd / 2) return;
   const uint32_t nq = p.q ? p.q_heads : 0, nk = p.k ? p.kv_heads : 0;
   uint32_t slot = blockIdx.y;
+  const uint32_t pos_c = p.n_items ? p.item_pos[col] : p.pos + col;
+  const uint64_t row_c = p.n_items ? p.item_row[col] : p.cache_row0 + col;
+  if (slot >= nq && row_c == ~0ull) return;   // an item whose row another shard holds: nothing to append
   if (slot >= nq + nk) {
     // V head: conversion only
     const uint32_t head = slot - nq - nk, kvd = p.kv_heads * hd;
     const uint64_t so = (uint64_t)col * p.v_col_stride + (uint64_t)head * hd + 2 * pr;
-    __half* dst = p.v_cache + (p.cache_row0 + col) * (uint64_t)kvd + (uint64_t)head * hd + 2 * pr;
+    __half* dst = p.v_cache + row_c * (uint64_t)kvd + (uint64_t)head * hd + 2 * pr;
     dst[0] = f16_rne(ld_act(p.v, so, p.in_f16));
     dst[1] = f16_rne(ld_act(p.v, so + 1, p.in_f16));
     return;
@@ -81,7 +84,7 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
       else if (p.angles) g = p.angles[(uint64_t)col * half + pr];
       else {
         double s, c;
-        sincos(__dmul_rn((double)(p.pos + col), p.inv_freq[pr]), &s, &c);
+        sincos(__dmul_rn((double)pos_c, p.inv_freq[pr]), &s, &c);
         g = make_angle(c, s);
       }
       ra = rot_exact(a, b, g, true);     // a cos - b sin
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
     } else if (p.q_out_f16) { __half* dst = reinterpret_cast<__half*>(p.q_out) + o; dst[d0] = __float2half_rn(ra); dst[d1] = __float2half_rn(rb); }
     else { float* dst = reinterpret_cast<float*>(p.q_out) + o; dst[d0] = ra; dst[d1] = rb; }
   } else {
-    __half* dst = p.k_cache + (p.cache_row0 + col) * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
+    __half* dst = p.k_cache + row_c * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
     dst[d0] = f16_rne(ra); dst[d1] = f16_rne(rb);
   }
   RTR(2);
@@ -356,8 +359,8 @@ cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_
   const bool vec = n_cols >= 16 && p.mode == PA_ROPE_F64 && (p.angles || p.n_ang) && p.in_f16 && p.n_rot % 16 == 0 && p.n_rot <= 256 && p.hd % 8 == 0 &&
                    (!p.q || (p.q_out_f16 == 1 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
                    (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0 && p.v_col_stride % 8 == 0));
-  if (vec) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
-  if (n_cols >= 16) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
+  if (vec && !p.n_items) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
+  if (n_cols >= 16 && !p.n_items) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
   const uint32_t slots = (p.q ? p.q_heads : 0) + (p.k ? p.kv_heads : 0) + (p.v ? p.kv_heads : 0);
   return launch_pdl(pa_rope_append_kernel, dim3(n_cols, slots), dim3(128), 0, st, p);
 }

@@ -35,7 +35,7 @@ class ShardPlan:
 
 class ShardedDecoder:
     """One decode step of a sharded layer.  `engine` needs set_origin(), rope(), rope_append(), decode_partial() and
-    merge() with AttnEngine's signatures; `dist` is torch.distributed (or a stand-in with all_gather_into_tensor).
+    merge() with AttnEngine's signatures (rope_append_items() is used when it is there); `dist` is torch.distributed (or a stand-in with all_gather_into_tensor).
     Every position stays global: the engine's layers are told which global row their cache starts at."""
 
     def __init__(self, engine, plan: ShardPlan, rank: int, dist, group=None, exchange: str = "nccl"):
@@ -52,13 +52,17 @@ class ShardedDecoder:
         n = len(seqs_pos)
         if self.exchange == "peer" and n == 1:      # one sequence: the whole layer step is one library call
             return eng.encode_layer_sharded(li, seqs_pos[0][1], q, k, v, gate, out, seq=seqs_pos[0][0])
-        q_rot = []
-        for i, (seq, pos) in enumerate(seqs_pos):
-            if plan.owner(pos) == self.rank:   # this rank owns the new row: rotate q and k, append k and v
-                q_rot.append(eng.rope_append(li, seq, pos, q[i:i + 1], k[i:i + 1], v[i:i + 1]))
-            else:
-                q_rot.append(eng.rope(q[i:i + 1], eng.cfg.n_heads, pos))
-        q_rot = q_rot[0] if n == 1 else _cat(q_rot)
+        if n > 1 and hasattr(eng, "rope_append_items"):
+            # every sequence's token in one launch; rows of other shards get their q rotated only
+            q_rot = eng.rope_append_items(li, seqs_pos, q, k, v)
+        else:
+            q_rot = []
+            for i, (seq, pos) in enumerate(seqs_pos):
+                if plan.owner(pos) == self.rank:   # this rank owns the new row: rotate q and k, append k and v
+                    q_rot.append(eng.rope_append(li, seq, pos, q[i:i + 1], k[i:i + 1], v[i:i + 1]))
+                else:
+                    q_rot.append(eng.rope(q[i:i + 1], eng.cfg.n_heads, pos))
+            q_rot = q_rot[0] if n == 1 else _cat(q_rot)
         if self.exchange == "peer":
             return eng.decode_exchange(li, [(seq, pos, 1) for seq, pos in seqs_pos], q_rot, gate, out)
         part = eng.decode_partial(li, [(seq, pos, 1) for seq, pos in seqs_pos], q_rot)

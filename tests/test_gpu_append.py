@@ -223,3 +223,36 @@ def test_head_norm_matches_the_reference_arithmetic_bit_for_bit(hd, heads, n_col
     # in place
     eng.head_norm(dx, heads, util.torch_dev(w), 1e-6, head_stride=hs)
     assert torch.equal(dx[:, :heads * hs].view(n_cols, heads, hs)[:, :, :hd], out[:, :heads * hs].view(n_cols, heads, hs)[:, :, :hd])
+
+
+def test_rope_append_items_equals_per_sequence_calls():
+    # one token of each of 8 sequences at different positions in one launch == 8 pa_rope_append calls, bit for bit; with a
+    # shard origin set, items outside the shard are rotated but not appended
+    import torch
+    nH, nKV, hd, n_rot, theta, n_seqs = 16, 2, 256, 64, 1e7, 8
+    mk = lambda: _engine(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=n_rot, rope_theta=theta, max_seq=600, act_dtype=torch.float16, n_seqs=n_seqs, max_cols=8)
+    a, b = mk(), mk()
+    rng = np.random.default_rng(3)
+    q = po.h2f(po.f16_rne(rng.standard_normal((n_seqs, nH * hd)).astype(np.float32)))
+    k = po.h2f(po.f16_rne(rng.standard_normal((n_seqs, nKV * hd)).astype(np.float32)))
+    v = po.h2f(po.f16_rne(rng.standard_normal((n_seqs, nKV * hd)).astype(np.float32)))
+    dq, dk, dv = (util.torch_dev(x, torch.float16) for x in (q, k, v))
+    seqs_pos = [(s, 37 * s + 5) for s in range(n_seqs)]
+    qa = a.rope_append_items(0, seqs_pos, dq, dk, dv).cpu().numpy()
+    qb = np.concatenate([b.rope_append(0, s, p, dq[i:i + 1], dk[i:i + 1], dv[i:i + 1]).cpu().numpy() for i, (s, p) in enumerate(seqs_pos)])
+    assert np.array_equal(qa.view(np.uint32), qb.view(np.uint32))
+    for s, p in seqs_pos:
+        ka, va = util.read_cache(a, 0, s, p, 1); kb, vb = util.read_cache(b, 0, s, p, 1)
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+        assert np.array_equal(ka[0], po.f16_rne(po.rope_neox_f64(k[s], nKV, hd, n_rot, p, theta)))
+    # a shard that starts at global position 100: items below it leave the caches alone
+    c = mk(); c.set_origin(0, 100)
+    before = c.cache(0, "k").clone()
+    qc = c.rope_append_items(0, seqs_pos, dq, dk, dv).cpu().numpy()
+    assert np.array_equal(qc.view(np.uint32), qa.view(np.uint32))
+    after = c.cache(0, "k")
+    for s, p in seqs_pos:
+        if p >= 100:
+            assert np.array_equal(after[s, p - 100].cpu().numpy().view(np.uint16), util.read_cache(a, 0, s, p, 1)[0][0])
+    touched = (after != before).any(dim=2).sum().item()
+    assert touched <= sum(1 for _, p in seqs_pos if p >= 100)
