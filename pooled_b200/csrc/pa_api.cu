@@ -278,6 +278,9 @@ extern "C" int pa_reset(pa_ctx* ctx) {
   *ctx->host_err = 0;
   ctx->failed = false;
   ctx->err.clear();
+  // nothing cached survives a failed step: the angle table is refilled, no early fetch is assumed safe
+  ctx->angles_valid = false; ctx->scope_active = false; ctx->scope_fresh = false;
+  ctx->inflight_layer = nullptr;
   return PA_OK;
 }
 
