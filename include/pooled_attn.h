@@ -142,7 +142,8 @@ PA_API int pa_head_norm(pa_ctx* ctx, const void* x, uint64_t col_stride, uint64_
  * then on pa_attn_layer / pa_attn_layer_host / pa_attn_step_host / pa_attn_layer_sharded on this layer apply
  * pa_head_norm to q and k first (one extra kernel per call, into scratch of the context), which makes the call the
  * whole of attn_glue_kv + attn core + gate (engine/wgsl/layer_fuse.js:87-146): q_full, k and v go in as the GEMVs
- * leave them.  Passing null weights turns it off. */
+ * leave them.  Passing null weights turns it off.  The first call on a context allocates that scratch: make it outside
+ * a stream capture. */
 PA_API int pa_layer_set_head_norm(pa_layer* layer, const float* q_w, const float* k_w, double eps);
 
 /* RoPE.  Replaces rope_part / rope_part_mc (engine/wgsl/qwen35.js:386-404, :858-875), the full-head rope
