@@ -3,7 +3,7 @@
 
     python bench.py --gpus N --steps K --warmup W [--workload c2|c1|c4|c5|c3] [--impl reference]
 
-Default workload (c2): BASELINE config 2, the 35B-MoE decode attention layer — 16 q / 2 kv heads, head_dim 256,
+Default workload (c2): the headline configuration, the 35B-MoE decode attention layer — 16 q / 2 kv heads, head_dim 256,
 partial RoPE (64 dims, theta 1e7), sigmoid gate, 32768-token f16 KV context, one new token — for the model's 10
 attention layers.  A step is one decode token through those 10 layers: RoPE + KV append + split-K decode + combine +
 gate per layer, each layer with its own caches (10 x 67 MB, so no layer's K/V survives in the 126 MB L2 until its

@@ -63,7 +63,7 @@ def test_attn_dec_js_cases(ref_inputs, run):
     print(f"run {run}: worst relDiff vs f64 {worst:.2e}")
 
 
-# ---- BASELINE configurations -------------------------------------------------------------------------
+# ---- the five benchmark configurations -------------------------------------------------------------------------
 
 def _config_inputs(cfg_id, nH, nKV, hd, rows, n_cols, outliers=False):
     K = util.normal_f16(0xB0B + cfg_id, (rows, nKV * hd)); V = util.normal_f16(0xC0DE + cfg_id, (rows, nKV * hd))

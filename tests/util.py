@@ -5,7 +5,7 @@ import numpy as np
 
 from oracle import po
 
-# BASELINE tolerance on f16 outputs: max-abs 2e-3 and max-rel 1e-2, the relative error taken as the reference's
+# Tolerance on f16 outputs: max-abs 2e-3 and max-rel 1e-2, the relative error taken as the reference's
 # own tests take it: max |diff| / max |ref| (tests/test_attn_dec.js:87-88)
 MAX_ABS, MAX_REL = 2e-3, 1e-2
 # the reference's own bound for attn_dec with f32 q and f32 outputs (tests/test_attn_dec.js:98)
