@@ -448,11 +448,16 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling captures)")
     ap.add_argument("--ctx", type=int, default=0, help="override the decode workloads' context length (scaling probes)")
     ap.add_argument("--cols", type=int, default=0, help="override the prompt length of the prefill workload (small profiling captures)")
-    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the decode kernel, if known")
+    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the dominant kernel (default: the figure of the committed capture, where one exists for the workload at its full per-launch size)")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.layers > 0:
         w["layers"] = args.layers
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures summarised
+    # under profiles/ (same per-launch shape as the bench's; the captures only use fewer layers)
+    CAPTURED_TRAFFIC = {"c2": 67.32e6 + 0.62e6, "c4": 67.34e6 + 1.56e6}
+    if args.traffic is None and args.ctx <= 0 and args.cols <= 0 and args.gpus == 1:
+        args.traffic = CAPTURED_TRAFFIC.get(args.workload)
     if args.ctx > 0 and args.workload != "c3":
         w["ctx"] = args.ctx
     if args.cols > 0 and args.workload == "c3":
