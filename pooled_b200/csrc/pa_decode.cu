@@ -3,7 +3,7 @@
 // One CTA per (split of the KV sequence, kv head, item).  All query rows that share the kv head — the G
 // heads of the GQA group times the item's columns, at most 64 — ride in the same CTA, so every K and V
 // byte is fetched from HBM once.  A producer thread streams 64-position K and V tiles with TMA
-// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of shared-memory slots guarded by
+// (cp.async.bulk.tensor, 128-byte swizzle, each CTA fetching its own tiles) into a ring of shared-memory slots guarded by
 // mbarriers; four consumer warps take the tiles apart with ldmatrix and multiply on the tensor cores
 // (mma.sync m16n8k16, f32 accumulate):
 //     S^T[pos, row] = K[pos, :] . Q[row, :]        warp w owns positions 16w .. 16w+15 of the tile
