@@ -97,8 +97,34 @@ PA_API int pa_layer_destroy(pa_layer* layer);
  * position passed to later calls stays global; appends must fall inside [origin, origin + max_seq), decode
  * partials cover the rows of [0, pos + c + 1) the shard holds (possibly none).  No counterpart in the reference. */
 PA_API int pa_layer_set_origin(pa_layer* layer, uint32_t origin);
+/* Tells the library which layer the engine runs after this one (NULL: unknown).  pooled's engines walk their layers in
+ * a fixed order (the loop over layers in forwardToken, engine/qwen35.js:4214-4222, and the last layer is followed by the
+ * first one of the next token), so the order is known when the layers are created.  A decode call on `layer` then asks
+ * L2, once it has requested its own last K/V tile, for the first tiles the same call on `next` will read: HBM keeps
+ * delivering while this call drains and the next one starts.  A hint only: results do not depend on it. */
+PA_API int pa_layer_set_next(pa_layer* layer, pa_layer* next);
 /* Device pointer of the K (which = 0) or V (1) cache: what _stateParts exports (engine/qwen35.js:129-141). */
 PA_API void* pa_cache_ptr(pa_layer* layer, int which);
+/* KV state of one sequence to and from the host: cache rows of global positions [pos0, pos1) x kv_dim f16, K (which = 0)
+ * or V (1), row p at host + (p - pos0) * kv_dim * 2 bytes.  These are the parts _stateParts lists per full-attention
+ * layer ({buf: kCache, bytes: pos * kvRow}, engine/qwen35.js:129-141) and exportState / importState move
+ * (engine/qwen35.js:153-196).  On a shard (pa_layer_set_origin) only the rows the shard holds are copied, each to its
+ * place in the same host image, so the ranks of a sharded sequence export disjoint ranges; rows_copied (may be NULL)
+ * receives how many.  Asynchronous on `stream` (use pinned host memory and pa_sync before reading). */
+PA_API int pa_cache_export(pa_layer* layer, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, void* host_dst,
+                           uint32_t* rows_copied, void* stream);
+PA_API int pa_cache_import(pa_layer* layer, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, const void* host_src,
+                           uint32_t* rows_copied, void* stream);
+/* GPU-side checkpoints of one sequence's rows [0, pos) of a layer: saveSlot / loadSlot / exportSlot / dropSlot
+ * (engine/qwen35.js:197-228, :157-165), copies on the device with no readback.  A slot costs two device buffers of
+ * pos * kv_dim * 2 bytes; pa_slot_load writes them back (into any sequence index of a layer of the same context and
+ * shard) and reports the saved position; pa_slot_export reads a slot back to the host without switching to it. */
+typedef struct pa_slot pa_slot;
+PA_API int pa_slot_save(pa_layer* layer, uint32_t seq, uint32_t pos, pa_slot** out, void* stream);
+PA_API int pa_slot_load(pa_layer* layer, uint32_t seq, const pa_slot* slot, uint32_t* pos_out, void* stream);
+PA_API int pa_slot_export(const pa_slot* slot, int which, void* host_dst, void* stream);
+PA_API int pa_slot_info(const pa_slot* slot, uint32_t* pos, uint32_t* first_row, uint32_t* rows);
+PA_API int pa_slot_drop(pa_slot* slot);
 PA_API const char* pa_last_error(pa_ctx* ctx);
 PA_API const char* pa_version(void);
 /* Waits for the stream and reports a device-side failure (onSubmittedWorkDone, engine/qwen35.js:3859). */
@@ -212,7 +238,15 @@ PA_API size_t pa_exchange_bytes(pa_ctx* ctx, uint32_t world, uint32_t max_rows);
 PA_API int pa_shared_alloc(pa_ctx* ctx, size_t bytes, void** dev_ptr, void* ipc_handle_out);
 PA_API int pa_shared_open(pa_ctx* ctx, const void* ipc_handle, void** dev_ptr);
 PA_API int pa_shared_close(pa_ctx* ctx, void* dev_ptr);
+/* pa_exchange_init starts a session: it waits for the device, zeroes this rank's own buffer and the call counter, so
+ * buffers may be reused after an earlier session.  Every rank must call it, and all ranks must pass a barrier of their
+ * own (any channel) between their pa_exchange_init and the first exchanging call of any rank: peers write into this
+ * rank's buffer from that call on. */
 PA_API int pa_exchange_init(pa_ctx* ctx, uint32_t rank, uint32_t world, void* const* bufs, uint32_t max_rows);
+/* Limit of the polling loop in which an exchanging call waits for the other ranks' records (sweeps over the missing
+ * entries; 0 restores the built-in 2^20, about a second).  When it runs out the kernel records status 7, finishes with
+ * what it has, and pa_sync reports PA_ETIMEOUT: a peer that died between steps costs one bounded wait, not a hang. */
+PA_API int pa_set_wait_limit(pa_ctx* ctx, uint32_t sweeps);
 /* pa_decode over this rank's shard with the cross-GPU merge inside the combine kernel: each CTA stores its merged
  * (o, m, l) slice into every rank's exchange buffer over NVLink, each value as one 8-byte {value, call tag} store,
  * spins (bounded) on its own buffer until the other ranks' entries carry the call's tag, merges and writes the gated
@@ -292,6 +326,14 @@ PA_API int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uint32_
 PA_API int pa_decode_static(int device, const void* k_cache, const void* v_cache, uint32_t cache_rows, uint32_t n_heads,
                             uint32_t n_kv_heads, uint32_t head_dim, uint32_t pos, uint32_t n_cols, const float* q,
                             const float* gate, float* out, void* stream, char* msg, size_t msg_len);
+/* Waits for `stream` and hands back the status word of pa_decode_static's bounded device-side waits on `device`
+ * (0: all satisfied; then PA_OK, else PA_ETIMEOUT and the outputs of the calls since the last clear are not to be
+ * trusted).  pa_decode_static clears the word at the start of each call, so ask before the next call.  A 4-byte copy out
+ * of the same built-in array: allocates nothing.  Further notes on pa_decode_static: it makes `device` the calling
+ * thread's current device and leaves it so; its one-time set-up is serialised between host threads; kernel attributes
+ * are set the first time each row-count class (1-8, 9-16, 17-32, 33-64 query rows per kv head) is used on a device, so
+ * the "first call outside a capture" rule holds per class. */
+PA_API int pa_decode_static_status(int device, void* stream, uint32_t* word);
 
 /* Counters since creation: what tests/bench_attn_ctx.js collects with timestamp queries. */
 typedef struct pa_stats {

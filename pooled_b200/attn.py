@@ -76,6 +76,7 @@ class AttnConfig:
     max_cols: int = 8
     splits: int = 0
     fast: bool = False
+    link_layers: bool = True          # layers run in index order, the last one followed by the first (pa_layer_set_next)
 
     @property
     def q_dim(self) -> int:
@@ -117,6 +118,8 @@ class AttnEngine:
         h = C.c_void_p()
         self.ctx = None
         self.layers: list[C.c_void_p] = []
+        self.slots: dict[str, dict] = {}
+        self._xc_keep = None
         self.L.check(self.L.pa_create(device, C.byref(pc), C.byref(h)))
         self.ctx = h
         try:
@@ -124,6 +127,9 @@ class AttnEngine:
                 lh = C.c_void_p()
                 self.L.check(self.L.pa_layer_create(self.ctx, cfg.n_seqs, cfg.max_seq, C.byref(lh)), self.ctx)
                 self.layers.append(lh)
+            if cfg.link_layers and cfg.n_layers > 1:
+                for li, lh in enumerate(self.layers):
+                    self.L.check(self.L.pa_layer_set_next(lh, self.layers[(li + 1) % cfg.n_layers]), self.ctx)
         except Exception:
             self.destroy()
             raise
@@ -144,6 +150,9 @@ class AttnEngine:
         return C.c_void_p(t.data_ptr()) if t is not None else None
 
     def destroy(self):
+        if self.ctx:
+            self.drop_all_slots()
+            self._exchange_release()
         for lh in self.layers:
             self.L.pa_layer_destroy(lh)
         self.layers = []
@@ -338,6 +347,91 @@ class AttnEngine:
                                           gate_head_stride or self.cfg.head_dim, self._p(out), out.stride(0), out.stride(1), self._st()))
         return out
 
+    # ---- session state: what the engine's exportState / importState / saveSlot / loadSlot move for its attention layers ----
+    def state_signature(self) -> dict:
+        """What a saved state must match to be loaded here (stateSignature, engine/qwen35.js:143-151, attention part)."""
+        c = self.cfg
+        return {"v": 1, "layers": c.n_layers, "kv": "f16", "dims": [c.kv_dim, c.n_kv_heads, c.head_dim]}
+
+    def _state_parts(self, pos: int):
+        """_stateParts (engine/qwen35.js:129-141): per layer the K rows [0, pos) then the V rows [0, pos)."""
+        return [(li, which, pos * self.cfg.kv_dim * 2) for li in range(len(self.layers)) for which in (0, 1)]
+
+    def export_state(self, pos: int, seq: int = 0) -> dict:
+        """exportState (engine/qwen35.js:153): {sig, pos, parts: [bytes]}, rows [0, pos) of every layer.  On a shard the
+        parts hold this rank's rows at their place and zeros elsewhere; `held` says which rows are this rank's."""
+        parts, held = [], []
+        for li, which, nbytes in self._state_parts(pos):
+            host = torch.zeros(max(nbytes, 1), dtype=torch.uint8).pin_memory()
+            n = C.c_uint32()
+            self._ck(self.L.pa_cache_export(self.layers[li], seq, 0, pos, which, C.c_void_p(host.data_ptr()), C.byref(n), self._st()))
+            parts.append(host); held.append(n.value)
+        self.sync()
+        return {"sig": self.state_signature(), "pos": pos, "parts": [bytes(h[:nb].numpy()) for h, (_, _, nb) in zip(parts, self._state_parts(pos))],
+                "held": held}
+
+    def import_state(self, st: dict, seq: int = 0) -> int:
+        """importState (engine/qwen35.js:181-196): refuses a state of another shape; returns the restored position."""
+        if st["sig"] != self.state_signature():
+            raise _l.PaError(-1, "saved state is for a different model, layer range or KV format")
+        parts = self._state_parts(st["pos"])
+        if len(parts) != len(st["parts"]) or any(nb != len(b) for (_, _, nb), b in zip(parts, st["parts"])):
+            raise _l.PaError(-1, "saved state has the wrong shape")
+        keep = []
+        for (li, which, nbytes), b in zip(parts, st["parts"]):
+            if not nbytes:
+                continue
+            host = torch.frombuffer(bytearray(b), dtype=torch.uint8).pin_memory()
+            keep.append(host)
+            self._ck(self.L.pa_cache_import(self.layers[li], seq, 0, st["pos"], which, C.c_void_p(host.data_ptr()), None, self._st()))
+        self.sync()
+        return st["pos"]
+
+    def save_slot(self, name: str, pos: int, seq: int = 0):
+        """saveSlot (engine/qwen35.js:200-211): a copy of rows [0, pos) of every layer on the device."""
+        self.drop_slot(name)
+        hs = []
+        for lh in self.layers:
+            h = C.c_void_p()
+            self._ck(self.L.pa_slot_save(lh, seq, pos, C.byref(h), self._st()))
+            hs.append(h)
+        self.slots[name] = {"pos": pos, "handles": hs}
+
+    def load_slot(self, name: str, seq: int = 0) -> int:
+        """loadSlot (engine/qwen35.js:212-222): returns the slot's position."""
+        sl = self.slots.get(name)
+        if sl is None:
+            raise _l.PaError(-1, "no saved slot " + name)
+        for lh, h in zip(self.layers, sl["handles"]):
+            self._ck(self.L.pa_slot_load(lh, seq, h, None, self._st()))
+        return sl["pos"]
+
+    def export_slot(self, name: str) -> dict:
+        """exportSlot (engine/qwen35.js:157-165): a slot read back without switching to it."""
+        sl = self.slots.get(name)
+        if sl is None:
+            raise _l.PaError(-1, "no saved slot " + name)
+        parts = []
+        for h in sl["handles"]:
+            rows = C.c_uint32()
+            self._ck(self.L.pa_slot_info(h, None, None, C.byref(rows)))
+            for which in (0, 1):
+                host = torch.zeros(max(rows.value * self.cfg.kv_dim * 2, 1), dtype=torch.uint8).pin_memory()
+                self._ck(self.L.pa_slot_export(h, which, C.c_void_p(host.data_ptr()), self._st()))
+                parts.append((host, rows.value * self.cfg.kv_dim * 2))
+        self.sync()
+        return {"sig": self.state_signature(), "pos": sl["pos"], "parts": [bytes(h[:nb].numpy()) for h, nb in parts]}
+
+    def drop_slot(self, name: str):
+        sl = self.slots.pop(name, None)
+        if sl:
+            for h in sl["handles"]:
+                self.L.pa_slot_drop(h)
+
+    def drop_all_slots(self):
+        for k in list(self.slots):
+            self.drop_slot(k)
+
     # ---- sharded decode with the merge over peer memory ----
     def exchange_setup(self, rank: int, world: int, dist=None, max_rows: int = 512):
         """Allocate this rank's exchange buffer, swap IPC handles with the other ranks (torch.distributed object
@@ -357,10 +451,26 @@ class AttnEngine:
                 pp = C.c_void_p()
                 self._ck(self.L.pa_shared_open(self.ctx, C.create_string_buffer(handles[r], 64), C.byref(pp)))
                 ptrs[r] = pp.value
-        self._xc_keep = (own, ptrs)
+        self._exchange_release()   # buffers of an earlier session
+        self._xc_keep = (own, ptrs, rank, world)
         self._ck(self.L.pa_exchange_init(self.ctx, rank, world, ptrs, max_rows))
         if world > 1:
             dist.barrier()   # nobody writes into a buffer that is not mapped yet
+
+    def _exchange_release(self):
+        if not self._xc_keep:
+            return
+        own, ptrs, rank, world = self._xc_keep
+        torch.cuda.synchronize(self.device)
+        for r in range(world):
+            if r != rank and ptrs[r]:
+                self.L.pa_shared_close(self.ctx, C.c_void_p(ptrs[r]))
+        self.L.pa_free(self.ctx, own)
+        self._xc_keep = None
+
+    def set_wait_limit(self, sweeps: int):
+        """Polling limit of the cross-GPU exchange wait (0: the built-in limit, about a second)."""
+        self._ck(self.L.pa_set_wait_limit(self.ctx, sweeps))
 
     def decode_exchange(self, li: int, items, q: torch.Tensor, gate: torch.Tensor | None = None, out: torch.Tensor | None = None,
                         q_head_stride: int | None = None, gate_head_stride: int | None = None) -> torch.Tensor:

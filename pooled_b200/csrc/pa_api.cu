@@ -6,6 +6,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <new>
 
 #include "pa_common.cuh"
@@ -154,6 +155,10 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   ctx->q_dim = cfg->n_heads * cfg->head_dim;
   ctx->kv_dim = cfg->n_kv_heads * cfg->head_dim;
   ctx->max_splits = 256;
+  if (const char* e = getenv("POOLED_ATTN_PRE_STAGES")) ctx->tune.pre_stages = atoi(e) < 0 ? 0 : atoi(e);
+  if (const char* e = getenv("POOLED_ATTN_NEXT_TILES")) ctx->tune.next_tiles = atoi(e) < 0 ? 0 : atoi(e);
+  ctx->tune.no_fuse = getenv("POOLED_ATTN_NO_FUSE") != nullptr;
+  ctx->tune.verify_mma_sync = getenv("POOLED_ATTN_VERIFY_MMA_SYNC") != nullptr;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -234,6 +239,13 @@ extern "C" int pa_layer_destroy(pa_layer* L) {
 extern "C" int pa_layer_set_origin(pa_layer* L, uint32_t origin) {
   if (!L) return PA_EINVAL;
   L->origin = origin;
+  return PA_OK;
+}
+
+extern "C" int pa_layer_set_next(pa_layer* L, pa_layer* next) {
+  if (!L) return PA_EINVAL;
+  if (next && next->ctx != L->ctx) return fail(L->ctx, PA_EINVAL, "pa_layer_set_next: the layers belong to different contexts");
+  L->next = next;
   return PA_OK;
 }
 
@@ -372,21 +384,6 @@ static int check_cols(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   return PA_OK;
 }
 
-#ifdef PA_TRACE
-// Development builds: one region of 256 CTAs x 256 timestamp slots per decode call, 32 regions in rotation, never
-// cleared (a replayed graph leaves the timestamps of its last replay).  Rows 0..159 decode CTAs, 160..223 combine
-// CTAs, 224..255 RoPE/append CTAs of the same layer call.
-static unsigned g_trace_call = 0;
-static unsigned long long* trace_region(unsigned call) {
-  static unsigned long long* tr = nullptr;
-  if (!tr) {
-    cudaMalloc(&tr, 32ull * 256 * 256 * 8);
-    cudaMemset(tr, 0, 32ull * 256 * 256 * 8);
-    if (getenv("PA_TRACE_PTR")) { FILE* f = fopen(getenv("PA_TRACE_PTR"), "w"); fprintf(f, "%llu\n", (unsigned long long)(uintptr_t)tr); fclose(f); }
-  }
-  return tr + (size_t)(call % 32) * 256 * 256;
-}
-#endif
 
 // cos / sin of a call of at most 64 angles, evaluated by the host's libm and kept while the position repeats (every
 // layer of a step asks for the same ones)
@@ -447,9 +444,6 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
       p.angles = ctx->angles;
     }
   }
-#ifdef PA_TRACE
-  if (n_cols <= 15) p.trace = trace_region(g_trace_call);   // the decode call that follows takes the same region
-#endif
   CU_TRY(ctx, launch_rope_append(p, n_cols, st));
   ctx->stats.kernel_launches++;
   if (L && k) {
@@ -594,22 +588,17 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   // fetched while that kernel still runs
   p.prefetch_old_rows = after_own_append ? 1u : 0u;
   p.early_limit = (after_own_append && ctx->inflight_layer == L) ? ctx->inflight_row0 : 0xffffffffu;
-  {
-    static const int env_pre = getenv("POOLED_ATTN_PRE_STAGES") ? atoi(getenv("POOLED_ATTN_PRE_STAGES")) : -1;
-    p.pre_stages = env_pre >= 0 ? (uint32_t)env_pre : 2u;
-  }
+  p.pre_stages = (uint32_t)ctx->tune.pre_stages;
+  p.next_tiles = (L->next && L->next->ctx == ctx) ? (uint32_t)ctx->tune.next_tiles : 0u;
   if (fz) {
     p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
     p.k_cache = L->k; p.v_cache = L->v;
     memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), (size_t)(ctx->cfg.n_rot / 2) * sizeof(Angle));
   }
-#ifdef PA_TRACE
-  p.trace = trace_region(g_trace_call++);
-#endif
   const int nt = (int)ceil_div(max_cols * ctx->G, 8);
   // One sequence with more than 8 query rows per kv head (a k-token verify block) goes to the tensor-core split-K
   // kernel; single tokens and batches of sequences stay on the streaming mma.sync kernel.
-  const bool verify_tc = n_items == 1 && nt > 1 && max_rows > 0 && !getenv("POOLED_ATTN_VERIFY_MMA_SYNC");
+  const bool verify_tc = n_items == 1 && nt > 1 && max_rows > 0 && !ctx->tune.verify_mma_sync;
   CUtensorMap tm_k, tm_v;
   PrefillParams vp{};
   if (verify_tc) {
@@ -620,9 +609,6 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
     vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit; vp.pre_stages = p.pre_stages;
-#ifdef PA_TRACE
-    vp.trace = p.trace;
-#endif
     vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);
@@ -633,9 +619,6 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   timing_mark(ctx, st, 1);
   CombineParams c{};
   c.o = ctx->part_o; c.ml = ctx->part_ml;
-#ifdef PA_TRACE
-  c.trace = p.trace;
-#endif
   const uint32_t rs = ns;
   c.o_row_stride = (uint64_t)rs * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
   c.ml_row_stride = (uint64_t)rs * 2; c.ml_part_stride = 2;
@@ -644,6 +627,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   c.act_f16 = ctx->cfg.act_dtype == PA_F16;
   c.partial_out = partial; c.partial_rows = (uint64_t)total_cols * ctx->cfg.n_heads;
   c.exchange = exchange ? 1 : 0; c.xc = ctx->xc; c.err = ctx->dev_err;
+  c.xch_sweeps = ctx->tune.wait_polls ? ctx->tune.wait_polls : (1u << 20);
   c.items = p.items; c.n_items = n_items;
   if (!ctx->core_only) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
   ctx->stats.kernel_launches += ctx->core_only ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
@@ -713,15 +697,6 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   const uint64_t seq_off = (uint64_t)seq * L->max_seq * ctx->kv_dim;
   if (int rc = make_cache_map(ctx, &tm_k, L->k + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
   if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
-#ifdef PA_TRACE
-  {
-    static unsigned long long* tr = nullptr;
-    if (!tr) cudaMalloc(&tr, 4096 * 256 * 8);
-    cudaMemsetAsync(tr, 0, 4096 * 256 * 8, st);
-    p.trace = tr;
-    if (getenv("PA_TRACE_PTR")) { FILE* f = fopen(getenv("PA_TRACE_PTR"), "w"); fprintf(f, "%llu\n", (unsigned long long)(uintptr_t)tr); fclose(f); }
-  }
-#endif
   timing_mark(ctx, st, 0);
   CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, st));
   timing_mark(ctx, st, 1);
@@ -778,7 +753,7 @@ extern "C" int pa_sigmoid_mul(pa_ctx* ctx, void* a, uint64_t a_col_stride, const
 static bool can_fuse_front(const pa_ctx* ctx, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs, const void* k, const void* v) {
   const uint32_t nr = ctx->cfg.n_rot, hd = ctx->cfg.head_dim;
   return !ctx->core_only && n_cols == 1 && ctx->cfg.rope_mode == PA_ROPE_F64 && ((hd == 256 && nr == 64) || (hd == 128 && nr == 128)) && ctx->G <= 8 &&
-         !(qcs & 1) && !(qhs & 1) && !((uintptr_t)q & 7) && !((uintptr_t)k & 7) && !((uintptr_t)v & 7) && !getenv("POOLED_ATTN_NO_FUSE");
+         !(qcs & 1) && !(qhs & 1) && !((uintptr_t)q & 7) && !((uintptr_t)k & 7) && !((uintptr_t)v & 7) && !ctx->tune.no_fuse;
 }
 
 static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t qcs, uint64_t qhs, const void* k,
@@ -808,7 +783,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // A k-token block on the tensor-core split-K kernel in its hi/lo form takes q as two f16 planes (high and low parts),
   // which the RoPE kernel writes directly: nothing is left to convert in the attention kernel's prologue.
   const bool planes = mode != PA_MODE_PREFILL && n_cols * ctx->G > 8 && n_cols * ctx->G <= (uint32_t)kMaxRows && !(ctx->cfg.flags & PA_FLAG_FAST) &&
-                      !getenv("POOLED_ATTN_VERIFY_MMA_SYNC");
+                      !ctx->tune.verify_mma_sync;
   if (sharded) {
     // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
     const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
@@ -817,9 +792,24 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
       pa_item it{seq, pos, 1, 0};
       return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true, &fz);
     }
+    // columns [c_lo, c_hi) of the block fall into this shard; a block may straddle a shard boundary, in which case
+    // each rank appends its own columns (q is rotated for all of them everywhere)
+    const uint64_t s_lo = L->origin, s_hi = (uint64_t)L->origin + L->max_seq;
+    const uint32_t c_lo = pos >= s_lo ? 0u : (uint32_t)std::min<uint64_t>(s_lo - pos, n_cols);
+    const uint32_t c_hi = (uint64_t)pos + n_cols <= s_hi ? n_cols : (pos >= s_hi ? 0u : (uint32_t)(s_hi - pos));
+    const bool some = c_lo < c_hi, straddles = some && !owns;
     if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
                                   owns ? v : nullptr, kcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, planes ? 2 : 0, true, kvcs))
       return rc;
+    if (straddles) {
+      const size_t es = ctx->cfg.act_dtype == PA_F16 ? 2 : 4;
+      const uint8_t* k2 = reinterpret_cast<const uint8_t*>(k) + (size_t)c_lo * kcs * es;
+      const uint8_t* v2 = reinterpret_cast<const uint8_t*>(v) + (size_t)c_lo * kvcs * es;
+      const float* t2 = cs_table ? cs_table + (size_t)c_lo * ctx->cfg.n_rot : nullptr;
+      if (int rc = rope_append_impl(L, ctx, seq, pos + c_lo, c_hi - c_lo, nullptr, 0, 0, 0, nullptr, 0, k2, v2, kcs, t2, ctx->cfg.rope_mode,
+                                    ctx->cfg.act_dtype == PA_F16, st, 0, true, kvcs))
+        return rc;
+    }
     pa_item it{seq, pos, n_cols, 0};
     if (planes)
       return decode_impl(L, &it, 1, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true,
@@ -954,6 +944,119 @@ extern "C" int pa_attn_step_host(pa_layer* const* layers, uint32_t n_layers, uin
   return pa_sync(ctx, stream);
 }
 
+
+// ------------------------------------------------------------------------------ cache export / import, slots --
+
+// rows of [pos0, pos1) this layer's shard holds: first global position and count
+static uint32_t shard_span(const pa_layer* L, uint32_t pos0, uint32_t pos1, uint32_t* first) {
+  const uint64_t lo = std::max<uint64_t>(pos0, L->origin), hi = std::min<uint64_t>(pos1, (uint64_t)L->origin + L->max_seq);
+  *first = (uint32_t)lo;
+  return hi > lo ? (uint32_t)(hi - lo) : 0u;
+}
+static int cache_copy(pa_layer* L, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, void* host, bool to_host, uint32_t* rows_out, void* stream,
+                      const char* who) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (rows_out) *rows_out = 0;
+  if (!host || (which != 0 && which != 1)) return fail(ctx, PA_EINVAL, "%s: null host buffer, or `which` is neither 0 (K) nor 1 (V)", who);
+  if (seq >= L->n_seqs || pos1 < pos0) return fail(ctx, PA_EINVAL, "%s: sequence %u of %u, positions [%u, %u)", who, seq, L->n_seqs, pos0, pos1);
+  uint32_t first;
+  const uint32_t n = shard_span(L, pos0, pos1, &first);
+  if (rows_out) *rows_out = n;
+  if (!n) return PA_OK;
+  cudaSetDevice(ctx->device);
+  const size_t row_bytes = (size_t)ctx->kv_dim * 2;
+  uint8_t* dev = reinterpret_cast<uint8_t*>(which ? L->v : L->k) + ((size_t)seq * L->max_seq + (first - L->origin)) * row_bytes;
+  uint8_t* h = reinterpret_cast<uint8_t*>(host) + (size_t)(first - pos0) * row_bytes;
+  if (to_host) CU_TRY(ctx, cudaMemcpyAsync(h, dev, (size_t)n * row_bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  else {
+    CU_TRY(ctx, cudaMemcpyAsync(dev, h, (size_t)n * row_bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    ctx->inflight_layer = nullptr;   // a copy is ordered by the stream like any kernel, but it is no PDL predecessor:
+  }                                  // nothing of the next call may start ahead of it (see decode_impl)
+  return PA_OK;
+}
+extern "C" int pa_cache_export(pa_layer* L, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, void* host_dst, uint32_t* rows_copied, void* stream) {
+  return cache_copy(L, seq, pos0, pos1, which, host_dst, true, rows_copied, stream, "pa_cache_export");
+}
+extern "C" int pa_cache_import(pa_layer* L, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, const void* host_src, uint32_t* rows_copied,
+                               void* stream) {
+  return cache_copy(L, seq, pos0, pos1, which, const_cast<void*>(host_src), false, rows_copied, stream, "pa_cache_import");
+}
+
+struct pa_slot {
+  pa_ctx* ctx = nullptr;
+  uint32_t pos = 0, first = 0, rows = 0;   // positions [0, pos) were saved; this shard held `rows` of them from `first`
+  size_t row_bytes = 0;
+  uint8_t* k = nullptr;
+  uint8_t* v = nullptr;
+};
+extern "C" int pa_slot_save(pa_layer* L, uint32_t seq, uint32_t pos, pa_slot** out, void* stream) {
+  if (!L || !out) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  *out = nullptr;
+  if (seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "pa_slot_save: sequence %u of %u", seq, L->n_seqs);
+  pa_slot* s = new (std::nothrow) pa_slot();
+  if (!s) return fail(ctx, PA_ENOMEM, "pa_slot_save: out of host memory");
+  s->ctx = ctx; s->pos = pos; s->row_bytes = (size_t)ctx->kv_dim * 2;
+  s->rows = shard_span(L, 0, pos, &s->first);
+  cudaSetDevice(ctx->device);
+  if (s->rows) {
+    const size_t bytes = (size_t)s->rows * s->row_bytes;
+    if (cudaMalloc(&s->k, bytes) != cudaSuccess || cudaMalloc(&s->v, bytes) != cudaSuccess) {
+      cudaGetLastError(); cudaFree(s->k); delete s;
+      return fail(ctx, PA_ENOMEM, "pa_slot_save: two copies of %u rows (%.0f MiB each) do not fit on the device", pos, bytes / 1048576.0);
+    }
+    const size_t off = ((size_t)seq * L->max_seq + (s->first - L->origin)) * s->row_bytes;
+    CU_TRY(ctx, cudaMemcpyAsync(s->k, reinterpret_cast<uint8_t*>(L->k) + off, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    CU_TRY(ctx, cudaMemcpyAsync(s->v, reinterpret_cast<uint8_t*>(L->v) + off, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  }
+  *out = s;
+  return PA_OK;
+}
+extern "C" int pa_slot_load(pa_layer* L, uint32_t seq, const pa_slot* s, uint32_t* pos_out, void* stream) {
+  if (!L || !s) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (s->ctx != ctx || s->row_bytes != (size_t)ctx->kv_dim * 2) return fail(ctx, PA_EINVAL, "pa_slot_load: the slot was saved from another context");
+  if (seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "pa_slot_load: sequence %u of %u", seq, L->n_seqs);
+  uint32_t first;
+  const uint32_t rows = shard_span(L, 0, s->pos, &first);
+  if (rows != s->rows || (rows && first != s->first)) return fail(ctx, PA_EINVAL, "pa_slot_load: the slot holds rows %u..%u, this layer's shard would hold %u..%u",
+                                                                  s->first, s->first + s->rows, first, first + rows);
+  cudaSetDevice(ctx->device);
+  if (rows) {
+    const size_t bytes = (size_t)rows * s->row_bytes, off = ((size_t)seq * L->max_seq + (first - L->origin)) * s->row_bytes;
+    CU_TRY(ctx, cudaMemcpyAsync(reinterpret_cast<uint8_t*>(L->k) + off, s->k, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    CU_TRY(ctx, cudaMemcpyAsync(reinterpret_cast<uint8_t*>(L->v) + off, s->v, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    ctx->inflight_layer = nullptr;
+  }
+  if (pos_out) *pos_out = s->pos;
+  return PA_OK;
+}
+extern "C" int pa_slot_export(const pa_slot* s, int which, void* host_dst, void* stream) {
+  if (!s || !host_dst || (which != 0 && which != 1)) return PA_EINVAL;
+  pa_ctx* ctx = s->ctx;
+  cudaSetDevice(ctx->device);
+  if (s->rows) CU_TRY(ctx, cudaMemcpyAsync(host_dst, which ? s->v : s->k, (size_t)s->rows * s->row_bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return PA_OK;
+}
+extern "C" int pa_slot_info(const pa_slot* s, uint32_t* pos, uint32_t* first_row, uint32_t* rows) {
+  if (!s) return PA_EINVAL;
+  if (pos) *pos = s->pos;
+  if (first_row) *first_row = s->first;
+  if (rows) *rows = s->rows;
+  return PA_OK;
+}
+extern "C" int pa_slot_drop(pa_slot* s) {
+  if (!s) return PA_OK;
+  cudaSetDevice(s->ctx->device);
+  cudaFree(s->k); cudaFree(s->v);
+  delete s;
+  return PA_OK;
+}
+
 // ------------------------------------------------------------------------------ peer exchange --
 
 extern "C" size_t pa_exchange_bytes(pa_ctx* ctx, uint32_t world, uint32_t max_rows) {
@@ -996,8 +1099,18 @@ extern "C" int pa_exchange_init(pa_ctx* ctx, uint32_t rank, uint32_t world, void
   if (!ctx->xc.ctr) {
     if (cudaMalloc(&x.ctr, 8) != cudaSuccess) { cudaGetLastError(); return fail(ctx, PA_ENOMEM, "pa_exchange_init: out of device memory"); }
   } else x.ctr = ctx->xc.ctr;
+  // A fresh session: call counter 0 and no entry in this rank's buffer that could carry a tag of the new session (the
+  // buffer may have served an earlier one).  The peers write into it only after the barrier that follows set-up.
+  CU_TRY(ctx, cudaDeviceSynchronize());
   CU_TRY(ctx, cudaMemset(x.ctr, 0, 8));
+  CU_TRY(ctx, cudaMemset(bufs[rank], 0, pa_exchange_bytes(ctx, world, max_rows)));
+  CU_TRY(ctx, cudaDeviceSynchronize());
   ctx->xc = x;
+  return PA_OK;
+}
+extern "C" int pa_set_wait_limit(pa_ctx* ctx, uint32_t sweeps) {
+  if (!ctx) return PA_EINVAL;
+  ctx->tune.wait_polls = sweeps;
   return PA_OK;
 }
 extern "C" int pa_decode_exchange(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t q_col_stride,

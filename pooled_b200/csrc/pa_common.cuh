@@ -76,6 +76,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// the same box, requested into L2 only (no shared-memory destination, nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
@@ -236,6 +242,14 @@ struct pa_ctx {
   size_t ev_used = 0;
   bool timing = false;
   bool core_only = false;        // profiling aid: calls launch their core kernel only
+  // measurement switches, read from the environment once when the context is created
+  struct Tuning {
+    int pre_stages = 2;          // POOLED_ATTN_PRE_STAGES: K/V tiles a decode CTA fetches ahead of its predecessor's end
+    int next_tiles = 2;          // POOLED_ATTN_NEXT_TILES: tiles of the next layer each decode CTA asks L2 to fetch at its end
+    bool no_fuse = false;        // POOLED_ATTN_NO_FUSE: RoPE/append -> decode -> combine chain instead of the fused front
+    bool verify_mma_sync = false;// POOLED_ATTN_VERIFY_MMA_SYNC: k-token blocks on the mma.sync kernel
+    uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)
+  } tune;
   bool failed = false;
   std::string err;
   pa_stats stats{};
@@ -248,6 +262,8 @@ struct pa_layer {
   __half* k = nullptr;
   __half* v = nullptr;
   CUtensorMap tm_k64, tm_v64;    // 64-row boxes over all sequences' rows, for the decode kernel
+  const pa_layer* next = nullptr; // the layer the engine runs after this one (pa_layer_set_next): its first tiles are
+                                  // requested into L2 while this layer's call drains
   const float* qnorm_w = nullptr;   // QK head-norm weights of this layer (device, f32 [head_dim]); nullptr: the layer
   const float* knorm_w = nullptr;   // call takes q and k as they come
   double norm_eps = 0.0;

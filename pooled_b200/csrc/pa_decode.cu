@@ -22,17 +22,6 @@
 
 namespace pa {
 
-#ifdef PA_TRACE
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TR(slot) do { if (p.trace && lane == 0 && (warp == 0 || warp == 4)) p.trace[(((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 256 + (slot)] = gtime(); } while (0)
-#else
-#define TR(slot) do {} while (0)
-#endif
-#ifdef PA_TRACE
-#define CTR(slot) do { if (p.trace && threadIdx.x == 0) p.trace[(160 + blockIdx.y * 16 + (blockIdx.x & 15)) * 256 + (slot)] = gtime(); } while (0)
-#else
-#define CTR(slot) do {} while (0)
-#endif
 
 constexpr int kT = 64;             // positions per tile
 constexpr int kConsumers = 128;    // 4 consumer warps
@@ -58,7 +47,8 @@ struct DecSmem {
 
 template <int HD, int NT, bool PRECISE>
 __global__ void __launch_bounds__(kDecThreads, 1)
-pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
+pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kn,
+                 const __grid_constant__ CUtensorMap tm_vn, const DecodeParams p) {
   using L = DecSmem<HD, NT, PRECISE>;
   constexpr int ROWS = L::ROWS, SLOT = L::SLOT, QP = L::QP, PP = L::PP;
   constexpr int MT = HD / 64;        // 16-dim output tiles per consumer warp
@@ -93,7 +83,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                  vempty = vfull + kMaxStages * 8;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  TR(0);
   // The consumers put their q loads in flight before the producer may start: a q load issued behind the
   // first 190 KB of K/V tiles of every SM would wait for all of them at the memory controllers.
   // With few query rows the values wait in registers across the barrier; with many they are staged into shared
@@ -182,7 +171,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     pdl_wait();      // q (and the partial buffers written at the end) belong to earlier kernels until here
     pdl_trigger();
-    TR(4);
     if (Q_IN_REGS) {
       if (fused) {
 #pragma unroll
@@ -241,7 +229,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     named_bar_arrive(3, kDecThreads);
     named_bar_sync(2, kDecThreads);
   }
-  TR(warp == 4 ? 128 : 1);
 
   if (warp == 4) {
     // ---------------------------------------------------------------- producer ----
@@ -266,16 +253,26 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         const uint32_t s = i % NS, ph = (i / NS) & 1;
         if (!waited && (tile0 + i + 1) * kT > old_rows) { pdl_wait(); waited = true; }
         mbar_wait(kempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
-        if (i < 30) TR(130 + 2 * i);
         mbar_expect_tx(kfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s);
         mbar_wait(vempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
-        if (i < 30) TR(131 + 2 * i);
         mbar_expect_tx(vfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
       }
     }
     if (n_tiles <= pre) { __syncwarp(); named_bar_sync(3, kDecThreads); }   // keeps the barrier balanced
+    if (lane == 0 && p.next_tiles) {
+      // Everything this CTA will read has been requested.  The engine's next layer call walks the same split of
+      // another cache: ask L2 for its first tiles now, so that HBM keeps delivering while this kernel drains, the
+      // combine runs and the next kernel starts up (a hint: nothing waits for it, and a line that is written later is
+      // simply updated in L2).
+      const int yn = (int)(p.items.seq[item] * p.next_max_seq + tile0 * kT);
+      const uint32_t n_pf = min(p.next_tiles, n_tiles);
+      for (uint32_t i = 0; i < n_pf; ++i) {
+        tma_prefetch_3d(&tm_kn, 0, yn + (int)(i * kT), z);
+        tma_prefetch_3d(&tm_vn, 0, yn + (int)(i * kT), z);
+      }
+    }
     if (lane == 0) {
       if (*s_err) {
         // a wait ran out somewhere: let the copies still in flight land (bounded) before the CTA exits
@@ -377,8 +374,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       for (int e = 0; e < 4; ++e) oacc[mt][nt][e] = 0.f;
   }
   named_bar_sync(1, kConsumers);   // q visible
-  TR(2);
-  TR(5);
 
   const uint32_t q_hi_s = smem_u32(q_hi), q_lo_s = smem_u32(q_lo), p_hi_s = smem_u32(p_hi), p_lo_s = smem_u32(p_lo);
 
@@ -399,7 +394,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       for (int a = 0; a < NA - 1; ++a) sacc_x[nt][a][0] = sacc_x[nt][a][1] = sacc_x[nt][a][2] = sacc_x[nt][a][3] = 0.f;
     }
     mbar_wait(kfull + 8 * s, ph, s_err, WAIT_KFULL);
-    if (i < 15) TR(8 + 8 * i);
     if (own_new && i == n_tiles - 1) {
       const uint32_t rr = n_rows - 1 - tile_pos;
       auto word_at = [&](uint8_t* slots, uint32_t wi) {   // 32-bit word wi of row rr in the swizzled tile
@@ -481,7 +475,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       for (int a = 0; a < NA - 1; ++a)
 #pragma unroll
         for (int e = 0; e < 4; ++e) sacc[nt][e] += sacc_x[nt][a][e];
-    if (i < 15) TR(9 + 8 * i);
 
     // ---- scale, causal mask, tile maximum per row ----
     const uint32_t pos_a = tile_pos + 16 * w + r, pos_b = pos_a + 8;
@@ -503,7 +496,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       if (r == 0) { s_max[w * ROWS + nt * 8 + 2 * j] = tmax[nt][0]; s_max[w * ROWS + nt * 8 + 2 * j + 1] = tmax[nt][1]; }
     }
     named_bar_sync(1, kConsumers);
-    if (i < 15) TR(10 + 8 * i);
 
     // ---- new running maximum, weights P = 2^(s - m), rescale factor ----
     float alpha[NT][2];
@@ -542,9 +534,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         oacc[mt][nt][2] *= alpha[nt][0]; oacc[mt][nt][3] *= alpha[nt][1];
       }
 
-    if (i < 15) TR(11 + 8 * i);
     mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
-    if (i < 15) TR(12 + 8 * i);
     if (own_new && i == n_tiles - 1 && tid < HD / 2) {   // made visible by the barrier below
       const uint32_t rr = n_rows - 1 - tile_pos, c16g = tid >> 2;
       *reinterpret_cast<uint32_t*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = v_new2;
@@ -559,7 +549,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       }
     }
     named_bar_sync(1, kConsumers);   // P (and the cleared rows) visible to every warp
-    if (i < 15) TR(13 + 8 * i);
 
     // ---- O^T += V^T . P^T, dims (w*MT + mt)*16 .. +15 ----
     if constexpr (NT <= 2) {
@@ -625,7 +614,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(vempty + 8 * s);
-    if (i < 15) TR(14 + 8 * i);
   }
 
   // ---- partial (o, m, l) per row ----
@@ -663,7 +651,6 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       }
     }
   if (*s_err && tid == 0) atomicMax(p.err, *s_err);
-  TR(3);
 }
 
 // ------------------------------------------------------------------------------ combine --
@@ -678,10 +665,8 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   __shared__ float4 s_acc[16][16];
   const uint32_t prow = blockIdx.x, slice = blockIdx.y, col = prow / p.n_heads, h = prow % p.n_heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  CTR(0);
   pdl_wait();      // the partial records belong to the kernel before this one
   pdl_trigger();
-  CTR(1);
   uint32_t ns = p.fixed_parts;
   if (ns == 0) {
     uint32_t it = 0;
@@ -729,7 +714,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   float Lsum = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) Lsum += s_red2[i];
-  CTR(2);
 
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -754,7 +738,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   }
   s_acc[grp][ln] = acc;
   __syncthreads();
-  CTR(3);
   __shared__ unsigned int s_epoch;
   float t = 0.f;
   if (tid < 64) {
@@ -789,7 +772,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
       const uint2* mine = reinterpret_cast<const uint2*>(x.peer[x.rank]);
       float mr[8], lr[8], orr[8];
       uint32_t pending = (1u << x.world) - 1u;
-      for (uint32_t it = 0; it < (1u << 20) && pending; ++it) {
+      for (uint32_t it = 0; it < p.xch_sweeps && pending; ++it) {
         uint32_t v[8][3], tg[8][3];
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
@@ -844,7 +827,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     if (p.act_f16) reinterpret_cast<__half*>(p.out)[oo] = __float2half_rn(rv);
     else reinterpret_cast<float*>(p.out)[oo] = rv;
   }
-  CTR(4);
 }
 
 // ------------------------------------------------------------------------------ launchers --
@@ -865,7 +847,10 @@ static cudaError_t launch_decode_t(const pa_layer* L, const DecodeParams& p, dim
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  return launch_pdl(kern, grid, dim3(kDecThreads), (size_t)bytes, st, L->tm_k64, L->tm_v64, pp);
+  const pa_layer* N = L->next;
+  if (!N || !pp.next_tiles || N->n_seqs != L->n_seqs) { N = L; pp.next_tiles = 0; }
+  pp.next_max_seq = N->max_seq;
+  return launch_pdl(kern, grid, dim3(kDecThreads), (size_t)bytes, st, L->tm_k64, L->tm_v64, N->tm_k64, N->tm_v64, pp);
 }
 
 template <int HD, bool PRECISE>

@@ -22,6 +22,8 @@
 #include <math.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "pa_params.cuh"
 
 namespace pa {
@@ -38,7 +40,8 @@ using namespace pa;
 // it to a kernel as if it were a pointer would hand the GPU a host address.
 static __device__ __align__(256) float g_static_scratch[64 + PA_STATIC_RECORDS * 256 + PA_STATIC_RECORDS * 2];
 
-static float* g_scratch_dev[64] = {};   // per device: the array's device address, looked up once
+static float* g_scratch_dev[64] = {};   // per device: the array's device address, looked up once (under g_setup_mu)
+static std::mutex g_setup_mu;
 static int g_smem_optin[64] = {};
 static int g_sm_count[64] = {};
 
@@ -86,6 +89,7 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
   }
   if (((uintptr_t)q & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return say(msg, msg_len, PA_EINVAL, "pa_decode_static: misaligned pointer");
   if (cudaSetDevice(device) != cudaSuccess) return say(msg, msg_len, PA_ECUDA, "pa_decode_static: cudaSetDevice failed (there is no CPU path)");
+  std::unique_lock<std::mutex> setup_lock(g_setup_mu);
   if (!g_scratch_dev[device]) {
     // one-time set-up for this device, with the device current: the array's address on THIS device
     float* ptr = nullptr;
@@ -102,6 +106,7 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
       return say(msg, msg_len, PA_EUNSUPPORTED, "pa_decode_static: this library is built for sm_100a only");
     g_scratch_dev[device] = ptr;
   }
+  setup_lock.unlock();
   float* scratch = g_scratch_dev[device];
   uint32_t* err = reinterpret_cast<uint32_t*>(scratch);
   float* part_o = scratch + 64;
@@ -131,7 +136,7 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
   p.n_heads = n_heads; p.G = G; p.max_seq = cache_rows;
   p.prefetch_old_rows = 0;
   p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)head_dim));
-  p.err = err; p.trace = nullptr;
+  p.err = err;
   p.items.seq[0] = 0; p.items.lim0[0] = (int32_t)pos + 1; p.items.n_rows[0] = n_rows; p.items.n_cols[0] = n_cols; p.items.col0[0] = 0;
 
   // the one thing that must start at zero: the status word (the records are rewritten before they are read)
@@ -151,4 +156,24 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
     return say(msg, msg_len, PA_ECUDA, "pa_decode_static: launching the combine kernel failed");
   }
   return PA_OK;
+}
+
+// The status word of the bounded device-side waits of the calls made so far on `stream` (0: every wait was satisfied).
+// A 4-byte copy out of the built-in array followed by a wait for the stream: allocates nothing.
+extern "C" PA_API int pa_decode_static_status(int device, void* stream, uint32_t* word) {
+  if (!word || device < 0 || device >= 64) return PA_EINVAL;
+  *word = 0;
+  float* scratch;
+  {
+    std::lock_guard<std::mutex> g(g_setup_mu);
+    scratch = g_scratch_dev[device];
+  }
+  if (!scratch) return PA_OK;   // no call has run on this device yet
+  if (cudaSetDevice(device) != cudaSuccess) return PA_ECUDA;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(word, scratch, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaGetLastError();
+    return PA_ECUDA;
+  }
+  return *word ? PA_ETIMEOUT : PA_OK;
 }

@@ -22,13 +22,14 @@ struct DecodeParams {
   uint32_t pre_stages;         // ... but only this many per CTA before the q loads are in flight
   uint32_t early_limit;        // ... and only rows below this one (the call before may still be writing its own row)
   float scale_log2;         // log2(e) / sqrt(head_dim)
+  // the layer the engine runs next (pa_layer_set_next): once a CTA has requested its own last tile it asks L2 for the
+  // first next_tiles tiles of the same split of that layer, so HBM keeps working across the kernel boundary
+  uint32_t next_tiles, next_max_seq;
   uint32_t* err;
-  unsigned long long* trace;   // development builds only (PA_TRACE): per-CTA timestamps; nullptr otherwise
   ItemList items;
 };
 
 struct CombineParams {
-  unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
   const float* o;        // record s of row prow: o + prow * o_row_stride + s * o_part_stride, HD floats
   const float* ml;       // (m, l) of it:        ml + prow * ml_row_stride + s * ml_part_stride
   uint64_t o_row_stride, o_part_stride, ml_row_stride, ml_part_stride;
@@ -42,11 +43,11 @@ struct CombineParams {
   ItemList items; uint32_t n_items;
   int exchange;          // != 0: publish the merged record to every rank, wait for theirs, merge across ranks, then out
   ExchangeView xc;
+  uint32_t xch_sweeps;   // polling limit of the exchange wait
   uint32_t* err;
 };
 
 struct RopeParams {
-  unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
   uint32_t trigger_early;      // 1: the dependent kernel may start before this one's own wait (inside a layer call only)
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
   void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
@@ -103,7 +104,6 @@ struct PrefillParams {
   uint32_t prefetch_old_rows;   // split-K form: K/V tiles wholly below the call's new rows may be fetched before the predecessor ends
   uint32_t early_limit;         // ... and below this row (the call before may still be writing its own row)
   uint32_t pre_stages;          // ... and only this many K tiles (one fewer V tiles) before the q loads are in flight
-  unsigned long long* trace;   // development builds only (PA_TRACE); nullptr otherwise
 };
 
 }  // namespace pa

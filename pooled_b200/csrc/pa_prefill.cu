@@ -26,17 +26,6 @@
 
 namespace pa {
 
-#ifdef PA_TRACE   // development builds: per-CTA timestamps of the pipeline stages
-__device__ __forceinline__ unsigned long long pf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-// A predicated store, not a branch: the marks sit between .sync.aligned tensor instructions, which want the warp
-// converged.
-#define PTR(slot) do { if (p.trace) { \
-    unsigned long long* a_ = p.trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + ((slot) < 256 ? (slot) : 255); \
-    const unsigned long long t_ = pf_gtime(); \
-    asm volatile("{\n\t.reg .pred pq;\n\tsetp.eq.u32 pq, %0, 0;\n\t@pq st.global.u64 [%1], %2;\n\t}" :: "r"((unsigned)lane), "l"(a_), "l"(t_) : "memory"); } } while (0)
-#else
-#define PTR(slot) do {} while (0)
-#endif
 
 constexpr int kBM = 128;   // query rows per CTA
 constexpr int kBN = 64;    // keys per tile
@@ -222,7 +211,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (tile0 >= tiles) return;                         // this split holds no row (uniform for the CTA)
     n_tiles = min(tiles, tile0 + tps) - tile0;
   }
-  if (warp == 4) PTR(0);
 
   if (warp == 1 && lane == 0) {
     *s_err = 0;
@@ -264,7 +252,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (SK && j == ((early && p.pre_stages == 0) ? 0u : 1u)) mbar_wait(BAR(Q_SENT, 0), 0, s_err, WAIT_QFULL);
         if (SK && j == 2) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
-        if (j < 10) PTR(70 + j);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
         tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(K_FULL, st));
       }
@@ -280,7 +267,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (!waited && (tile0 + j + 1) * kBN > old_rows) { pdl_wait(); waited = true; }
         if (SK && j == 1) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);   // slot 1 stages query rows until then
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
-        if (j < 10) PTR(80 + j);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
         tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(V_FULL, st));
       }
@@ -302,10 +288,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       tc_fence_after();
       auto issue_qk = [&](uint32_t j) {
         const uint32_t sb = j % kSBuf, st = j % NK;
-        if (j < 10) PTR(90 + 3 * j);
         mbar_wait(BAR(K_FULL, st), (j / NK) & 1, s_err, WAIT_KFULL);
         tc_fence_after();
-        if (j < 10) PTR(91 + 3 * j);
         const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[NK - 1]);
         const uint32_t ts = t_s0 + sb * kBN;
         // lower half of the head dims: Q from tensor memory; upper half: Q from shared memory
@@ -318,7 +302,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                       kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, 1u);
         umma_commit_elected(leader, BAR(K_EMPTY, st));
         umma_commit_elected(leader, BAR(S_FULL, sb));
-        if (j < 10) PTR(92 + 3 * j);
       };
       // The scores run two tiles ahead of the weights: S(j+2) is issued before P V (j), so the softmax of tile j+1
       // never waits behind the P V of tile j-1.  S(j+2) reuses the TMEM tile of S(j-1) / P(j-1); P V (j-1) was issued
@@ -328,12 +311,9 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t sb = j % kSBuf, st = j % NV;
         if (j + 2 < n_tiles) issue_qk(j + 2);
-        if (j < 10) PTR(130 + 3 * j);
         mbar_wait(BAR(P_FULL, sb), (j / kSBuf) & 1, s_err, WAIT_QFULL);
-        if (j < 10) PTR(131 + 3 * j);
         mbar_wait(BAR(V_FULL, st), (j / NV) & 1, s_err, WAIT_VFULL);
         tc_fence_after();
-        if (j < 10) PTR(132 + 3 * j);
         const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[NV - 1]);
         const uint32_t tp = t_s0 + sb * kBN;     // P(j): packed f16 pairs in the first 32 columns of S(j)'s tile
 #pragma unroll
@@ -369,7 +349,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t q_es = p.q_f16 ? 2u : 4u, q_ch = planes ? HD * 4 / 16 : HD * q_es / 16;     // 16-byte chunks per staged row
     if (early) pdl_wait();
     pdl_trigger();
-    if (warp == 4) PTR(4);
     if (SK) {
       const uint32_t pairs = p.n_cols * p.G, st_tid = tid - 128, total = pairs * q_ch;
       for (uint32_t idx = st_tid; idx < total; idx += 128) {
@@ -386,7 +365,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mbar_arrive(BAR(Q_SENT, 0));
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       named_bar_sync(1, 128);
-      if (warp == 4) PTR(5);
     }
     const uint8_t* my_stage = stage_row(lr & 63u);
     auto stage_ld = [&](uint32_t c) { return *reinterpret_cast<const uint4*>(my_stage + ((c ^ (lr & 7u)) << 4)); };
@@ -451,7 +429,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       tc_fence_before();
       mbar_arrive(BAR(Q_FULL, 0));
     }
-    if (warp == 4) PTR(1);
     // keys [0, lim) are visible to this row
     const uint32_t lim = SK ? (uint32_t)min(max(p.lim0 + (int32_t)min(sk_c, p.n_cols - 1), 0), (int32_t)p.n_rows) : p0 + row + 1;
     float m_st = SK ? -1.0e30f : -INFINITY, l_sum = 0.f;   // split-K: a split may hold no visible key of a row
@@ -459,7 +436,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       const uint32_t b = j % kSBuf, u = j / kSBuf, kv0 = (tile0 + j) * kBN;
       mbar_wait(BAR(S_FULL, b), u & 1, s_err, WAIT_MMA);
       tc_fence_after();
-      if (warp == 4 && j < 10) PTR(8 + 6 * j);
       float s[kBN];
       {
         float t0[32], t1[32];
@@ -473,7 +449,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 #pragma unroll
         for (int i = 0; i < kBN; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], 1);
       }
-      if (warp == 4 && j < 10) PTR(9 + 6 * j);
       // maximum of the raw scores (the scale is positive), causal mask on tiles that reach this row's diagonal
       if (kv0 + kBN > lim) {
 #pragma unroll
@@ -501,7 +476,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           tmem_st32(t_o + c * 32 + lane_addr, o);
         }
       }
-      if (warp == 4 && j < 10) PTR(10 + 6 * j);
       // P = 2^(s - m) as packed f16 pairs over the first 32 columns of this S buffer (its scores are in registers now)
       uint32_t pw[32];
       float ls = 0.f;
@@ -515,15 +489,12 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       l_sum += ls;
       tmem_st32u(t_s0 + b * kBN + lane_addr, pw);
       tmem_wait_st();
-      if (warp == 4 && j < 10) PTR(12 + 6 * j);
       tc_fence_before();
       mbar_arrive(BAR(P_FULL, b));
-      if (warp == 4 && j < 10) PTR(13 + 6 * j);
     }
     // ---- epilogue: O / l, gate, store ----
     mbar_wait(BAR(O_DONE, 0), 0, s_err, WAIT_MMA);
     tc_fence_after();
-    if (warp == 4) PTR(2);
     const float inv_l = 1.f / l_sum;
     const uint32_t col = c0 + row;
     if (SK) {
@@ -578,7 +549,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
     }
     tc_fence_before();
-    if (warp == 4) PTR(3);
   }
   __syncthreads();
   if (warp == 2) {

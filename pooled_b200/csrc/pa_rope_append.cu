@@ -35,12 +35,6 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
   const uint32_t col = blockIdx.x, half = p.n_rot / 2, hd = p.hd, pr = threadIdx.x;
   // The kernel after this one may start fetching old cache rows while this one runs (it never touches the rows or
   // the rotated q written here before its own wait); this kernel itself writes nothing before its predecessor ends.
-#ifdef PA_TRACE
-#define RTR(slot) do { if (p.trace && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); p.trace[(224 + (blockIdx.y & 31)) * 256 + (slot)] = t_; } } while (0)
-#else
-#define RTR(slot) do {} while (0)
-#endif
-  RTR(0);
   // by-value angles go through shared memory: launch parameters indexed differently by every thread are served one
   // address at a time.  Done ahead of the wait, while the predecessor still runs.
   __shared__ Angle s_ang[64];
@@ -51,7 +45,6 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
   }
   pdl_wait();
   if (!p.trigger_early) pdl_trigger();
-  RTR(1);
   if (pr >= hd / 2) return;
   const uint32_t nq = p.q ? p.q_heads : 0, nk = p.k ? p.kv_heads : 0;
   uint32_t slot = blockIdx.y;
@@ -108,7 +101,6 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
     __half* dst = p.k_cache + row_c * (uint64_t)(p.kv_heads * hd) + (uint64_t)head * hd;
     dst[d0] = f16_rne(ra); dst[d1] = f16_rne(rb);
   }
-  RTR(2);
 }
 
 // Many columns (prefill chunks): one 256-thread CTA per column.  The column's n_rot/2 angles are evaluated once and

@@ -42,7 +42,15 @@ SYMBOLS = {
     "pa_layer_create": (_i, [_vp, _u32, _u32, C.POINTER(_vp)]),
     "pa_layer_destroy": (_i, [_vp]),
     "pa_layer_set_origin": (_i, [_vp, _u32]),
+    "pa_layer_set_next": (_i, [_vp, _vp]),
     "pa_cache_ptr": (_vp, [_vp, _i]),
+    "pa_cache_export": (_i, [_vp, _u32, _u32, _u32, _i, _vp, C.POINTER(_u32), _vp]),
+    "pa_cache_import": (_i, [_vp, _u32, _u32, _u32, _i, _vp, C.POINTER(_u32), _vp]),
+    "pa_slot_save": (_i, [_vp, _u32, _u32, C.POINTER(_vp), _vp]),
+    "pa_slot_load": (_i, [_vp, _u32, _vp, C.POINTER(_u32), _vp]),
+    "pa_slot_export": (_i, [_vp, _i, _vp, _vp]),
+    "pa_slot_info": (_i, [_vp, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
+    "pa_slot_drop": (_i, [_vp]),
     "pa_last_error": (C.c_char_p, [_vp]),
     "pa_version": (C.c_char_p, []),
     "pa_sync": (_i, [_vp, _vp]),
@@ -80,6 +88,8 @@ SYMBOLS = {
     "pa_attn_layer_host": (_i, [_vp, _u32, _u32, _u32, _i, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
     "pa_attn_step_host": (_i, [C.POINTER(_vp), _u32, _u32, _u32, _u32, _i, _vp, _u64, _u64, _u64, _vp, _vp, _u64, _u64, _vp, _u64, _u64, _u64, _vp, _u64, _u64, _vp]),
     "pa_decode_static": (_i, [_i, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, C.c_char_p, _sz]),
+    "pa_decode_static_status": (_i, [_i, _vp, C.POINTER(_u32)]),
+    "pa_set_wait_limit": (_i, [_vp, _u32]),
     "pa_get_stats": (_i, [_vp, C.POINTER(PaStats)]),
     "pa_timing_begin": (_i, [_vp, _u32]),
     "pa_set_core_only": (_i, [_vp, _i]),

@@ -32,6 +32,15 @@ class ShardPlan:
     def local_pos(self, rank: int, pos: int) -> int:
         return pos - rank * self.chunk
 
+    def block_columns(self, rank: int, pos: int, n_cols: int) -> tuple[int, int]:
+        """Columns [c_lo, c_hi) of a k-token block at pos .. pos + n_cols - 1 whose rows rank holds (empty when
+        c_lo >= c_hi).  A block that straddles a chunk boundary is appended in two parts, each by its owner; this is
+        the rule pa_attn_layer_sharded applies."""
+        lo, hi = rank * self.chunk, (rank + 1) * self.chunk
+        c_lo = 0 if pos >= lo else min(lo - pos, n_cols)
+        c_hi = n_cols if pos + n_cols <= hi else (0 if pos >= hi else hi - pos)
+        return c_lo, c_hi
+
 
 class ShardedDecoder:
     """One decode step of a sharded layer.  `engine` needs set_origin(), rope(), rope_append(), decode_partial() and
@@ -42,6 +51,10 @@ class ShardedDecoder:
         """exchange: "nccl" (all-gather of the record blocks, then pa_merge) or "peer" (pa_decode_exchange: the combine
         kernel itself stores the records into every rank's buffer over NVLink and merges; needs engine.exchange_setup)."""
         self.eng, self.plan, self.rank, self.dist, self.group, self.exchange = engine, plan, rank, dist, group, exchange
+        # a layer's extent is its max_seq: a longer cache would make this rank attend (and append) rows of the next
+        # rank's chunk as well, and the merge would count those positions twice
+        if engine.cfg.max_seq != plan.chunk:
+            raise ValueError(f"sharded decode needs layer caches of exactly one chunk: max_seq {engine.cfg.max_seq} != chunk {plan.chunk}")
         for li in range(engine.cfg.n_layers):
             engine.set_origin(li, rank * plan.chunk)
 

@@ -17,7 +17,7 @@ NH, NKV, HD, CHUNK = 4, 2, 64, 96
 
 
 class _Cfg:
-    n_heads, n_kv_heads, head_dim, n_layers, q_dim = NH, NKV, HD, 1, NH * HD
+    n_heads, n_kv_heads, head_dim, n_layers, q_dim, max_seq = NH, NKV, HD, 1, NH * HD, CHUNK
 
 
 class FakeEngine:
@@ -98,6 +98,29 @@ def test_shard_plan():
     with pytest.raises(ValueError):
         p.owner(400)
     assert [p.local_rows(r, 250) for r in range(4)] == [100, 100, 50, 0] and p.local_pos(2, 250) == 50
+
+
+def test_block_columns_cover_a_straddling_block_once():
+    p = ShardPlan(4, 100)
+    assert p.block_columns(0, 97, 5) == (0, 3) and p.block_columns(1, 97, 5) == (3, 5)       # rows 97..99 | 100..101
+    assert p.block_columns(2, 97, 5)[0] >= p.block_columns(2, 97, 5)[1]                      # nothing for rank 2
+    assert p.block_columns(1, 100, 5) == (0, 5) and p.block_columns(0, 100, 5)[1] == 0
+    for pos in (0, 95, 99, 100, 196, 299, 395):
+        for n in (1, 4, 5, 8):
+            if pos + n > 400:
+                continue
+            got = sorted(c for r in range(4) for c in range(*p.block_columns(r, pos, n)))
+            assert got == list(range(n)), (pos, n)                                             # every column exactly once
+            for r in range(4):
+                lo, hi = p.block_columns(r, pos, n)
+                assert all(p.owner(pos + c) == r for c in range(lo, hi))
+
+
+def test_sharded_decoder_refuses_caches_longer_than_a_chunk():
+    eng = FakeEngine()
+    eng.cfg = type("C", (), dict(vars(_Cfg), max_seq=CHUNK + 64))()
+    with pytest.raises(ValueError, match="one chunk"):
+        ShardedDecoder(eng, ShardPlan(2, CHUNK), 0, None)
 
 
 def test_sharded_decode_world2_gloo():
