@@ -189,7 +189,7 @@ PA_API int pa_kv_append(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_
 
 /* Fused front of the path: rotate q into q_rot (f32 [n_cols][n_heads*head_dim]), rotate k, append k and
  * v.  Replaces attn_glue_kv minus the head norm (engine/wgsl/layer_fuse.js:87-146).  q_rot may be NULL:
- * the rotated q then stays in the context's own buffer for the pa_attend call that follows. */
+ * the rotated q then stays in the context's own buffer, which a following pa_decode reads when its q is NULL. */
 PA_API int pa_rope_append(pa_layer* layer, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q,
                           uint64_t q_col_stride, uint64_t q_head_stride, const void* k, const void* v,
                           uint64_t kv_col_stride, const float* cs_table, float* q_rot, void* stream);
@@ -206,7 +206,8 @@ PA_API int pa_rope_append_items(pa_layer* layer, const pa_item* items, uint32_t 
  * (engine/qwen35.js:1619-1640) and the attn_dec branch of _encAttnCore (:2494-2499).
  * q: rotated queries, dtype q_dtype, [total columns][q_col_stride]; the items' columns follow one another
  * in q, gate and out.  gate may be NULL; with an interleaved q_full buffer pass gate = q + head_dim and
- * the same strides (engine/wgsl/attn_dec.js:282-283).  n_cols * (n_heads / n_kv_heads) <= 64 per item. */
+ * the same strides (engine/wgsl/attn_dec.js:282-283).  n_cols * (n_heads / n_kv_heads) <= 64 per item.  q = NULL: the
+ * rotated q that the preceding pa_rope_append / pa_rope_append_items call left in the context (its q_rot = NULL). */
 PA_API int pa_decode(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q, int q_dtype,
                      uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
                      uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);

@@ -284,17 +284,29 @@ PO_API void po_attn_f32_fast(const float* q, uint64_t q_stride, const uint16_t* 
   uint32_t G = n_heads / n_kv, kv_dim = n_kv * hd;
   float rs = 1.0f / sqrtf((float)hd);
   int total = (int)(n_cols * n_heads);
+  /* With fewer (column, head) jobs than threads the sequence is cut into chunks as well, each job leaving an
+   * unnormalised (acc, m, l) record that is merged afterwards: every host thread gets work. */
+  int nthr = 1;
+#ifdef _OPENMP
+  nthr = omp_get_max_threads();
+#endif
+  int chunks = 1;
+  if (total < nthr) { chunks = (nthr + total - 1) / total; if (chunks > 64) chunks = 64; }
+  float* part = (float*)malloc((size_t)total * chunks * (hd + 2) * sizeof(float));
+  if (!part) return;
 #pragma omp parallel for schedule(dynamic, 1)
-  for (int job = 0; job < total; job++) {
-    uint32_t col = (uint32_t)job / n_heads, h = (uint32_t)job % n_heads;
+  for (int job = 0; job < total * chunks; job++) {
+    int rc = job / chunks, ch = job % chunks;
+    uint32_t col = (uint32_t)rc / n_heads, h = (uint32_t)rc % n_heads;
     uint32_t g = h / G;
     uint64_t n = pos0 + col + 1;
+    uint64_t per = (n + chunks - 1) / chunks, t0 = per * ch, t1 = t0 + per < n ? t0 + per : n;
     const float* qh = q + col * q_stride + (size_t)h * hd;
     float acc[512];
     float kf[512];
     for (uint32_t d = 0; d < hd; d++) acc[d] = 0;
     float m = -3.0e38f, l = 0;
-    for (uint64_t t = 0; t < n; t++) {
+    for (uint64_t t = t0; t < t1; t++) {
       const uint16_t* kr = k_cache + t * kv_dim + (size_t)g * hd;
       const uint16_t* vr = v_cache + t * kv_dim + (size_t)g * hd;
       for (uint32_t d = 0; d < hd; d++) kf[d] = po_h2f(kr[d]);
@@ -310,13 +322,39 @@ PO_API void po_attn_f32_fast(const float* q, uint64_t q_stride, const uint16_t* 
       l += p;
       for (uint32_t d = 0; d < hd; d++) acc[d] += p * po_h2f(vr[d]);
     }
+    float* pr = part + (size_t)job * (hd + 2);
+    for (uint32_t d = 0; d < hd; d++) pr[d] = acc[d];
+    pr[hd] = m; pr[hd + 1] = l;
+  }
+  for (int rc = 0; rc < total; rc++) {
+    uint32_t col = (uint32_t)rc / n_heads, h = (uint32_t)rc % n_heads;
+    const float* pr = part + (size_t)rc * chunks * (hd + 2);
+    float M = -3.0e38f, L = 0;
+    for (int c = 0; c < chunks; c++) if (pr[(size_t)c * (hd + 2) + hd] > M) M = pr[(size_t)c * (hd + 2) + hd];
     float* o = out + col * out_stride + (size_t)h * hd;
+    for (uint32_t d = 0; d < hd; d++) o[d] = 0;
+    for (int c = 0; c < chunks; c++) {
+      const float* r = pr + (size_t)c * (hd + 2);
+      float w = r[hd + 1] > 0 ? expf(r[hd] - M) : 0.0f;
+      L += r[hd + 1] * w;
+      for (uint32_t d = 0; d < hd; d++) o[d] += r[d] * w;
+    }
     for (uint32_t d = 0; d < hd; d++) {
-      float r = acc[d] / l;
+      float r = o[d] / L;
       if (gate) r *= 1.0f / (1.0f + expf(-gate[col * gate_stride + (size_t)h * hd + d]));
       o[d] = r;
     }
   }
+  free(part);
+}
+
+/* Number of host threads the threaded functions use from now on (0 or less: leave as is). */
+PO_API void po_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
 }
 
 PO_API int po_threads(void) {

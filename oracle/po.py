@@ -49,6 +49,7 @@ def lib():
         L.po_attn_f32ref.argtypes = attn + [f32p, C.c_uint64]
         L.po_attn_f32_fast.argtypes = attn + [f32p, C.c_uint64]
         L.po_threads.restype = C.c_int
+        L.po_set_threads.argtypes = [C.c_int]
         L.po_lse_merge.argtypes = [f64p, f64p, f64p, C.c_uint32, C.c_uint32, f64p]
         L.po_lcg_dec_next.restype = C.c_uint32; L.po_lcg_dec_next.argtypes = [u32p]
         L.po_lcg_tile_next.restype = C.c_uint32; L.po_lcg_tile_next.argtypes = [u32p]
@@ -144,6 +145,12 @@ def attn_f32_fast(q, k_cache, v_cache, n_heads, n_kv, hd, pos0, n_cols, gate=Non
 
 def threads() -> int:
     return int(lib().po_threads())
+
+
+def set_threads(n: int) -> int:
+    """Host threads the threaded oracle functions use from now on; returns the count in effect."""
+    lib().po_set_threads(int(n))
+    return threads()
 
 
 def gen_attn_dec(seed: int, max_seq: int, kv_dim: int, q_dim: int, n_cols: int = 4):

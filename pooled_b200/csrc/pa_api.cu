@@ -642,6 +642,9 @@ extern "C" int pa_decode(pa_layer* L, const pa_item* items, uint32_t n_items, co
   if (!L) return PA_EINVAL;
   GUARD(L->ctx);
   if (!out) return fail(L->ctx, PA_EINVAL, "pa_decode: null out");
+  if (!q) {   // the rotated q a preceding pa_rope_append / pa_rope_append_items left in the context (q_rot = NULL there)
+    q = L->ctx->q_rot; q_dtype = PA_F32; q_col_stride = L->ctx->q_dim; q_head_stride = L->ctx->cfg.head_dim;
+  }
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
                      (cudaStream_t)stream, "pa_decode");
 }

@@ -30,6 +30,18 @@ def test_exports_every_declared_symbol(pa):
     assert b"sm_100a" in pa.pa_version()
 
 
+def test_js_binding_table_names_every_export():
+    # js/pooled_attn.js is the Deno FFI table a maintainer copies; it must list exactly the header's exports, with as
+    # many parameters as the ctypes table that the GPU tests call through
+    js = open(os.path.join(ROOT, "js", "pooled_attn.js")).read()
+    table = js[js.index("export const SYMBOLS = {"):js.index("\n};")]
+    entries = dict(re.findall(r"^\s+(pa_\w+): \{ parameters: \[(.*?)\], result:", table, flags=re.M))
+    assert set(entries) == set(L.SYMBOLS), set(entries) ^ set(L.SYMBOLS)
+    for name, params in entries.items():
+        n = len([x for x in params.split(",") if x.strip()])
+        assert n == len(L.SYMBOLS[name][1]), name
+
+
 def test_struct_layouts_match_the_header():
     assert C.sizeof(L.PaConfig) == 4 * 4 + 8 + 5 * 4 + 5 * 4 + 4 or C.sizeof(L.PaConfig) % 8 == 0
     assert C.sizeof(L.PaItem) == 16 and C.sizeof(L.PaStats) == 24

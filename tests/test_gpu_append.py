@@ -55,6 +55,13 @@ def test_rope_append_matches_oracle_bit_for_bit(hd, n_rot, theta, nH, nKV, pos, 
         q = po.normal(10, n_cols * qd).astype(np.float32).reshape(n_cols, qd)
         k = po.normal(11, n_cols * kvd).astype(np.float32).reshape(n_cols, kvd)
         v = po.normal(12, n_cols * kvd).astype(np.float32).reshape(n_cols, kvd)
+    # the rows on either side of the appended ones carry a pattern no conversion produces here
+    POISON = 0x5a5a
+    for name in ("k", "v"):
+        c = eng.cache(0, name)
+        if pos > 0:
+            c[0, pos - 1] = POISON
+        c[0, pos + n_cols:pos + n_cols + 3] = POISON
     q_rot = eng.rope_append(0, 0, pos, util.torch_dev(q, td), util.torch_dev(k, td), util.torch_dev(v, td))
     eng.sync()
     gk, gv = util.read_cache(eng, 0, 0, pos, n_cols)
@@ -71,9 +78,12 @@ def test_rope_append_matches_oracle_bit_for_bit(hd, n_rot, theta, nH, nKV, pos, 
     # needs the f32 flip to straddle an f16 boundary too.  On these seeded inputs neither happens.
     assert bad_k == 0, f"{bad_k} cache halves differ"
     assert bad_q <= 2, f"{bad_q} rotated q values differ in f32 bits"
-    # rows around the appended ones are untouched
+    # rows around the appended ones are untouched: the poison is still there
+    after_k, after_v = util.read_cache(eng, 0, 0, pos + n_cols, 3)
+    assert np.all(after_k == POISON) and np.all(after_v == POISON), "rows past the appended ones were written"
     if pos > 0:
-        assert not np.any(util.read_cache(eng, 0, 0, pos - 1, 1)[0] != util.read_cache(eng, 0, 0, pos - 1, 1)[0])
+        before_k, before_v = util.read_cache(eng, 0, 0, pos - 1, 1)
+        assert np.all(before_k == POISON) and np.all(before_v == POISON), "the row before the appended ones was written"
 
 
 @pytest.mark.parametrize("dtype", ["f16", "f32"])

@@ -148,6 +148,43 @@ def test_config5_batched_long_context_reduced():
     util.assert_close(out, np.stack(refs), "config 5 (reduced)")
 
 
+def test_config5_full_size_batched_step():
+    # config 5 at its own size: 8 sequences x 131072-row context in one layer (2.1 GB of K and V), one token each at position
+    # 131072 through the batched front (pa_rope_append_items) and one batched decode call.  Row offsets pass 2^30 bytes,
+    # TMA row coordinates pass 10^6, the plan is 9 splits over 2049 tiles.  Sequences 0 and 7 are checked against the
+    # float64 oracle (the criterion of tests/test_attn_dec.js:87-98) and their appended rows bit for bit; the other
+    # sequences hold the same K/V content as sequence 0 shifted by one row each, so their outputs must be finite and
+    # differ from sequence 0's.
+    import torch
+    n_seqs, ctx, nH, nKV, hd, n_rot, theta = 8, 131072, 16, 2, 256, 64, 1e7
+    kvd, qd = nKV * hd, nH * hd
+    eng = _engine(nH, nKV, hd, ctx + 8, act="f16", n_seqs=n_seqs, max_cols=8)
+    base = po.np_f16_rne(po.normal(0xB0B + 5, (ctx + 8) * kvd) * 0.9).reshape(ctx + 8, kvd)
+    vbase = po.np_f16_rne(po.normal(0xC0DE + 5, (ctx + 8) * kvd)).reshape(ctx + 8, kvd)
+    tk, tv = torch.from_numpy(base.view(np.int16)).cuda(), torch.from_numpy(vbase.view(np.int16)).cuda()
+    for s in range(n_seqs):
+        eng.cache(0, "k")[s, :ctx] = tk[s:s + ctx]
+        eng.cache(0, "v")[s, :ctx] = tv[s:s + ctx]
+    q = util.normal_f16(0xA11CE + 5, (n_seqs, qd)); kn = util.normal_f16(71, (n_seqs, kvd)); vn = util.normal_f16(72, (n_seqs, kvd))
+    g = util.normal_f16(0x6A7E + 5, (n_seqs, qd))
+    d = lambda a: util.torch_dev(a, torch.float16)
+    seqs_pos = [(s, ctx) for s in range(n_seqs)]
+    q_rot = eng.rope_append_items(0, seqs_pos, d(q), d(kn), d(vn))
+    out = eng.decode(0, [(s, ctx, 1) for s in range(n_seqs)], q_rot, d(g)).float().cpu().numpy()
+    eng.sync()
+    assert np.all(np.isfinite(out))
+    for s in (0, n_seqs - 1):
+        k_row = po.f16_rne(po.rope_neox_f64(kn[s], nKV, hd, n_rot, ctx, theta)); v_row = po.f16_rne(vn[s])
+        gk, gv = util.read_cache(eng, 0, s, ctx, 1)
+        assert np.array_equal(gk[0], k_row) and np.array_equal(gv[0], v_row), f"sequence {s}: appended row differs"
+        Kf = np.concatenate([base[s:s + ctx], k_row[None]]); Vf = np.concatenate([vbase[s:s + ctx], v_row[None]])
+        ref = po.attn_f64(po.rope_neox_f64(q[s], nH, hd, n_rot, ctx, theta)[None], Kf, Vf, nH, nKV, hd, ctx, 1, g[s][None])
+        ma, mr = util.assert_close(out[s][None], ref, f"config 5 full size, sequence {s}")
+        print(f"config 5 full size, sequence {s}: max-abs {ma:.2e} max-rel {mr:.2e}")
+    assert all(np.abs(out[s] - out[0]).max() > 1e-3 for s in range(1, n_seqs))
+    eng.destroy()
+
+
 # ---- edges ---------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("nH,nKV,hd", [(16, 2, 256), (24, 4, 256), (16, 8, 128), (8, 8, 128), (32, 2, 256)])

@@ -118,9 +118,13 @@ def test_config3_full_size_properties():
     out = eng.encode_layer(0, 0, d(q), d(k), d(v), None, mode="prefill").float().cpu().numpy()
     eng.sync()
     assert np.all(np.isfinite(out))
-    cols = [0, 1, 63, 64, 127, 128, 4095, 4096, 8000, 8191]
+    # the first, the last and one interior column of each of the 64 CTA tiles of 128 columns (every CTA of the
+    # 24-head x 64-tile schedule has columns under the oracle), plus the first 64-key tile's edges
+    rng = np.random.default_rng(3)
+    cols = sorted({0, 1, 63, 64} | {t * 128 + o for t in range(T // 128) for o in (0, 127, int(rng.integers(1, 127)))})
     ref, Kf, Vf = _oracle_layer(q, k, v, None, nH, nKV, hd, 64, 1e7, 0, cols)
-    util.assert_close(out[cols], ref, "config 3 sampled columns")
+    ma, mr = util.assert_close(out[cols], ref, "config 3 sampled columns")
+    print(f"config 3 full size: {len(cols)} columns, max-abs {ma:.2e} max-rel {mr:.2e}")
     gk, gv = util.read_cache(eng, 0, 0, 0, T)
     assert np.array_equal(gk, Kf) and np.array_equal(gv, Vf), "KV append is not bit-exact at full size"
     # column 0 attends one key: its output is exactly that V row (per kv head), whatever q is
