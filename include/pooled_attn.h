@@ -65,7 +65,7 @@ enum {
 typedef struct pa_config {
   uint32_t n_heads;     /* query heads */
   uint32_t n_kv_heads;  /* K/V heads; n_heads % n_kv_heads == 0 */
-  uint32_t head_dim;    /* 128 or 256 */
+  uint32_t head_dim;    /* 64, 128 or 256 */
   uint32_t n_rot;       /* rotated dims per head (== head_dim for full RoPE); even, multiple of 2 */
   double rope_theta;
   uint32_t rope_mode;   /* pa_rope_mode */
@@ -212,6 +212,19 @@ PA_API int pa_decode(pa_layer* layer, const pa_item* items, uint32_t n_items, co
                      uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride,
                      uint64_t gate_head_stride, void* out, uint64_t out_col_stride, void* stream);
 
+/* Gather mode of the decode (the QSA kernels: attn_dec with gather = stride, engine/wgsl/attn_dec.js:33-38, :67-70, :105,
+ * :170-181, and attnDecMcWGSL({gather}), engine/wgsl/qwen4exp_batch.js:590-641): column c attends the cache rows its
+ * list names instead of rows 0 .. seqLen-1.  row_lists: u32 on the device, list_stride words per column: [0] = n, then n
+ * row indices of sequence seq, ascending (n <= list_stride - 1; every listed row is visible to the column).  List
+ * position t stands where position t stands in the dense kernel, so the list 0 .. seqLen-1 gives the very bits
+ * pa_decode gives for the same columns passed as one-column items.  The lengths stay on the device (the reference's
+ * selection kernels write them there); the library sizes its grid for list_stride - 1 rows.  At most 32 columns a
+ * call, at most 8 query heads per kv head.  An empty list gives zeros. */
+PA_API int pa_decode_gather(pa_layer* layer, uint32_t seq, uint32_t n_cols, const uint32_t* row_lists, uint32_t list_stride,
+                            const void* q, int q_dtype, uint64_t q_col_stride, uint64_t q_head_stride, const void* gate,
+                            uint64_t gate_col_stride, uint64_t gate_head_stride, void* out, uint64_t out_col_stride,
+                            void* stream);
+
 /* The same, stopping before normalisation: one (o[head_dim], m, l) f32 record per (column, head) over the
  * rows this cache holds, for a KV sequence sharded across GPUs.  partial: f32 [rows * head_dim] holding o
  * (unnormalised), followed by f32 [rows][2] holding (m in natural-log units, l); rows = total columns *
@@ -349,9 +362,10 @@ PA_API int pa_get_stats(pa_ctx* ctx, pa_stats* out);
  * tests/bench_attn_ctx.js:39-70 give in the reference.  pa_timing_begin arms up to max_events launches;
  * pa_timing_end waits for them and returns their summed duration and count. */
 PA_API int pa_timing_begin(pa_ctx* ctx, uint32_t max_events);
-/* Profiling aid: while on, pa_attn_layer / pa_decode launch their core kernel only (no RoPE/append, no combine), so
- * that successive calls put core launches back to back, as tests/bench/attn_tile_bench.js times one kernel alone.
- * Outputs are not produced while it is on. */
+/* Profiling aid: while on, pa_attn_layer / pa_decode launch their core kernel only (no RoPE/append, no merge of the
+ * split records), so that successive calls put core launches back to back, as tests/bench/attn_tile_bench.js times
+ * one kernel alone.  Outputs are not produced while it is on, and nothing else may write the caches meanwhile: a
+ * pa_attn_layer launch starts fetching K/V ahead of the previous launch's end, as it does inside a token step. */
 PA_API int pa_set_core_only(pa_ctx* ctx, int on);
 PA_API int pa_timing_end(pa_ctx* ctx, double* core_ms, uint64_t* core_launches);
 

@@ -46,6 +46,7 @@ export const SYMBOLS = {
   pa_rope_append: { parameters: [P, U32, U32, U32, P, U64, U64, P, P, U64, P, P, P], result: I32 },
   pa_rope_append_items: { parameters: [P, BUF, U32, P, U64, U64, P, P, U64, P, P], result: I32 },
   pa_decode: { parameters: [P, BUF, U32, P, I32, U64, U64, P, U64, U64, P, U64, P], result: I32 },
+  pa_decode_gather: { parameters: [P, U32, U32, P, U32, P, I32, U64, U64, P, U64, U64, P, U64, P], result: I32 },
   pa_decode_partial: { parameters: [P, BUF, U32, P, I32, U64, U64, P, P], result: I32 },
   pa_merge: { parameters: [P, P, U32, U32, P, U64, U64, P, U64, P], result: I32 },
   pa_exchange_bytes: { parameters: [P, U32, U32], result: U64 },

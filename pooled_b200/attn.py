@@ -255,6 +255,19 @@ class AttnEngine:
                                   q_head_stride or self.cfg.head_dim, gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
         return out
 
+    def decode_gather(self, li: int, row_lists: torch.Tensor, q: torch.Tensor, gate: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                      seq: int = 0, q_head_stride: int | None = None, gate_head_stride: int | None = None) -> torch.Tensor:
+        """Decode over listed cache rows (the QSA gather mode of attn_dec, engine/wgsl/attn_dec.js:33-38): row_lists is an
+        int32 device tensor [n_cols, stride] holding per column its length n, then n rows ascending."""
+        n_cols = q.shape[0]
+        assert row_lists.dtype == torch.int32 and row_lists.is_cuda and row_lists.shape[0] == n_cols and row_lists.is_contiguous()
+        if out is None:
+            out = torch.empty((n_cols, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_decode_gather(self.layers[li], seq, n_cols, self._p(row_lists), row_lists.shape[1], self._p(q), _dt(q.dtype), q.stride(0),
+                                         q_head_stride or self.cfg.head_dim, gp, gcs, ghs, self._p(out), out.stride(0), self._st()))
+        return out
+
     def decode_partial(self, li: int, items, q: torch.Tensor, q_head_stride: int | None = None) -> torch.Tensor:
         """Per-(column, head) records over this cache's rows: float32 [rows*head_dim (o) + rows*2 (m, l)]."""
         total = sum(it[2] for it in items)

@@ -104,7 +104,7 @@ extern "C" uint32_t pa_tile_split_len(uint32_t seq_end, uint32_t fa_split, uint3
 
 // Splits per (item, kv head): enough CTAs to give every SM one, never more than one wave, at least two
 // 64-row tiles each.  Depends on the call's longest column and item count only.
-static uint32_t plan_splits(const pa_ctx* ctx, uint32_t n_rows, uint32_t n_items, uint32_t total_cols = 0) {
+static uint32_t plan_splits(const pa_ctx* ctx, uint32_t n_rows, uint32_t n_items, uint32_t total_cols = 0, uint32_t groups = 1) {
   const uint32_t tiles = ceil_div(n_rows, 64);
   if (!total_cols) total_cols = n_items;
   uint32_t want = ctx->cfg.splits ? ctx->cfg.splits : (uint32_t)ctx->sm_count / (ctx->cfg.n_kv_heads * n_items);
@@ -113,7 +113,7 @@ static uint32_t plan_splits(const pa_ctx* ctx, uint32_t n_rows, uint32_t n_items
   if (cap < 1) cap = 1;
   if (want > cap) want = cap;
   if (want > ctx->max_splits) want = ctx->max_splits;
-  const uint32_t fit = (uint32_t)(ctx->part_slots / ((size_t)total_cols * ctx->cfg.n_heads));
+  const uint32_t fit = (uint32_t)(ctx->part_slots / ((size_t)total_cols * ctx->cfg.n_heads * groups));   // records: one per (row, split, consumer group)
   if (want > fit) want = fit;
   return want;
 }
@@ -132,8 +132,8 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   *out = nullptr;
   if (cfg->n_heads < 1 || cfg->n_kv_heads < 1 || cfg->n_heads % cfg->n_kv_heads)
     return fail(nullptr, PA_EINVAL, "pa_create: n_heads %u must be a multiple of n_kv_heads %u", cfg->n_heads, cfg->n_kv_heads);
-  if (cfg->head_dim != 128 && cfg->head_dim != 256)
-    return fail(nullptr, PA_EUNSUPPORTED, "pa_create: head_dim %u is not supported (128 or 256)", cfg->head_dim);
+  if (cfg->head_dim != 64 && cfg->head_dim != 128 && cfg->head_dim != 256)
+    return fail(nullptr, PA_EUNSUPPORTED, "pa_create: head_dim %u is not supported (64, 128 or 256)", cfg->head_dim);
   if (cfg->n_rot > cfg->head_dim || (cfg->n_rot & 1) || (cfg->rope_mode != PA_ROPE_NONE && cfg->n_rot < 2))
     return fail(nullptr, PA_EINVAL, "pa_create: n_rot %u must be even and at most head_dim", cfg->n_rot);
   if (cfg->rope_mode > PA_ROPE_TABLE || cfg->act_dtype > PA_F16) return fail(nullptr, PA_EINVAL, "pa_create: bad rope_mode or act_dtype");
@@ -159,6 +159,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   if (const char* e = getenv("POOLED_ATTN_NEXT_TILES")) ctx->tune.next_tiles = atoi(e) < 0 ? 0 : atoi(e);
   ctx->tune.no_fuse = getenv("POOLED_ATTN_NO_FUSE") != nullptr;
   ctx->tune.verify_mma_sync = getenv("POOLED_ATTN_VERIFY_MMA_SYNC") != nullptr;
+  ctx->tune.no_merge = getenv("POOLED_ATTN_NO_MERGE") != nullptr;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -181,6 +182,9 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   ctx->part_slots = 16384;
   if ((e = cudaMalloc(&ctx->part_o, ctx->part_slots * cfg->head_dim * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(part_o)", e);
   if ((e = cudaMalloc(&ctx->part_ml, ctx->part_slots * 2 * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(part_ml)", e);
+  ctx->merge_slots = 2u * kMaxItems * cfg->n_kv_heads;
+  if ((e = cudaMalloc(&ctx->merge_ctr, ctx->merge_slots * 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(merge counters)", e);
+  if ((e = cudaMemset(ctx->merge_ctr, 0, ctx->merge_slots * 4)) != cudaSuccess) return bail(PA_ECUDA, "cudaMemset(merge counters)", e);
   if ((e = cudaMalloc(&ctx->dev_err, 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMalloc(err)", e);
   if ((e = cudaMemset(ctx->dev_err, 0, 4)) != cudaSuccess) return bail(PA_ECUDA, "cudaMemset(err)", e);
   if ((e = cudaMallocHost(&ctx->host_err, 4)) != cudaSuccess) return bail(PA_ENOMEM, "cudaMallocHost(err)", e);
@@ -192,7 +196,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
 extern "C" int pa_destroy(pa_ctx* ctx) {
   if (!ctx) return PA_OK;
   cudaSetDevice(ctx->device);
-  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->norm_q); cudaFree(ctx->norm_k); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err);
+  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->norm_q); cudaFree(ctx->norm_k); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err); cudaFree(ctx->merge_ctr);
   cudaFree(ctx->stage_dev);
   for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
@@ -286,7 +290,9 @@ extern "C" int pa_sync(pa_ctx* ctx, void* stream) {
 extern "C" int pa_reset(pa_ctx* ctx) {
   if (!ctx) return PA_EINVAL;
   cudaGetLastError();
-  if (cudaMemset(ctx->dev_err, 0, 4) != cudaSuccess) return fail(ctx, PA_ECUDA, "pa_reset: the device does not answer");
+  if (cudaDeviceSynchronize() != cudaSuccess || cudaMemset(ctx->dev_err, 0, 4) != cudaSuccess ||
+      cudaMemset(ctx->merge_ctr, 0, ctx->merge_slots * 4) != cudaSuccess)
+    return fail(ctx, PA_ECUDA, "pa_reset: the device does not answer");
   *ctx->host_err = 0;
   ctx->failed = false;
   ctx->err.clear();
@@ -561,9 +567,12 @@ static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, Item
 // the token's unrotated k / v row for the fused front of the decode kernel
 struct FusedFront { const void* k; const void* v; bool append; uint32_t pos; };
 
+// a gathered call: the columns' row lists on the device, one list of `stride` words per column
+struct GatherLists { const uint32_t* lists; uint32_t stride; };
+
 static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false,
-                       bool exchange = false, const FusedFront* fz = nullptr, const void* q_lo = nullptr) {
+                       bool exchange = false, const FusedFront* fz = nullptr, const void* q_lo = nullptr, const GatherLists* gl = nullptr) {
   pa_ctx* ctx = L->ctx;
   if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
   if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
@@ -577,7 +586,20 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
       return fail(ctx, PA_EUNSUPPORTED, "%s: %u query rows exceed the %u rows of the exchange buffers", who, total_cols * ctx->cfg.n_heads, ctx->xc.max_rows);
   }
   cudaSetDevice(ctx->device);
-  uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols);
+  const int nt = (int)ceil_div(max_cols * ctx->G, 8);
+  // One sequence with more than 8 query rows per kv head (a k-token verify block) goes to the tensor-core split-K
+  // kernel; single tokens and batches of sequences stay on the streaming mma.sync kernel.
+  const bool verify_tc = n_items == 1 && nt > 1 && max_rows > 0 && !ctx->tune.verify_mma_sync && !gl && ctx->cfg.head_dim >= 128;
+  const uint32_t groups = verify_tc ? 1u : (uint32_t)decode_groups(nt);   // records per split
+  uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols, groups);
+  if (gl) {
+    // the lists' lengths live on the device: the grid is sized for the longest list possible and each CTA derives its
+    // own column's plan (plan_splits' rule without the cap by the row count, which the kernel applies)
+    ns = plan_splits(ctx, 0x40000000u, n_items, total_cols, groups);
+    const uint32_t most = std::max(1u, ceil_div(gl->stride - 1, 64) / 2);
+    if (ns > most) ns = most;
+    p.gather = gl->lists; p.gather_stride = gl->stride; p.k_cache = L->k; p.v_cache = L->v;
+  }
   if (n_items == 1 && max_cols * ctx->G > 8) { const uint32_t fit = (uint32_t)(ctx->part_slots / (2ull * total_cols * ctx->cfg.n_heads)); if (ns > fit) ns = fit; if (ns > 256) ns = 256; if (ns < 1) ns = 1; }
   p.q = q; p.q_f16 = q_dtype == PA_F16; p.q_col_stride = qcs; p.q_head_stride = qhs;
   p.part_o = ctx->part_o; p.part_ml = ctx->part_ml; p.n_splits = ns;
@@ -595,10 +617,6 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     p.k_cache = L->k; p.v_cache = L->v;
     memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), (size_t)(ctx->cfg.n_rot / 2) * sizeof(Angle));
   }
-  const int nt = (int)ceil_div(max_cols * ctx->G, 8);
-  // One sequence with more than 8 query rows per kv head (a k-token verify block) goes to the tensor-core split-K
-  // kernel; single tokens and batches of sequences stay on the streaming mma.sync kernel.
-  const bool verify_tc = n_items == 1 && nt > 1 && max_rows > 0 && !ctx->tune.verify_mma_sync;
   CUtensorMap tm_k, tm_v;
   PrefillParams vp{};
   if (verify_tc) {
@@ -613,24 +631,34 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);
   }
+  // One kernel per call where the merge can be shared out among the call's own CTAs: all of them resident at once (one
+  // wave at one CTA per SM), and at least half as many CTAs per (item, kv head) as there are (row, 64-dim slice) units.
+  const uint32_t units = max_cols * ctx->G * (ctx->cfg.head_dim / 64);
+  const bool merge = !partial && !exchange && !verify_tc && nt <= 2 && !ctx->core_only && !ctx->tune.no_merge && max_rows > 0 &&
+                     (uint64_t)ns * ctx->cfg.n_kv_heads * n_items <= (uint64_t)ctx->sm_count && 2 * ns >= units;
+  if (merge) {
+    p.merge = 1; p.merge_ctr = ctx->merge_ctr;
+    p.gate = gate; p.gate_col_stride = gcs; p.gate_head_stride = ghs; p.out = out; p.out_col_stride = ocs; p.act_f16 = ctx->cfg.act_dtype == PA_F16;
+  }
   timing_mark(ctx, st, 0);
   if (verify_tc) CU_TRY(ctx, launch_verify(L, vp, tm_k, tm_v, ctx->cfg.n_kv_heads, st));
   else if (max_rows > 0) CU_TRY(ctx, launch_decode(L, p, dim3(ns, ctx->cfg.n_kv_heads, n_items), nt, st));
   timing_mark(ctx, st, 1);
   CombineParams c{};
   c.o = ctx->part_o; c.ml = ctx->part_ml;
-  const uint32_t rs = ns;
+  const uint32_t rs = ns * groups;
   c.o_row_stride = (uint64_t)rs * ctx->cfg.head_dim; c.o_part_stride = ctx->cfg.head_dim;
   c.ml_row_stride = (uint64_t)rs * 2; c.ml_part_stride = 2;
-  c.n_heads = ctx->cfg.n_heads; c.fixed_parts = 0; c.n_splits = ns;
+  c.n_heads = ctx->cfg.n_heads; c.fixed_parts = 0; c.n_splits = ns; c.groups = groups;
+  c.gather = p.gather; c.gather_stride = p.gather_stride;
   c.gate = gate; c.gate_col_stride = gcs; c.gate_head_stride = ghs; c.out = out; c.out_col_stride = ocs;
   c.act_f16 = ctx->cfg.act_dtype == PA_F16;
   c.partial_out = partial; c.partial_rows = (uint64_t)total_cols * ctx->cfg.n_heads;
   c.exchange = exchange ? 1 : 0; c.xc = ctx->xc; c.err = ctx->dev_err;
   c.xch_sweeps = ctx->tune.wait_polls ? ctx->tune.wait_polls : (1u << 20);
   c.items = p.items; c.n_items = n_items;
-  if (!ctx->core_only) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
-  ctx->stats.kernel_launches += ctx->core_only ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
+  if (!ctx->core_only && !merge) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
+  ctx->stats.kernel_launches += (ctx->core_only || merge) ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
   // this call's kernel waited for everything before it; what it appends itself is what may still be in flight
   if (fz && fz->append) { ctx->inflight_layer = L; ctx->inflight_row0 = max_rows ? max_rows - 1 : 0; }
   else ctx->inflight_layer = nullptr;
@@ -647,6 +675,26 @@ extern "C" int pa_decode(pa_layer* L, const pa_item* items, uint32_t n_items, co
   }
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
                      (cudaStream_t)stream, "pa_decode");
+}
+
+extern "C" int pa_decode_gather(pa_layer* L, uint32_t seq, uint32_t n_cols, const uint32_t* row_lists, uint32_t list_stride, const void* q, int q_dtype,
+                                uint64_t q_col_stride, uint64_t q_head_stride, const void* gate, uint64_t gate_col_stride, uint64_t gate_head_stride,
+                                void* out, uint64_t out_col_stride, void* stream) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (!out || !row_lists) return fail(ctx, PA_EINVAL, "pa_decode_gather: null out or row lists");
+  if (n_cols < 1 || n_cols > (uint32_t)kMaxItems) return fail(ctx, PA_EINVAL, "pa_decode_gather: 1 to %d columns per call", kMaxItems);
+  if (list_stride < 2 || ((uintptr_t)row_lists & 3)) return fail(ctx, PA_EINVAL, "pa_decode_gather: list_stride must be at least 2 (the length word and one row)");
+  if (seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "pa_decode_gather: sequence %u of %u", seq, L->n_seqs);
+  if (ctx->G > 8) return fail(ctx, PA_EUNSUPPORTED, "pa_decode_gather: more than 8 query heads per kv head");
+  // every column is its own item (its list is its own K/V stream); positions are list positions, all of them visible
+  pa_item items[kMaxItems];
+  const uint32_t longest = std::min<uint32_t>(list_stride - 1, L->max_seq);
+  for (uint32_t c = 0; c < n_cols; ++c) items[c] = pa_item{seq, L->origin + longest - 1, 1, 0};
+  GatherLists gl{row_lists, list_stride};
+  return decode_impl(L, items, n_cols, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
+                     (cudaStream_t)stream, "pa_decode_gather", false, false, nullptr, nullptr, &gl);
 }
 
 extern "C" int pa_decode_partial(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t q_col_stride,
@@ -786,7 +834,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // A k-token block on the tensor-core split-K kernel in its hi/lo form takes q as two f16 planes (high and low parts),
   // which the RoPE kernel writes directly: nothing is left to convert in the attention kernel's prologue.
   const bool planes = mode != PA_MODE_PREFILL && n_cols * ctx->G > 8 && n_cols * ctx->G <= (uint32_t)kMaxRows && !(ctx->cfg.flags & PA_FLAG_FAST) &&
-                      !ctx->tune.verify_mma_sync;
+                      !ctx->tune.verify_mma_sync && ctx->cfg.head_dim >= 128;
   if (sharded) {
     // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
     const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
@@ -836,9 +884,9 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
     return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
   pa_item it{seq, pos, n_cols, 0};
   if (planes)
-    return decode_impl(L, &it, 1, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", !ctx->core_only, false, nullptr,
+    return decode_impl(L, &it, 1, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", true, false, nullptr,
                        reinterpret_cast<const __half*>(ctx->q_rot) + (size_t)ctx->cfg.max_cols * ctx->q_dim);
-  return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", !ctx->core_only);
+  return decode_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", true);
 }
 
 extern "C" int pa_attn_layer(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, int mode, const void* q, uint64_t q_col_stride,

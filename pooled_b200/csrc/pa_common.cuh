@@ -20,7 +20,7 @@ namespace pa {
 // reaches the end of the kernel and the host reports PA_ETIMEOUT instead of a hung GPU.
 constexpr uint32_t kWaitPolls = 1u << 24;  // with 32..64 ns back-off: well under a second
 
-enum : uint32_t { WAIT_KFULL = 1, WAIT_VFULL = 2, WAIT_EMPTY = 3, WAIT_MMA = 4, WAIT_TMEM = 5, WAIT_QFULL = 6 };
+enum : uint32_t { WAIT_KFULL = 1, WAIT_VFULL = 2, WAIT_EMPTY = 3, WAIT_MMA = 4, WAIT_TMEM = 5, WAIT_QFULL = 6, WAIT_PEER = 7, WAIT_MERGE = 8 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -168,6 +168,12 @@ __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) 
 
 // ---- host side -----------------------------------------------------------------------------------
 
+// Consumer groups of the decode kernel for a call of nt 8-row groups of query rows.  The kernel is written for one or
+// two groups of four warps (two take alternate tiles and leave a record each); one is what runs: with two, a group
+// may ask for a slot of the shared ring before the other group's earlier tile has landed in it, and a parity wait
+// cannot tell those two phases apart.
+__host__ __device__ constexpr int decode_groups(int nt) { return nt >= 0 ? 1 : 2; }
+
 constexpr int kMaxItems = 32;     // items of one batched decode call
 constexpr int kMaxRows = 64;      // query rows (columns x heads of one kv head) one decode CTA carries
 
@@ -230,6 +236,8 @@ struct pa_ctx {
   float* part_ml = nullptr;    // device: f32 [rows][splits][2]
   uint32_t max_splits = 0;
   size_t part_slots = 0;       // (query row, split) records the partial buffers hold
+  unsigned int* merge_ctr = nullptr;   // device: per (item, kv head) of a decode call, records left and CTAs done merging (zero between calls)
+  uint32_t merge_slots = 0;
   uint32_t* dev_err = nullptr;   // device error word (bounded waits)
   uint32_t* host_err = nullptr;  // pinned mirror
   void* norm_q = nullptr;        // normed q / k of the current layer call (act_dtype, [max_cols][q_dim] / [max_cols][kv_dim])
@@ -248,6 +256,7 @@ struct pa_ctx {
     int next_tiles = 2;          // POOLED_ATTN_NEXT_TILES: tiles of the next layer each decode CTA asks L2 to fetch at its end
     bool no_fuse = false;        // POOLED_ATTN_NO_FUSE: RoPE/append -> decode -> combine chain instead of the fused front
     bool verify_mma_sync = false;// POOLED_ATTN_VERIFY_MMA_SYNC: k-token blocks on the mma.sync kernel
+    bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel
     uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)
   } tune;
   bool failed = false;

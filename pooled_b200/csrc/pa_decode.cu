@@ -14,7 +14,16 @@
 // The kernel is HBM-bound: 2 * rows * head_dim * 2 bytes per kv head; the math needs a fraction of the
 // time a tile takes to arrive.
 //
-// Each CTA writes an unnormalised partial (o, m, l) per query row; pa_combine_kernel merges the splits
+// With at most 16 query rows the consumers come as two groups of four warps that take alternate tiles of the CTA's
+// range, each with its own running (m, l, o): one group's tile is latency-bound (fragment loads, two barriers, the
+// exponentials: about 1.3 us), two in flight keep up with data that arrives faster than that (from L2, or while the
+// ring is full).  Each group leaves its own partial record.
+//
+// Gather mode (pa_decode_gather): a column attends a list of cache rows instead of rows 0 .. n-1.  List position t
+// stands where position t stands otherwise; the producer warp fetches the listed rows with 16-byte cp.async into the
+// very slots and swizzle a TMA tile would fill, so everything after the load is the same arithmetic in the same order.
+//
+// Each group writes an unnormalised partial (o, m, l) per query row; pa_combine_kernel merges the records
 // (out = sum o_s e^(m_s-M) / sum l_s e^(m_s-M)), applies the sigmoid gate and stores f32 or f16.
 //
 // Stands in for attn_dec / attn_dec_combine / attn_dec_combine_g of pooled (engine/wgsl/attn_dec.js:67-287).
@@ -24,20 +33,118 @@ namespace pa {
 
 
 constexpr int kT = 64;             // positions per tile
-constexpr int kConsumers = 128;    // 4 consumer warps
-constexpr int kDecThreads = 160;   // + 1 producer warp
+constexpr int kConsumers = 128;    // 4 consumer warps per group
 constexpr int kMaxStages = 8;
+
+
+// acc += x * w, each component one fused multiply-add: the merge inside the decode kernel (merge_slice_128) and the
+// combine kernel round the same way, so either path gives the same bits
+__device__ __forceinline__ void fma4(float4& acc, const float4& x, float w) {
+  acc.x = __fmaf_rn(x.x, w, acc.x); acc.y = __fmaf_rn(x.y, w, acc.y); acc.z = __fmaf_rn(x.z, w, acc.z); acc.w = __fmaf_rn(x.w, w, acc.w);
+}
+
+// LSE merge of the ns split records of one query row over one 64-dim slice, gate and store, by the 128 consumer threads
+// of a decode CTA: the arithmetic of pa_combine_kernel, operation for operation and in the same order (that kernel has
+// 256 threads; thread t here does the work of its threads t and t + 128), so a call gives the same bits whether its
+// records are merged here or there.  o_rec / ml_rec: record 0 of the row; records follow one another.  Scratch: 6 KB of
+// shared memory no one else uses any more.  bar: the group's named barrier.
+struct MergeScratch { float w[512]; float red[8]; float red2[8]; float4 acc[16][16]; };
+template <int HD>
+__device__ __forceinline__ void merge_slice_128(const float* __restrict__ o_rec, const float* __restrict__ ml_rec, uint32_t ns, uint32_t slice, int t,
+                                                MergeScratch& sc, uint32_t bar, bool gated, float gv, bool empty_is_zero, int act_f16, void* out, uint64_t oo) {
+  const int wv = t >> 5, lane = t & 31, ln = t & 15, gA = t >> 4;
+  // everything is requested before the first use: one memory round trip
+  float mv[4], lv[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t s = t + 128 * k;
+    mv[k] = -3.0e38f; lv[k] = 0.f;
+    if (s < ns) { mv[k] = __ldcg(ml_rec + 2 * s); lv[k] = __ldcg(ml_rec + 2 * s + 1); }
+  }
+  const float* ob = o_rec + slice * 64 + ln * 4;
+  float4 xa[8], xb[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint32_t sa = gA + 16 * u, sb = gA + 8 + 16 * u;
+    xa[u] = sa < ns ? __ldcg(reinterpret_cast<const float4*>(ob + (size_t)sa * HD)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    xb[u] = sb < ns ? __ldcg(reinterpret_cast<const float4*>(ob + (size_t)sb * HD)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float M = fmaxf(fmaxf(mv[0], mv[1]), fmaxf(mv[2], mv[3]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  if (lane == 0) sc.red[wv] = M;
+  named_bar_sync(bar, kConsumers);
+  M = fmaxf(fmaxf(sc.red[0], sc.red[1]), fmaxf(sc.red[2], sc.red[3]));
+  float wk[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t s = t + 128 * k;
+    wk[k] = s < ns ? __expf(mv[k] - M) : 0.f;
+    sc.w[s] = wk[k];
+  }
+  // the combine kernel's thread v sums records v and v + 256, then its warp reduces: v = t and v = t + 128 here
+  float LpA = __fmaf_rn(lv[2], wk[2], __fmul_rn(lv[0], wk[0])), LpB = __fmaf_rn(lv[3], wk[3], __fmul_rn(lv[1], wk[1]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    LpA = __fadd_rn(LpA, __shfl_xor_sync(0xffffffffu, LpA, o));
+    LpB = __fadd_rn(LpB, __shfl_xor_sync(0xffffffffu, LpB, o));
+  }
+  if (lane == 0) { sc.red2[wv] = LpA; sc.red2[wv + 4] = LpB; }
+  named_bar_sync(bar, kConsumers);
+  float Lsum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) Lsum = __fadd_rn(Lsum, sc.red2[i]);
+  float4 accA = make_float4(0.f, 0.f, 0.f, 0.f), accB = accA;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint32_t sa = gA + 16 * u, sb = gA + 8 + 16 * u;
+    fma4(accA, xa[u], sa < ns ? sc.w[sa] : 0.f);
+    fma4(accB, xb[u], sb < ns ? sc.w[sb] : 0.f);
+  }
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t g = gA + 8 * h;
+    float4& acc = h ? accB : accA;
+    for (uint32_t s0 = g + 128; s0 < ns; s0 += 64) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t s = s0 + 16 * u;
+        x[u] = s < ns ? __ldcg(reinterpret_cast<const float4*>(ob + (size_t)s * HD)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t s = s0 + 16 * u;
+        fma4(acc, x[u], s < ns ? sc.w[s] : 0.f);
+      }
+    }
+  }
+  sc.acc[gA][ln] = accA; sc.acc[gA + 8][ln] = accB;
+  named_bar_sync(bar, kConsumers);
+  if (t < 64) {
+    const float* sa = reinterpret_cast<const float*>(sc.acc);
+    float tt = sa[t];
+#pragma unroll
+    for (int i = 1; i < 16; ++i) tt = __fadd_rn(tt, sa[i * 64 + t]);
+    float rv = (empty_is_zero && Lsum == 0.f) ? 0.f : __fdiv_rn(tt, Lsum);
+    if (gated) rv = __fmul_rn(rv, __fdiv_rn(1.0f, __fadd_rn(1.0f, __expf(-gv))));
+    if (act_f16) reinterpret_cast<__half*>(out)[oo + t] = __float2half_rn(rv);
+    else reinterpret_cast<float*>(out)[oo + t] = rv;
+  }
+  named_bar_sync(bar, kConsumers);   // the scratch is free again
+}
 
 template <int HD, int NT, bool PRECISE>
 struct DecSmem {
+  static constexpr int NG = decode_groups(NT);       // consumer groups
+  static constexpr int THREADS = NG * kConsumers + 32;   // + 1 producer warp
   static constexpr int ROWS = NT * 8;
   static constexpr int SLOT = kT * HD * 2;           // bytes of one K or V tile
   static constexpr int QP = HD * 2 + 16;             // q row pitch (bytes): 16-byte skew against bank conflicts
   static constexpr int PP = ROWS * 2;                // P^T row pitch (bytes)
   static constexpr int Q_BYTES = ROWS * QP * (PRECISE ? 2 : 1);
-  static constexpr int P_BYTES = kT * PP * (PRECISE ? 2 : 1);
-  static constexpr int MISC = 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 2048;   // + the fused front's angles
-  static constexpr int fixed_bytes() { return Q_BYTES + P_BYTES + MISC; }
+  static constexpr int P_BYTES = kT * PP * (PRECISE ? 2 : 1);      // per group
+  static constexpr int MISC = NG * 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 2048 + 1024;   // + the fused front's angles and new row
+  static constexpr int fixed_bytes() { return Q_BYTES + NG * P_BYTES + MISC; }
   static int stages_for(int smem_limit) {
     int s = (smem_limit - 1024 - fixed_bytes()) / (2 * SLOT);
     return s > kMaxStages ? kMaxStages : s;
@@ -46,19 +153,27 @@ struct DecSmem {
 };
 
 template <int HD, int NT, bool PRECISE>
-__global__ void __launch_bounds__(kDecThreads, 1)
+__global__ void __launch_bounds__(DecSmem<HD, NT, PRECISE>::THREADS, 1)
 pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kn,
                  const __grid_constant__ CUtensorMap tm_vn, const DecodeParams p) {
   using L = DecSmem<HD, NT, PRECISE>;
   constexpr int ROWS = L::ROWS, SLOT = L::SLOT, QP = L::QP, PP = L::PP;
+  constexpr int NG = L::NG, CONS = NG * kConsumers, kDecThreads = L::THREADS, PW = 4 * NG;   // PW: the producer warp
   constexpr int MT = HD / 64;        // 16-dim output tiles per consumer warp
   constexpr int CH = HD / 64;        // 128-byte chunks per cache row of one kv head
 
   const uint32_t split = blockIdx.x, g = blockIdx.y, item = blockIdx.z;
   const uint32_t n_cols = p.items.n_cols[item];
-  const uint32_t n_rows = p.items.n_rows[item];                // cache rows the last column sees
+  if (p.gather) pdl_wait();   // the lists may come from the kernel before this one
+  // gather: the item is one column whose list (length, then rows ascending) lives on the device; the split plan is
+  // what the host would make for that many rows
+  const uint32_t* g_list = p.gather ? p.gather + (size_t)p.items.col0[item] * p.gather_stride : nullptr;
+  const uint32_t n_rows = g_list ? min(g_list[0], p.gather_stride - 1u) : p.items.n_rows[item];   // cache rows the last column sees
   const uint32_t tiles = (n_rows + kT - 1) / kT;
-  const uint32_t tps = (tiles + p.n_splits - 1) / p.n_splits;  // tiles per split
+  // every item plans for its own length: at least two tiles per CTA, at most the launch's split count (the longest
+  // item's plan, or in gather mode the most any list could need)
+  const uint32_t ns_eff = min(p.n_splits, max(1u, tiles / 2));
+  const uint32_t tps = (tiles + ns_eff - 1) / max(ns_eff, 1u);  // tiles per split
   const uint32_t tile0 = split * tps;
   if (tile0 >= tiles) return;
   const uint32_t tile1 = min(tiles, tile0 + tps);
@@ -71,17 +186,21 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   uint8_t* v_slots = base + NS * SLOT;
   uint8_t* q_hi = v_slots + NS * SLOT;
   uint8_t* q_lo = q_hi + ROWS * QP;
-  uint8_t* p_hi = q_hi + L::Q_BYTES;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = warp < PW ? warp >> 2 : 0;                    // consumer group of this warp
+  uint8_t* p_hi = q_hi + L::Q_BYTES + grp * L::P_BYTES;          // P^T of this group
   uint8_t* p_lo = p_hi + kT * PP;
-  float* s_max = reinterpret_cast<float*>(p_hi + L::P_BYTES);   // [4][ROWS]
+  float* s_max0 = reinterpret_cast<float*>(q_hi + L::Q_BYTES + NG * L::P_BYTES);
+  float* s_max = s_max0 + grp * 8 * ROWS;                       // [4][ROWS] of this group
   float* s_l = s_max + 4 * ROWS;                                // [4][ROWS]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_l + 4 * ROWS); // kfull, kempty, vfull, vempty [kMaxStages] each
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_max0 + NG * 8 * ROWS); // kfull, kempty, vfull, vempty [kMaxStages] each
   volatile uint32_t* s_err = reinterpret_cast<volatile uint32_t*>(bars + 4 * kMaxStages);
   Angle* s_ang = reinterpret_cast<Angle*>(bars + 4 * kMaxStages + 8);   // [64], fused front only
+  uint32_t* s_newk = reinterpret_cast<uint32_t*>(s_ang + 64);           // the token's own K / V row as f16 pairs (fused front)
+  uint32_t* s_newv = s_newk + 128;
 
   const uint32_t kfull = smem_u32(bars), kempty = kfull + kMaxStages * 8, vfull = kempty + kMaxStages * 8,
                  vempty = vfull + kMaxStages * 8;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // The consumers put their q loads in flight before the producer may start: a q load issued behind the
   // first 190 KB of K/V tiles of every SM would wait for all of them at the memory controllers.
@@ -212,12 +331,13 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   // behind all of them at the memory controllers.  A call that may not fetch ahead of its predecessor waits there
   // before its first tile; one that may fetches `pre_stages` tiles first and the rest after it, so that the early
   // burst has drained by the time the small loads of the critical path (q here, the predecessor's last stores) go.
-  if (warp == 4) {
+  if (warp == PW) {
     if (lane == 0) {
       *s_err = 0;
+      const uint32_t full_count = g_list ? 32u : 1u;   // a TMA tile completes by bytes; a gathered one by its 32 lanes' copies
       for (uint32_t s = 0; s < NS; ++s) {
-        mbar_init(kfull + 8 * s, 1);
-        mbar_init(vfull + 8 * s, 1);
+        mbar_init(kfull + 8 * s, full_count);
+        mbar_init(vfull + 8 * s, full_count);
         mbar_init(kempty + 8 * s, 4);
         mbar_init(vempty + 8 * s, 4);
       }
@@ -226,11 +346,12 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     __syncwarp();
     named_bar_arrive(2, kDecThreads);
   } else {
+    if (warp >= 4) pdl_wait();   // the second group reads shared memory only, but writes its records at the end
     named_bar_arrive(3, kDecThreads);
     named_bar_sync(2, kDecThreads);
   }
 
-  if (warp == 4) {
+  if (warp == PW) {
     // ---------------------------------------------------------------- producer ----
     // the whole warp walks the loop (named barrier 3 wants all of it); lane 0 issues
     const uint32_t pre = p.prefetch_old_rows ? p.pre_stages : 0u;
@@ -243,6 +364,40 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
     }
+    if (g_list) {
+      // ---- gathered rows: lane l copies the 16-byte chunks l, l + 32, ... of each listed row into the slot and swizzle
+      //      a TMA tile would fill; rows past the list's end repeat its last row (their scores are masked, their V
+      //      rows cleared, as for a tile that reaches past the sequence) ----
+      __syncwarp();
+      named_bar_sync(3, kDecThreads);
+      pdl_wait();
+      constexpr int CPR = HD / 8;                      // 16-byte chunks per row of one kv head
+      const uint64_t seq_row0 = (uint64_t)p.items.seq[item] * p.max_seq;
+      const uint32_t kvd = gridDim.y * HD;
+      for (uint32_t i = 0; i < n_tiles; ++i) {
+        const uint32_t s = i % NS, ph = (i / NS) & 1, tpos = (tile0 + i) * kT;
+        const uint32_t ra = min(g_list[1 + min(tpos + lane, n_rows - 1)], p.max_seq - 1);
+        const uint32_t rb = min(g_list[1 + min(tpos + 32 + lane, n_rows - 1)], p.max_seq - 1);
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t full = (which ? vfull : kfull) + 8 * s, empty = (which ? vempty : kempty) + 8 * s;
+          if (lane == 0) mbar_wait(empty, ph ^ 1, s_err, WAIT_EMPTY);
+          __syncwarp();
+          const __half* cache = which ? p.v_cache : p.k_cache;
+          const uint32_t dst0 = smem_u32((which ? v_slots : k_slots) + s * SLOT);
+#pragma unroll 4
+          for (uint32_t idx = lane; idx < kT * CPR; idx += 32) {
+            const uint32_t r = idx / CPR, c16g = idx % CPR;
+            const uint32_t row = __shfl_sync(0xffffffffu, r < 32 ? ra : rb, r & 31);
+            const __half* src = cache + (seq_row0 + row) * kvd + (uint64_t)g * HD + c16g * 8;
+            const uint32_t dst = dst0 + (c16g >> 3) * (kT * 128) + r * 128 + (((c16g & 7) ^ (r & 7)) << 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+          }
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full) : "memory");
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this warp is in flight when it leaves
+    } else
     for (uint32_t i = 0; i < n_tiles; ++i) {
       if (i == pre) {
         __syncwarp();
@@ -260,7 +415,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
       }
     }
-    if (n_tiles <= pre) { __syncwarp(); named_bar_sync(3, kDecThreads); }   // keeps the barrier balanced
+    if (!g_list && n_tiles <= pre) { __syncwarp(); named_bar_sync(3, kDecThreads); }   // keeps the barrier balanced
     if (lane == 0 && p.next_tiles) {
       // Everything this CTA will read has been requested.  The engine's next layer call walks the same split of
       // another cache: ask L2 for its first tiles now, so that HBM keeps delivering while this kernel drains, the
@@ -289,9 +444,11 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   }
 
   // ------------------------------------------------------------------ consumers ----
-  const int w = warp, r = lane >> 2, j = lane & 3;
+  const int w = warp & 3, r = lane >> 2, j = lane & 3;
+  const int ltid = tid - grp * kConsumers;       // thread within its consumer group
+  const uint32_t gbar = grp ? 4u : 1u;           // the group's own named barrier
 
-  if (Q_IN_REGS) {
+  if (Q_IN_REGS && grp == 0) {
     if (own_new) { kx = act_cvt(kx); vx = act_cvt(vx); kxb = act_cvt(kxb); }
     if (fused) {
 #pragma unroll
@@ -340,6 +497,9 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       k_new2 = h16(kx.x) | (h16(kx.y) << 16);
       k_new2b = h16(kxb.x) | (h16(kxb.y) << 16);
       v_new2 = h16(vx.x) | (h16(vx.y) << 16);
+      // the row also goes to shared memory: the group that takes the sequence's last tile places it there
+      if (HD == 256) { s_newk[tid] = k_new2; s_newv[tid] = v_new2; }
+      else { if (tid < 32) { s_newk[tid] = k_new2; s_newk[tid + 32] = k_new2b; } if (tid < HD / 2) s_newv[tid] = v_new2; }
       const uint64_t ro = ((uint64_t)p.items.seq[item] * p.max_seq + (n_rows - 1)) * ((uint64_t)gridDim.y * HD) + (uint64_t)g * HD + 2 * tid;
       if (HD == 256) {
         *reinterpret_cast<uint32_t*>(p.k_cache + ro) = k_new2;
@@ -373,11 +533,11 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
       for (int e = 0; e < 4; ++e) oacc[mt][nt][e] = 0.f;
   }
-  named_bar_sync(1, kConsumers);   // q visible
+  named_bar_sync(5, CONS);   // q (and the token's own row) visible to both groups
 
   const uint32_t q_hi_s = smem_u32(q_hi), q_lo_s = smem_u32(q_lo), p_hi_s = smem_u32(p_hi), p_lo_s = smem_u32(p_lo);
 
-  for (uint32_t i = 0; i < n_tiles; ++i) {
+  for (uint32_t i = grp; i < n_tiles; i += NG) {
     const uint32_t s = i % NS, ph = (i / NS) & 1;
     const uint32_t tile_pos = (tile0 + i) * kT;
     const uint32_t ks_base = smem_u32(k_slots + s * SLOT), vs_base = smem_u32(v_slots + s * SLOT);
@@ -400,9 +560,8 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         const uint32_t c16g = wi >> 2;
         return reinterpret_cast<uint32_t*>(slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (wi & 3) * 4);
       };
-      if (HD == 256) *word_at(k_slots, tid) = k_new2;
-      else if (tid < 32) { *word_at(k_slots, tid) = k_new2; *word_at(k_slots, tid + 32) = k_new2b; }
-      named_bar_sync(1, kConsumers);
+      if (ltid < HD / 2) *word_at(k_slots, ltid) = s_newk[ltid];
+      named_bar_sync(gbar, kConsumers);
     }
     if constexpr (NT <= 2) {
       // Software-pipelined: the fragments of step k2 + 1 are requested before the MMAs of step k2 are issued, so
@@ -495,7 +654,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       }
       if (r == 0) { s_max[w * ROWS + nt * 8 + 2 * j] = tmax[nt][0]; s_max[w * ROWS + nt * 8 + 2 * j + 1] = tmax[nt][1]; }
     }
-    named_bar_sync(1, kConsumers);
+    named_bar_sync(gbar, kConsumers);
 
     // ---- new running maximum, weights P = 2^(s - m), rescale factor ----
     float alpha[NT][2];
@@ -535,20 +694,20 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       }
 
     mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
-    if (own_new && i == n_tiles - 1 && tid < HD / 2) {   // made visible by the barrier below
-      const uint32_t rr = n_rows - 1 - tile_pos, c16g = tid >> 2;
-      *reinterpret_cast<uint32_t*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (tid & 3) * 4) = v_new2;
+    if (own_new && i == n_tiles - 1 && ltid < HD / 2) {   // made visible by the barrier below
+      const uint32_t rr = n_rows - 1 - tile_pos, c16g = ltid >> 2;
+      *reinterpret_cast<uint32_t*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + rr * 128 + (((c16g & 7) ^ (rr & 7)) << 4) + (ltid & 3) * 4) = s_newv[ltid];
     }
     if (tile_pos + kT > n_rows) {
       // rows of the tile past the sequence end hold whatever the cache holds there (possibly NaN):
       // their weights are zero, but 0 * NaN is NaN, so clear them
       const uint32_t nv = n_rows - tile_pos;
-      for (uint32_t idx = tid; idx < (kT - nv) * (HD / 8); idx += kConsumers) {
+      for (uint32_t idx = ltid; idx < (kT - nv) * (HD / 8); idx += kConsumers) {
         const uint32_t row = nv + idx / (HD / 8), c16g = idx % (HD / 8);
         *reinterpret_cast<uint4*>(v_slots + s * SLOT + (c16g >> 3) * (kT * 128) + row * 128 + (((c16g & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
       }
     }
-    named_bar_sync(1, kConsumers);   // P (and the cleared rows) visible to every warp
+    named_bar_sync(gbar, kConsumers);   // P (and the cleared rows) visible to every warp of the group
 
     // ---- O^T += V^T . P^T, dims (w*MT + mt)*16 .. +15 ----
     if constexpr (NT <= 2) {
@@ -627,7 +786,8 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       l += __shfl_xor_sync(0xffffffffu, l, 16);
       if (r == 0) s_l[w * ROWS + nt * 8 + 2 * j + e] = l;
     }
-  named_bar_sync(1, kConsumers);
+  named_bar_sync(gbar, kConsumers);
+  // one record per (split, group): the group's share of the split's tiles (possibly none: m = -3e38, l = 0, o = 0)
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -636,7 +796,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       if (row >= live_rows) continue;
       const uint32_t c = row / G, hh = row % G;
       const uint64_t prow = (uint64_t)(p.items.col0[item] + c) * p.n_heads + g * G + hh;
-      const uint64_t slot = prow * p.n_splits + split;
+      const uint64_t slot = (prow * p.n_splits + split) * NG + grp;
       float* po = p.part_o + slot * HD;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
@@ -650,10 +810,62 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         p.part_ml[slot * 2 + 1] = l;
       }
     }
+  if constexpr (NT <= 2) if (p.merge) {
+    // ---- one kernel per call: when every CTA of this (item, kv head) has left its record, the CTAs share out the
+    //      merge: (query row, 64-dim slice) units, dealt round-robin; LSE merge, gate and store as pa_combine_kernel does.
+    //      All CTAs of the launch are resident together (the host checks that the grid fits the GPU in one wave), so
+    //      the wait below is for CTAs that are running; it is bounded all the same. ----
+    const uint32_t ns_live = (tiles + tps - 1) / tps;             // CTAs of this (item, kv head) that hold tiles
+    const uint32_t n_units = live_rows * (HD / 64);
+    unsigned int* ctr = p.merge_ctr + 2 * ((size_t)item * gridDim.y + g);   // [0] records left, [1] CTAs done merging
+    // the gate value of this CTA's first unit is requested now and has landed by the time the records may be read
+    float gv0 = 0.f;
+    const bool gated = p.gate != nullptr;
+    auto unit_addr = [&](uint32_t u, uint64_t& prow, uint32_t& slice, uint64_t& go, uint64_t& oo) {
+      const uint32_t row = u / (HD / 64); slice = u % (HD / 64);
+      const uint32_t c = row / G, hh = row % G, col = p.items.col0[item] + c, h = g * G + hh;
+      prow = (uint64_t)col * p.n_heads + h;
+      go = (uint64_t)col * p.gate_col_stride + (uint64_t)h * p.gate_head_stride + slice * 64;
+      oo = (uint64_t)col * p.out_col_stride + (uint64_t)h * HD + slice * 64;
+    };
+    auto gate_ld = [&](uint64_t go) {
+      return p.act_f16 ? __half2float(reinterpret_cast<const __half*>(p.gate)[go + ltid]) : reinterpret_cast<const float*>(p.gate)[go + ltid];
+    };
+    if (split < n_units && gated && ltid < 64) {
+      uint64_t prow, go, oo; uint32_t slice;
+      unit_addr(split, prow, slice, go, oo);
+      gv0 = gate_ld(go);
+    }
+    __threadfence();                       // this thread's record stores, device-wide
+    named_bar_sync(gbar, kConsumers);
+    if (ltid == 0) {
+      atomicAdd(ctr, 1u);
+      uint32_t polls = 0;
+      while (*reinterpret_cast<volatile unsigned int*>(ctr) < ns_live && !*s_err) {
+        if (++polls > (1u << 20)) { *s_err = WAIT_MERGE; break; }
+        if (polls > 8) __nanosleep(64);
+      }
+      __threadfence();
+    }
+    named_bar_sync(gbar, kConsumers);
+    MergeScratch& sc = *reinterpret_cast<MergeScratch*>(k_slots);   // the ring is idle: every tile has been consumed
+    if (!*s_err) {
+      for (uint32_t u = split; u < n_units; u += ns_live) {
+        uint64_t prow, go, oo; uint32_t slice;
+        unit_addr(u, prow, slice, go, oo);
+        const float gv = (u == split) ? gv0 : ((gated && ltid < 64) ? gate_ld(go) : 0.f);
+        const uint64_t rec0 = prow * p.n_splits * NG;
+        merge_slice_128<HD>(p.part_o + rec0 * HD, p.part_ml + rec0 * 2, ns_live * NG, slice, ltid, sc, gbar, gated, gv, p.gather != nullptr, p.act_f16, p.out, oo);
+      }
+    }
+    // the last CTA to finish clears the counters for the next call (every other CTA is past its wait by then)
+    if (ltid == 0 && atomicAdd(ctr + 1, 1u) == ns_live - 1) { ctr[0] = 0; ctr[1] = 0; }
+  }
   if (*s_err && tid == 0) atomicMax(p.err, *s_err);
 }
 
 // ------------------------------------------------------------------------------ combine --
+
 
 // grid (query rows, HD / 64): one CTA per (column, head, 64-dim slice).  Every thread fetches the (m, l) of up to two
 // splits while 16 groups of 16 lanes (a float4 each) fetch the o records, splits 16 apart, eight loads in flight per
@@ -671,9 +883,12 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   if (ns == 0) {
     uint32_t it = 0;
     for (uint32_t i = 0; i < p.n_items; ++i) if (col >= p.items.col0[i]) it = i;
-    const uint32_t n_rows = p.items.n_rows[it];
-    const uint32_t tiles = (n_rows + kT - 1) / kT, tps = (tiles + p.n_splits - 1) / p.n_splits;
-    ns = tiles ? (tiles + tps - 1) / tps : 0;   // a shard that holds no row of the item: an empty record
+    // gather: one column per item, its length on the device; the plan is the one the decode kernel derived from it
+    const uint32_t n_rows = p.gather ? min(p.gather[(size_t)col * p.gather_stride], p.gather_stride - 1u) : p.items.n_rows[it];
+    const uint32_t tiles = (n_rows + kT - 1) / kT;
+    const uint32_t n_sp = min(p.n_splits, max(1u, tiles / 2));
+    const uint32_t tps = (tiles + n_sp - 1) / max(n_sp, 1u);
+    ns = tiles ? ((tiles + tps - 1) / tps) * p.groups : 0;   // a shard that holds no row of the item: an empty record
   }
   // Everything the CTA reads is requested before the first use: the (m, l) pairs, the o records of the first 128
   // splits (eight float4 per lane, splits 16 apart) and the gate value.  One memory round trip instead of three.
@@ -706,21 +921,21 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   for (int i = 1; i < 8; ++i) M = fmaxf(M, s_red[i]);
   const float w0 = (uint32_t)tid < ns ? __expf(m0 - M) : 0.f, w1 = (uint32_t)tid + 256 < ns ? __expf(m1 - M) : 0.f;
   s_w[tid] = w0; s_w[tid + 256] = w1;
-  float Lp = l0 * w0 + l1 * w1;
+  float Lp = __fmaf_rn(l1, w1, __fmul_rn(l0, w0));
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) Lp += __shfl_xor_sync(0xffffffffu, Lp, o);
+  for (int o = 16; o > 0; o >>= 1) Lp = __fadd_rn(Lp, __shfl_xor_sync(0xffffffffu, Lp, o));
   if (lane == 0) s_red2[warp] = Lp;
   __syncthreads();
   float Lsum = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) Lsum += s_red2[i];
+  for (int i = 0; i < 8; ++i) Lsum = __fadd_rn(Lsum, s_red2[i]);
 
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
     const uint32_t s = grp + 16 * u;
     const float wgt = s < ns ? s_w[s] : 0.f;
-    acc.x += x8[u].x * wgt; acc.y += x8[u].y * wgt; acc.z += x8[u].z * wgt; acc.w += x8[u].w * wgt;
+    fma4(acc, x8[u], wgt);
   }
   for (uint32_t s0 = grp + 128; s0 < ns; s0 += 64) {
     float4 x[4];
@@ -733,7 +948,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     for (int u = 0; u < 4; ++u) {
       const uint32_t s = s0 + 16 * u;
       const float wgt = s < ns ? s_w[s] : 0.f;
-      acc.x += x[u].x * wgt; acc.y += x[u].y * wgt; acc.z += x[u].z * wgt; acc.w += x[u].w * wgt;
+      fma4(acc, x[u], wgt);
     }
   }
   s_acc[grp][ln] = acc;
@@ -744,7 +959,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     const float* sa = reinterpret_cast<const float*>(s_acc);
     t = sa[tid];
 #pragma unroll
-    for (int i = 1; i < 16; ++i) t += sa[i * 64 + tid];
+    for (int i = 1; i < 16; ++i) t = __fadd_rn(t, sa[i * 64 + tid]);
   }
   if constexpr (XCH) {
     // ---- publish this rank's record slice to every rank, wait for theirs, merge across ranks ----
@@ -821,8 +1036,8 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
       }
       return;
     }
-    float rv = t / Lsum;
-    if (gated) rv *= 1.0f / (1.0f + __expf(-gv));
+    float rv = (p.gather && Lsum == 0.f) ? 0.f : __fdiv_rn(t, Lsum);   // an empty list attends nothing
+    if (gated) rv = __fmul_rn(rv, __fdiv_rn(1.0f, __fadd_rn(1.0f, __expf(-gv))));
     const uint64_t oo = (uint64_t)col * p.out_col_stride + (uint64_t)h * HD + d;
     if (p.act_f16) reinterpret_cast<__half*>(p.out)[oo] = __float2half_rn(rv);
     else reinterpret_cast<float*>(p.out)[oo] = rv;
@@ -840,6 +1055,7 @@ static cudaError_t launch_decode_t(const pa_layer* L, const DecodeParams& p, dim
   pp.n_stages = (uint32_t)stages;
   const int bytes = S::total_bytes(stages);
   static bool attr_set[64] = {};
+  if (pp.gather && (!pp.k_cache || !pp.v_cache)) return cudaErrorInvalidValue;
   auto kern = pa_decode_kernel<HD, NT, PRECISE>;
   const int dev = L->ctx->device & 63;
   if (!attr_set[dev]) {
@@ -850,7 +1066,7 @@ static cudaError_t launch_decode_t(const pa_layer* L, const DecodeParams& p, dim
   const pa_layer* N = L->next;
   if (!N || !pp.next_tiles || N->n_seqs != L->n_seqs) { N = L; pp.next_tiles = 0; }
   pp.next_max_seq = N->max_seq;
-  return launch_pdl(kern, grid, dim3(kDecThreads), (size_t)bytes, st, L->tm_k64, L->tm_v64, N->tm_k64, N->tm_v64, pp);
+  return launch_pdl(kern, grid, dim3(S::THREADS), (size_t)bytes, st, L->tm_k64, L->tm_v64, N->tm_k64, N->tm_v64, pp);
 }
 
 template <int HD, bool PRECISE>
@@ -867,6 +1083,7 @@ cudaError_t launch_decode(const pa_layer* L, const DecodeParams& p, dim3 grid, i
   const bool precise = !(L->ctx->cfg.flags & PA_FLAG_FAST);
   if (L->ctx->cfg.head_dim == 256) return precise ? launch_decode_nt<256, true>(L, p, grid, nt, st) : launch_decode_nt<256, false>(L, p, grid, nt, st);
   if (L->ctx->cfg.head_dim == 128) return precise ? launch_decode_nt<128, true>(L, p, grid, nt, st) : launch_decode_nt<128, false>(L, p, grid, nt, st);
+  if (L->ctx->cfg.head_dim == 64) return precise ? launch_decode_nt<64, true>(L, p, grid, nt, st) : launch_decode_nt<64, false>(L, p, grid, nt, st);
   return cudaErrorInvalidValue;
 }
 
@@ -876,6 +1093,8 @@ cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, 
                                          : launch_pdl(pa_combine_kernel<256, false>, dim3(rows, 4), dim3(256), 0, st, p);
   if (head_dim == 128) return p.exchange ? launch_pdl(pa_combine_kernel<128, true>, dim3(rows, 2), dim3(256), 0, st, p)
                                          : launch_pdl(pa_combine_kernel<128, false>, dim3(rows, 2), dim3(256), 0, st, p);
+  if (head_dim == 64) return p.exchange ? launch_pdl(pa_combine_kernel<64, true>, dim3(rows, 1), dim3(256), 0, st, p)
+                                        : launch_pdl(pa_combine_kernel<64, false>, dim3(rows, 1), dim3(256), 0, st, p);
   return cudaErrorInvalidValue;
 }
 

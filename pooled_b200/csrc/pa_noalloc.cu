@@ -81,8 +81,10 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
   if (n_cols < 1 || n_cols * G > (uint32_t)kMaxRows)
     return say(msg, msg_len, PA_EUNSUPPORTED, "pa_decode_static: n_cols * (n_heads / n_kv_heads) must be between 1 and 64");
   if ((uint64_t)pos + n_cols > cache_rows || cache_rows >= (1u << 31)) return say(msg, msg_len, PA_EINVAL, "pa_decode_static: pos + n_cols passes cache_rows");
+  const int nt = (int)((n_cols * G + 7) / 8);
+  const uint32_t groups = (uint32_t)decode_groups(nt);   // the decode kernel leaves one record per (row, split, consumer group)
   const uint32_t rows = n_cols * n_heads;
-  if (rows > PA_STATIC_RECORDS) {
+  if (rows * groups > PA_STATIC_RECORDS) {
     char b[160];
     snprintf(b, sizeof b, "pa_decode_static: %u query rows need more than the %d records of the built-in scratch array", rows, PA_STATIC_RECORDS);
     return say(msg, msg_len, PA_EUNSUPPORTED, b);
@@ -127,7 +129,7 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
   uint32_t ns = (uint32_t)ctx.sm_count / n_kv_heads;
   if (ns < 1) ns = 1;
   if (ns > (tiles / 2 > 1 ? tiles / 2 : 1)) ns = tiles / 2 > 1 ? tiles / 2 : 1;
-  if (ns > PA_STATIC_RECORDS / rows) ns = PA_STATIC_RECORDS / rows;   // fit the records into the fixed array
+  if (ns > PA_STATIC_RECORDS / (rows * groups)) ns = PA_STATIC_RECORDS / (rows * groups);   // fit the records into the fixed array
   if (ns > 256) ns = 256;
 
   DecodeParams p{};
@@ -141,14 +143,14 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
 
   // the one thing that must start at zero: the status word (the records are rewritten before they are read)
   if (cudaMemsetAsync(err, 0, 4, st) != cudaSuccess) return say(msg, msg_len, PA_ECUDA, "pa_decode_static: cudaMemsetAsync failed");
-  if (launch_decode(&layer, p, dim3(ns, n_kv_heads, 1), (int)((n_cols * G + 7) / 8), st) != cudaSuccess) {
+  if (launch_decode(&layer, p, dim3(ns, n_kv_heads, 1), nt, st) != cudaSuccess) {
     cudaGetLastError();
     return say(msg, msg_len, PA_ECUDA, "pa_decode_static: launching the decode kernel failed");
   }
   CombineParams c{};
   c.o = part_o; c.ml = part_ml;
-  c.o_row_stride = (uint64_t)ns * head_dim; c.o_part_stride = head_dim; c.ml_row_stride = (uint64_t)ns * 2; c.ml_part_stride = 2;
-  c.n_heads = n_heads; c.fixed_parts = 0; c.n_splits = ns;
+  c.o_row_stride = (uint64_t)ns * groups * head_dim; c.o_part_stride = head_dim; c.ml_row_stride = (uint64_t)ns * groups * 2; c.ml_part_stride = 2;
+  c.n_heads = n_heads; c.fixed_parts = 0; c.n_splits = ns; c.groups = groups;
   c.gate = gate; c.gate_col_stride = ctx.q_dim; c.gate_head_stride = head_dim; c.out = out; c.out_col_stride = ctx.q_dim; c.act_f16 = 0;
   c.partial_out = nullptr; c.partial_rows = rows; c.items = p.items; c.n_items = 1;
   if (launch_combine((int)head_dim, c, rows, st) != cudaSuccess) {

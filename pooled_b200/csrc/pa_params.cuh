@@ -25,6 +25,13 @@ struct DecodeParams {
   // the layer the engine runs next (pa_layer_set_next): once a CTA has requested its own last tile it asks L2 for the
   // first next_tiles tiles of the same split of that layer, so HBM keeps working across the kernel boundary
   uint32_t next_tiles, next_max_seq;
+  // gather mode: item i is one column attending the rows listed at gather + col0[i] * gather_stride: [0] = n, then n
+  // cache rows ascending (k_cache / v_cache above are the layer's caches)
+  const uint32_t* gather; uint32_t gather_stride;
+  // merge != 0: no combine kernel follows; the CTAs of each (item, kv head) merge their own records, gate and store
+  uint32_t merge; unsigned int* merge_ctr;
+  const void* gate; uint64_t gate_col_stride, gate_head_stride;
+  void* out; uint64_t out_col_stride; int act_f16;
   uint32_t* err;
   ItemList items;
 };
@@ -35,6 +42,8 @@ struct CombineParams {
   uint64_t o_row_stride, o_part_stride, ml_row_stride, ml_part_stride;
   uint32_t n_heads, fixed_parts;  // fixed_parts != 0: that many records per row; else from the item's split plan
   uint32_t n_splits;
+  uint32_t groups;                // records per split (the decode kernel's consumer groups)
+  const uint32_t* gather; uint32_t gather_stride;   // gather mode: the columns' row lists (their lengths set the plan)
   const void* gate; uint64_t gate_col_stride, gate_head_stride;
   void* out; uint64_t out_col_stride;
   int act_f16;

@@ -12,8 +12,12 @@
 //               carries the K / V slices only; completion is signalled to mbarriers with tcgen05.commit
 //   warp 2      allocates / frees tensor memory
 //   warps 4-7   softmax: thread r owns query row r (TMEM lane r): stores its Q row into TMEM as f16 pairs, then per
-//               tile tcgen05.ld of its S row, causal mask, running max / sum, P = 2^(s - m) as f16 pairs back into
-//               TMEM (tcgen05.st), and the epilogue (O / l, sigmoid gate, store)
+//   (and 8-11)  tile tcgen05.ld of its S row, causal mask, running max / sum, P = 2^(s - m) as f16 pairs back into
+//               TMEM (tcgen05.st), and the epilogue (O / l, sigmoid gate, store).  The causal prefill runs two such
+//               groups on alternate KV tiles (warp w and warp w + 4 reach the same 32 TMEM lanes): the exponentials
+//               of a 128 x 64 tile take one group about as long as the tile's two products take the tensor cores,
+//               so with one group the tensor pipe idles half of the time.  A row's reference maximum travels with
+//               the tiles from group to group through shared memory; each group keeps its own share of the row sum
 // S(j+1) is issued before the softmax of tile j has finished, so the tensor cores work on the next scores while
 // the weights of the current tile are being formed.  O is rescaled only when a row's running maximum has grown by
 // more than 2^8 since its last rescale (weights stay below 2^8, exact in f32 sums and safe in f16); the rescale
@@ -29,7 +33,6 @@ namespace pa {
 
 constexpr int kBM = 128;   // query rows per CTA
 constexpr int kBN = 64;    // keys per tile
-constexpr int kPfThreads = 256;
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------------
 
@@ -172,28 +175,39 @@ struct PfSmem {
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
   static constexpr int QS_BYTES = HD * 128;         // upper half of the head dims of Q: [HD/128][128 rows][128 B]
   static constexpr int X_BYTES = 0;
+  // softmax warpgroups: the causal prefill runs two, which take alternate KV tiles of the CTA's 128 query rows (the
+  // exponentials of one tile take about as long as its two products on the tensor cores, so one group leaves the
+  // tensor pipe idle half of the time); the split-K form keeps one
+  static constexpr int NGRP = MODE == 0 ? 2 : 1;
+  static constexpr int THREADS = 128 + 128 * NGRP;   // 4 service warps (K producer, MMA, TMEM, V producer) + the softmax warps
   static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
-  static constexpr int TOTAL = 1024 + OFF_BAR + 256;
-  // tensor memory columns: lower half of Q (HD/4: f16 pairs) | S0 S1 S2 (64 each; P overwrites the first 32 of
-  // its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
-  static constexpr int T_Q = 0, T_S = HD / 4, T_O = HD / 4 + kSBuf * kBN;
+  static constexpr int OFF_ROW = OFF_BAR + 256;      // per-row hand-over between the softmax groups: m[128], l[2][128], l's reference[2][128]
+  static constexpr int TOTAL = 1024 + OFF_ROW + 5 * 128 * 4;
+  // tensor memory columns: the first TQC 64-dim chunks of Q (32 columns of f16 pairs each: half of the row, all of it
+  // at head_dim 64) | S0 S1 S2 (64 each; P overwrites the first 32 of its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
+  static constexpr int TQC = HD == 64 ? 1 : HD / 128;
+  static constexpr int T_Q = 0, T_S = TQC * 32, T_O = TQC * 32 + kSBuf * kBN;
   static constexpr int TMEM_COLS = 512;
 };
 
 template <int HD, int MODE>
-__global__ void __launch_bounds__(kPfThreads, 1)
+__global__ void __launch_bounds__(PfSmem<HD, MODE>::THREADS, 1)
 pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
   using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
   constexpr bool SK = MODE != 0, PREC = MODE == 2;
-  constexpr int NK = L::NK, NV = L::NV;
+  constexpr int NK = L::NK, NV = L::NV, NGRP = L::NGRP;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 25);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 28);
   volatile uint32_t* s_err = s_tmem + 1;
+  float* s_rm = reinterpret_cast<float*>(base + L::OFF_ROW);   // [128] reference maximum of each query row (scaled, log2 units)
+  float* s_rl = s_rm + 128;                                    // [2][128] each group's row sum ...
+  float* s_rr = s_rl + 256;                                    // [2][128] ... and the reference maximum it is expressed in
   const uint32_t bar0 = smem_u32(bars);
-  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23, Q_SENT = 24 };
+  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23, Q_SENT = 24,
+         M_READY = 25 /* [2]: group g has published the row maxima after its tile */ };
   uint8_t* q_s = base + L::OFF_Q;
   auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
@@ -218,9 +232,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     for (int i = 0; i < NV; ++i) { mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1); }
     for (int i = 0; i < kSBuf; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
-    mbar_init(BAR(Q_FULL, 0), 128);
+    mbar_init(BAR(Q_FULL, 0), 128 * NGRP);
     mbar_init(BAR(Q_ISSUED, 0), 128);
     mbar_init(BAR(Q_SENT, 0), 128);
+    mbar_init(BAR(M_READY, 0), 128); mbar_init(BAR(M_READY, 1), 128);
     fence_barrier_init();
   }
   if (warp == 2) {
@@ -292,13 +307,14 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         tc_fence_after();
         const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[NK - 1]);
         const uint32_t ts = t_s0 + sb * kBN;
-        // lower half of the head dims: Q from tensor memory; upper half: Q from shared memory
+        // the head dims whose Q chunks sit in tensor memory first, then those whose Q comes from shared memory
+        constexpr int TS_STEPS = L::TQC * 4;
 #pragma unroll
-        for (int ks = 0; ks < HD / 32; ++ks)
+        for (int ks = 0; ks < TS_STEPS; ++ks)
           umma_f16_ts(leader, ts, t_q + ks * 8, kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
 #pragma unroll
-        for (int ks = HD / 32; ks < HD / 16; ++ks)
-          umma_f16_ss(leader, ts, q_desc + (uint64_t)(((((ks - HD / 32) >> 2)) * (kBM * 128) + (ks & 3) * 32) >> 4),
+        for (int ks = TS_STEPS; ks < HD / 16; ++ks)
+          umma_f16_ss(leader, ts, q_desc + (uint64_t)(((((ks - TS_STEPS) >> 2)) * (kBM * 128) + (ks & 3) * 32) >> 4),
                       kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, 1u);
         umma_commit_elected(leader, BAR(K_EMPTY, st));
         umma_commit_elected(leader, BAR(S_FULL, sb));
@@ -326,7 +342,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax + epilogue ----
-    const uint32_t qd = warp - 4, row = qd * 32 + lane;
+    const uint32_t wg = (warp - 4) >> 2;                 // softmax group: takes KV tiles wg, wg + NGRP, ...
+    const uint32_t qd = (warp - 4) & 3, row = qd * 32 + lane;   // a warp reaches the 32 TMEM lanes of its index mod 4
     const uint32_t lane_addr = (qd * 32) << 16;
     // split-K: a (column, head-of-group) pair per row; MODE 2: per two rows (even: high parts, odd: low parts)
     const bool is_lo = SK && (PREC ? (row & 1u) != 0 : row >= 64);
@@ -350,7 +367,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (early) pdl_wait();
     pdl_trigger();
     if (SK) {
-      const uint32_t pairs = p.n_cols * p.G, st_tid = tid - 128, total = pairs * q_ch;
+      const uint32_t pairs = p.n_cols * p.G, st_tid = tid - 128, total = pairs * q_ch;   // (one softmax group in this form)
       for (uint32_t idx = st_tid; idx < total; idx += 128) {
         const uint32_t pr = idx / q_ch, c = idx % q_ch;
         const uint32_t half_ch = HD * 2 / 16;
@@ -371,29 +388,32 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ---- this thread's Q row -> f16 pairs: lower half of the dims to tensor memory, upper half to shared memory ----
     {
       const uint64_t off = (uint64_t)(SK ? p.col0 + (live ? sk_c : 0) : c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)head * p.q_head_stride;
-      // 128 elements per round (the loads of a round are all in flight together): rounds below HD/2 go to tensor
-      // memory (64 columns), the others to shared memory (two 128-byte row chunks)
+      // ER elements per round (the loads of a round are all in flight together), in 64-dim chunks: the first TQC chunks
+      // of the row go to tensor memory (32 columns each), the others to shared memory (one 128-byte row chunk each)
+      constexpr int ER = HD >= 128 ? 128 : 64, ROUNDS = HD / ER, HCN = ER / 64;
 #pragma unroll 1
-      for (int c2 = 0; c2 < HD / 128; ++c2) {
-        uint32_t w[64];
+      for (int c2 = 0; c2 < ROUNDS; ++c2) {
+        // with two softmax groups each stages one round of its rows (head_dim 256); a single round is the first group's
+        if (NGRP == 2 && (uint32_t)(ROUNDS == 2 ? c2 : 0) != wg) continue;
+        uint32_t w[ER / 2];
         if (p.q_f16) {
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c2 * 128);
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + off + c2 * ER);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < ER / 8; ++i) {
             const uint32_t cb = (planes && is_lo) ? HD * 2 / 16 : 0;
-            const uint4 x = (live && (planes || !is_lo)) ? (SK ? stage_ld(cb + c2 * 16 + i) : src[i]) : make_uint4(0, 0, 0, 0);   // plain f16 q has no low part
+            const uint4 x = (live && (planes || !is_lo)) ? (SK ? stage_ld(cb + c2 * (ER / 8) + i) : src[i]) : make_uint4(0, 0, 0, 0);   // plain f16 q has no low part
             w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
           }
         } else {
-          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c2 * 128);
-          float4 xs[32];
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + off + c2 * ER);
+          float4 xs[ER / 4];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (SK) { const uint4 r4 = live ? stage_ld(c2 * 32 + i) : make_uint4(0, 0, 0, 0); xs[i] = *reinterpret_cast<const float4*>(&r4); }
+          for (int i = 0; i < ER / 4; ++i) {
+            if (SK) { const uint4 r4 = live ? stage_ld(c2 * (ER / 4) + i) : make_uint4(0, 0, 0, 0); xs[i] = *reinterpret_cast<const float4*>(&r4); }
             else xs[i] = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
           }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < ER / 4; ++i) {
             float4 x = xs[i];
             if (is_lo) {   // what the f16 high part leaves over
               x.x -= __half2float(__float2half_rn(x.x)); x.y -= __half2float(__float2half_rn(x.y));
@@ -402,22 +422,22 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
-        if (c2 == HD / 128 - 1) {
+        if (c2 == ROUNDS - 1) {
           // this thread is done with the staging area: the producers may fetch into it (and may send the tiles they
           // held back so that the early burst would not queue in front of the q requests)
           fence_proxy_async();
           mbar_arrive(BAR(Q_ISSUED, 0));
         }
 #pragma unroll
-        for (int hc = 0; hc < 2; ++hc) {
-          const int c = 2 * c2 + hc;
+        for (int hc = 0; hc < HCN; ++hc) {
+          const int c = HCN * c2 + hc;
           uint32_t wc[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) wc[i] = w[32 * hc + i];
-          if (c < HD / 128) {
+          if (c < L::TQC) {
             tmem_st32u(t_q + c * 32 + lane_addr, wc);
           } else {
-            uint8_t* dst = q_s + (c - HD / 128) * (kBM * 128) + row * 128;
+            uint8_t* dst = q_s + (c - L::TQC) * (kBM * 128) + row * 128;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               *reinterpret_cast<uint4*>(dst + ((i ^ (row & 7)) << 4)) = make_uint4(wc[4 * i], wc[4 * i + 1], wc[4 * i + 2], wc[4 * i + 3]);
@@ -431,8 +451,12 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     }
     // keys [0, lim) are visible to this row
     const uint32_t lim = SK ? (uint32_t)min(max(p.lim0 + (int32_t)min(sk_c, p.n_cols - 1), 0), (int32_t)p.n_rows) : p0 + row + 1;
-    float m_st = SK ? -1.0e30f : -INFINITY, l_sum = 0.f;   // split-K: a split may hold no visible key of a row
-    for (uint32_t j = 0; j < n_tiles; ++j) {
+    // m_st: the row's reference maximum (the weights of a tile are 2^(s - m_st); it moves only when a tile's maximum
+    // passes it by more than 2^8).  With two softmax groups it travels with the tiles: the group that took tile j - 1
+    // publishes it in s_rm, the group that takes tile j picks it up there.  l_sum: this group's share of the row sum,
+    // expressed in the reference m_l.  (split-K: a split may hold no visible key of a row, hence the finite start.)
+    float m_st = SK ? -1.0e30f : -INFINITY, l_sum = 0.f, m_l = m_st;
+    for (uint32_t j = wg; j < n_tiles; j += NGRP) {
       const uint32_t b = j % kSBuf, u = j / kSBuf, kv0 = (tile0 + j) * kBN;
       mbar_wait(BAR(S_FULL, b), u & 1, s_err, WAIT_MMA);
       tc_fence_after();
@@ -458,10 +482,20 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 #pragma unroll
       for (int i = 1; i < kBN; ++i) mt = fmaxf(mt, s[i]);
       mt *= p.scale_log2;
+      if (NGRP == 2 && j > 0) {
+        mbar_wait(BAR(M_READY, (j - 1) & 1), ((j - 1) >> 1) & 1, s_err, WAIT_MMA);
+        m_st = s_rm[row];
+      }
       float alpha = 1.f;
       bool grow = false;
       if (!SK && j == 0) m_st = mt;                 // key 0 is visible to every row, so mt is finite
-      else if (mt > m_st + 8.f) { alpha = ex2_approx(m_st - mt); m_st = mt; l_sum *= alpha; grow = true; }
+      else if (mt > m_st + 8.f) { alpha = ex2_approx(m_st - mt); m_st = mt; grow = true; }
+      if (NGRP == 2) {
+        // hand the reference on at once: the other group's next tile needs nothing else from this one
+        s_rm[row] = m_st;
+        mbar_arrive(BAR(M_READY, j & 1));
+      }
+      if (m_st != m_l) { l_sum *= ex2_approx(m_l - m_st); m_l = m_st; }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // O must not change under the previous P V: wait for it, then rescale this warp's 32 rows in TMEM
         const uint32_t jb = (j - 1) % kSBuf, ju = (j - 1) / kSBuf;
@@ -493,6 +527,15 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       mbar_arrive(BAR(P_FULL, b));
     }
     // ---- epilogue: O / l, gate, store ----
+    if (NGRP == 2) {
+      // the row sum is the two groups' shares brought to the final reference; O already is in it
+      s_rl[wg * 128 + row] = l_sum; s_rr[wg * 128 + row] = m_l;
+      const uint32_t last = n_tiles - 1;
+      mbar_wait(BAR(M_READY, last & 1), (last >> 1) & 1, s_err, WAIT_MMA);
+      named_bar_sync(2, 128 * NGRP);
+      const float m_fin = s_rm[row];
+      l_sum = s_rl[row] * ex2_approx(s_rr[row] - m_fin) + s_rl[128 + row] * ex2_approx(s_rr[128 + row] - m_fin);
+    }
     mbar_wait(BAR(O_DONE, 0), 0, s_err, WAIT_MMA);
     tc_fence_after();
     const float inv_l = 1.f / l_sum;
@@ -521,6 +564,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     } else {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
+      if (NGRP == 2 && (uint32_t)(c & 1) != wg) continue;   // the groups share the columns out
       float o[32];
       tmem_ld32(t_o + c * 32 + lane_addr, o);
       if (row < rows_valid) {
@@ -558,7 +602,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   if (tid == 0 && *s_err) atomicMax(p.err, *s_err);
 }
 
-int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ctx->cfg.head_dim == 128; }
+int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ctx->cfg.head_dim == 128 || ctx->cfg.head_dim == 64; }
 
 template <int HD, int MODE>
 static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, dim3 grid, cudaStream_t st) {
@@ -570,15 +614,20 @@ static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CU
     attr_set[dev] = true;
   }
   if (MODE == 0) {
-    pa_prefill_kernel<HD, MODE><<<grid, kPfThreads, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, p);
+    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, p);
     return cudaGetLastError();
   }
-  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(kPfThreads), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, p);
+  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, p);
 }
 
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
   const dim3 grid((p.n_cols + kBM - 1) / kBM, p.n_heads);
-  return L->ctx->cfg.head_dim == 256 ? launch_pf<256, 0>(L, p, tm_k, tm_v, grid, st) : launch_pf<128, 0>(L, p, tm_k, tm_v, grid, st);
+  switch (L->ctx->cfg.head_dim) {
+    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, grid, st);
+    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, grid, st);
+    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, grid, st);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 // k-token verify block (more than 8 query rows per kv head) on the tensor cores: split-K form of the same kernel

@@ -71,6 +71,7 @@ SYMBOLS = {
     "pa_rope_append": (_i, [_vp, _u32, _u32, _u32, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _vp, _vp]),
     "pa_rope_append_items": (_i, [_vp, _vp, _u32, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _vp]),
     "pa_decode": (_i, [_vp, C.POINTER(PaItem), _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
+    "pa_decode_gather": (_i, [_vp, _u32, _u32, _vp, _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_decode_partial": (_i, [_vp, C.POINTER(PaItem), _u32, _vp, _i, _u64, _u64, _vp, _vp]),
     "pa_merge": (_i, [_vp, _vp, _u32, _u32, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_exchange_bytes": (_sz, [_vp, _u32, _u32]),

@@ -187,7 +187,7 @@ def test_config5_full_size_batched_step():
 
 # ---- edges ---------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("nH,nKV,hd", [(16, 2, 256), (24, 4, 256), (16, 8, 128), (8, 8, 128), (32, 2, 256)])
+@pytest.mark.parametrize("nH,nKV,hd", [(16, 2, 256), (24, 4, 256), (16, 8, 128), (8, 8, 128), (32, 2, 256), (8, 2, 64)])
 @pytest.mark.parametrize("seq_len", [1, 2, 63, 64, 65, 127, 128, 129, 1000, 4097])
 def test_short_and_ragged_contexts(nH, nKV, hd, seq_len):
     eng = _engine(nH, nKV, hd, 4200, act="f32", rope_mode="none")

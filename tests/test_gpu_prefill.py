@@ -16,12 +16,13 @@ def _engine(nH, nKV, hd, max_seq, act="f32", max_cols=1024, n_rot=64, theta=1e7,
 
 
 # ---- the reference's own tile test, retargeted: tests/unit/attn_tile_test.js:118-131 --------------------------------
-# (its hd 64 case is outside this library's shapes and is checked to be refused instead)
+# (all six cases, in the reference's order: the LCG seed carries over from case to case)
 TILE_CASES = [
     dict(name="MoE shape, first pass", hd=256, nH=16, nKV=2, nc=16, basePos=0, maxSeq=512),
     dict(name="MoE shape, 5 splits, partial tile", hd=256, nH=16, nKV=2, nc=16, basePos=301, maxSeq=4096),
     dict(name="27B shape, 2 big splits", hd=256, nH=24, nKV=4, nc=16, basePos=173, maxSeq=512),
     dict(name="27B shape, TK 16", hd=256, nH=24, nKV=4, nc=16, basePos=90, maxSeq=4096),
+    dict(name="small head, 1 split target", hd=64, nH=8, nKV=2, nc=16, basePos=219, maxSeq=2048),
     dict(name="8-column batch", hd=128, nH=12, nKV=2, nc=8, basePos=77, maxSeq=1024),
 ]
 
@@ -46,11 +47,39 @@ def test_attn_tile_js_cases():
         print(f"{t['name']}: max-abs {ma:.2e} max-rel {mr:.2e}")
 
 
-def test_head_dim_64_is_refused():
+def test_head_dims_outside_64_128_256_are_refused():
+    # attnTileConfig takes any multiple of 16 up to 256 (engine/wgsl/attn_tile.js:44); the TMA boxes and the tensor-core
+    # tiles here are built from 64-element chunks, so 64, 128 and 256 (every shape pooled's models use) are what exists
     from pooled_b200 import PaError
-    with pytest.raises(PaError) as e:
-        _engine(8, 2, 64, 2048)
-    assert e.value.code == -2
+    for hd in (96, 80, 512):
+        with pytest.raises(PaError) as e:
+            _engine(8, 2, hd, 2048)
+        assert e.value.code == -2
+
+
+@pytest.mark.parametrize("n_cols,pos,act", [(700, 0, "f16"), (130, 219, "f32")])
+def test_head_dim_64_prefill_chunks_and_decode(n_cols, pos, act):
+    # head_dim 64 (the reference's "small head" case) beyond the 16-column pass of its unit test: several 128-column
+    # CTA tiles, a chunk that starts past row 0, and the decode kernel on the same cache
+    import torch
+    nH, nKV, hd = 8, 2, 64
+    td = torch.float16 if act == "f16" else torch.float32
+    eng = _engine(nH, nKV, hd, pos + n_cols + 8, act=act, max_cols=1024, n_rot=64, rope_mode="f64")
+    q, k, v, g = _inputs(9, nH, nKV, hd, pos + n_cols)
+    d = lambda a: util.torch_dev(a, td)
+    if pos:
+        eng.encode_layer(0, 0, d(q[:pos]), d(k[:pos]), d(v[:pos]), d(g[:pos]), mode="prefill")
+    out = eng.encode_layer(0, pos, d(q[pos:]), d(k[pos:]), d(v[pos:]), d(g[pos:]), mode="prefill").float().cpu().numpy()
+    eng.sync()
+    ref, Kf, Vf = _oracle_layer(q, k, v, g, nH, nKV, hd, 64, 1e7, 0)
+    gk, gv = util.read_cache(eng, 0, 0, 0, pos + n_cols)
+    assert np.array_equal(gk, Kf) and np.array_equal(gv, Vf), "KV append is not bit-exact"
+    util.assert_close(out, ref[pos:], f"head_dim 64 prefill at {pos}")
+    for c in (0, pos, pos + n_cols - 1):
+        qr = eng.rope(d(q[c:c + 1]), nH, c)
+        one = eng.decode(0, [(0, c, 1)], qr, d(g[c:c + 1])).float().cpu().numpy()
+        util.assert_close(one[0], ref[c], f"head_dim 64 decode at {c}")
+    eng.sync()
 
 
 def _inputs(cfg_id, nH, nKV, hd, n_cols):
