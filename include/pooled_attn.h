@@ -45,6 +45,11 @@ typedef enum pa_status {
 
 typedef enum pa_dtype { PA_F32 = 0, PA_F16 = 1 } pa_dtype;
 
+/* Cache formats of a layer.  pooled's engines keep f16 (Qwen35Engine's "flash" caches, the default here), int8 with one
+ * f32 scale per 32 values (kvQ8: kv_store_q8 / attn_flash_q8, engine/wgsl/qwen35.js:97-139, :908-946) or f32 (the dense
+ * engine, engine/wgsl/dense.js:22-136). */
+typedef enum pa_kv_format { PA_KV_F16 = 0, PA_KV_Q8 = 1, PA_KV_F32 = 2 } pa_kv_format;
+
 typedef enum pa_rope_mode {
   PA_ROPE_NONE = 0,  /* q and k arrive already rotated */
   PA_ROPE_F64 = 1,   /* angle pos * theta^(-2i/n_rot), cos/sin and products in float64, f32 result
@@ -92,6 +97,14 @@ PA_API int pa_destroy(pa_ctx* ctx);
 /* Replaces the per-layer cache allocation and bind groups (engine/qwen35.js:1102-1145).  Fails with a
  * readable message when the caches do not fit (engine/qwen35.js:378-383 throws at create as well). */
 PA_API int pa_layer_create(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, pa_layer** out);
+/* The same with the cache format chosen.  PA_KV_F16 is pa_layer_create.  PA_KV_Q8: int8 [n_seqs][max_seq][kv_dim] plus f32
+ * scales [n_seqs][max_seq][kv_dim / 32]; the append is kv_store_q8's arithmetic bit for bit (scale = max|x| / 127 per 32
+ * values, round to nearest even, clamp to +-127), attention dequantises value * scale as attn_flash_q8 does.
+ * PA_KV_F32: f32 caches.  On such layers pa_kv_append, pa_rope_append, pa_decode (any n_cols, each column attended on
+ * its own as the reference's kernels do), pa_prefill, pa_attn_layer(_host), pa_cache_export / _import work; the sharded
+ * and gathered calls, pa_decode_partial and the slots are for f16 caches (PA_EUNSUPPORTED).  At most 16 query heads
+ * per kv head.  These formats run a plain vector-load kernel, not the TMA / tensor-core ones of the f16 cache. */
+PA_API int pa_layer_create_fmt(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, int kv_format, pa_layer** out);
 PA_API int pa_layer_destroy(pa_layer* layer);
 /* Declares this layer's caches a shard of longer sequences: cache row 0 holds global position `origin`.  Every
  * position passed to later calls stays global; appends must fall inside [origin, origin + max_seq), decode
@@ -103,14 +116,17 @@ PA_API int pa_layer_set_origin(pa_layer* layer, uint32_t origin);
  * L2, once it has requested its own last K/V tile, for the first tiles the same call on `next` will read: HBM keeps
  * delivering while this call drains and the next one starts.  A hint only: results do not depend on it. */
 PA_API int pa_layer_set_next(pa_layer* layer, pa_layer* next);
-/* Device pointer of the K (which = 0) or V (1) cache: what _stateParts exports (engine/qwen35.js:129-141). */
+/* Device pointer of the K (which = 0) or V (1) cache, or of the K (2) / V (3) scales of a PA_KV_Q8 layer: what
+ * _stateParts exports (engine/qwen35.js:129-141). */
 PA_API void* pa_cache_ptr(pa_layer* layer, int which);
 /* KV state of one sequence to and from the host: cache rows of global positions [pos0, pos1) x kv_dim f16, K (which = 0)
  * or V (1), row p at host + (p - pos0) * kv_dim * 2 bytes.  These are the parts _stateParts lists per full-attention
  * layer ({buf: kCache, bytes: pos * kvRow}, engine/qwen35.js:129-141) and exportState / importState move
  * (engine/qwen35.js:153-196).  On a shard (pa_layer_set_origin) only the rows the shard holds are copied, each to its
  * place in the same host image, so the ranks of a sharded sequence export disjoint ranges; rows_copied (may be NULL)
- * receives how many.  Asynchronous on `stream` (use pinned host memory and pa_sync before reading). */
+ * receives how many.  Asynchronous on `stream` (use pinned host memory and pa_sync before reading).  Other formats: a row
+ * is kv_dim bytes (PA_KV_Q8) or kv_dim * 4 bytes (PA_KV_F32), and which = 2 / 3 are the K / V scales of a PA_KV_Q8 layer
+ * (kv_dim / 32 * 4 bytes a row: the kScale / vScale parts of _stateParts). */
 PA_API int pa_cache_export(pa_layer* layer, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, void* host_dst,
                            uint32_t* rows_copied, void* stream);
 PA_API int pa_cache_import(pa_layer* layer, uint32_t seq, uint32_t pos0, uint32_t pos1, int which, const void* host_src,

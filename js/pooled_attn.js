@@ -15,6 +15,7 @@ export const SYMBOLS = {
   pa_create: { parameters: [I32, BUF, BUF], result: I32 },
   pa_destroy: { parameters: [P], result: I32 },
   pa_layer_create: { parameters: [P, U32, U32, BUF], result: I32 },
+  pa_layer_create_fmt: { parameters: [P, U32, U32, I32, BUF], result: I32 },
   pa_layer_destroy: { parameters: [P], result: I32 },
   pa_layer_set_origin: { parameters: [P, U32], result: I32 },
   pa_layer_set_next: { parameters: [P, P], result: I32 },

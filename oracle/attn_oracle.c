@@ -229,6 +229,70 @@ PO_API void po_attn_f64(const float* q, uint64_t q_stride, const uint16_t* k_cac
   }
 }
 
+/* ------------------------------------------- int8 and f32 caches (kvQ8, dense) -- */
+
+/* kv_store_q8 (engine/wgsl/qwen35.js:908-946): n values (a multiple of 32) of a K or V row; per block of 32,
+ * scale = max|x| / 127 in f32, inv = 1 / scale (0 for an all-zero block), value = clamp(round(x * inv), -127, 127)
+ * with WGSL's round (ties to even).  attn_flash_q8 (engine/wgsl/qwen35.js:97-139) reads value * scale. */
+PO_API void po_kv_store_q8(const float* x, uint32_t n, int8_t* q, float* scales) {
+  for (uint32_t b = 0; b < n / 32; b++) {
+    float a = 0.0f;
+    for (int i = 0; i < 32; i++) { float v = fabsf(x[b * 32 + i]); if (v > a) a = v; }
+    float sc = a / 127.0f;
+    float inv = sc > 0.0f ? 1.0f / sc : 0.0f;
+    scales[b] = sc;
+    for (int i = 0; i < 32; i++) {
+      float r = nearbyintf(x[b * 32 + i] * inv);
+      if (r < -127.0f) r = -127.0f;
+      if (r > 127.0f) r = 127.0f;
+      q[b * 32 + i] = (int8_t)(int)r;
+    }
+  }
+}
+PO_API void po_dequant_q8(const int8_t* q, const float* scales, uint32_t n, float* x) {
+  for (uint32_t i = 0; i < n; i++) x[i] = (float)q[i] * scales[i / 32];
+}
+
+/* po_attn_f64 over f32 K/V values (an f32 cache as the dense engine keeps, engine/wgsl/dense.js:22-136, or the
+ * dequantised values of an int8 cache): the same float64 definition, tests/test_attn_dec.js:72-82. */
+PO_API void po_attn_f64_kv32(const float* q, uint64_t q_stride, const float* k_cache, const float* v_cache,
+                             uint32_t n_heads, uint32_t n_kv, uint32_t hd, uint64_t pos0, uint32_t n_cols,
+                             const float* gate, uint64_t gate_stride, double* out, uint64_t out_stride) {
+  uint32_t G = n_heads / n_kv, kv_dim = n_kv * hd;
+  double rs = sqrt((double)hd);
+  int total = (int)(n_cols * n_heads);
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int job = 0; job < total; job++) {
+    uint32_t col = (uint32_t)job / n_heads, h = (uint32_t)job % n_heads;
+    uint32_t g = h / G;
+    uint64_t n = pos0 + col + 1;
+    double* sc = (double*)malloc(sizeof(double) * n);
+    const float* qh = q + col * q_stride + (size_t)h * hd;
+    double M = -INFINITY;
+    for (uint64_t t = 0; t < n; t++) {
+      const float* kr = k_cache + t * kv_dim + (size_t)g * hd;
+      double s = 0;
+      for (uint32_t d = 0; d < hd; d++) s += (double)qh[d] * (double)kr[d];
+      sc[t] = s / rs;
+      if (sc[t] > M) M = sc[t];
+    }
+    double L = 0;
+    for (uint64_t t = 0; t < n; t++) { sc[t] = exp(sc[t] - M); L += sc[t]; }
+    double* o = out + col * out_stride + (size_t)h * hd;
+    for (uint32_t d = 0; d < hd; d++) o[d] = 0;
+    for (uint64_t t = 0; t < n; t++) {
+      const float* vr = v_cache + t * kv_dim + (size_t)g * hd;
+      double w = sc[t];
+      for (uint32_t d = 0; d < hd; d++) o[d] += w * (double)vr[d];
+    }
+    for (uint32_t d = 0; d < hd; d++) {
+      o[d] /= L;
+      if (gate) { double gg = gate[col * gate_stride + (size_t)h * hd + d]; o[d] *= 1.0 / (1.0 + exp(-gg)); }
+    }
+    free(sc);
+  }
+}
+
 /* The model-level reference's form of the same attention: scores and weights
  * stored as f32 (Float32Array sc), JavaScript double arithmetic in between,
  * the output accumulated into an f32 array one position at a time, gate

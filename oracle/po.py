@@ -48,6 +48,9 @@ def lib():
         L.po_attn_f64.argtypes = attn + [f64p, C.c_uint64]
         L.po_attn_f32ref.argtypes = attn + [f32p, C.c_uint64]
         L.po_attn_f32_fast.argtypes = attn + [f32p, C.c_uint64]
+        L.po_attn_f64_kv32.argtypes = [f32p, C.c_uint64, f32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint32, f32p, C.c_uint64, f64p, C.c_uint64]
+        L.po_kv_store_q8.argtypes = [f32p, C.c_uint32, C.POINTER(C.c_int8), f32p]
+        L.po_dequant_q8.argtypes = [C.POINTER(C.c_int8), f32p, C.c_uint32, f32p]
         L.po_threads.restype = C.c_int
         L.po_set_threads.argtypes = [C.c_int]
         L.po_lse_merge.argtypes = [f64p, f64p, f64p, C.c_uint32, C.c_uint32, f64p]
@@ -141,6 +144,45 @@ def attn_f32ref(q, k_cache, v_cache, n_heads, n_kv, hd, pos0, n_cols, gate=None)
 
 def attn_f32_fast(q, k_cache, v_cache, n_heads, n_kv, hd, pos0, n_cols, gate=None):
     return _attn(lib().po_attn_f32_fast, np.float32, q, k_cache, v_cache, n_heads, n_kv, hd, pos0, n_cols, gate)
+
+
+def kv_store_q8(x: np.ndarray):
+    """kv_store_q8 of rows x [..., n] (n % 32 == 0): (int8 values, f32 scales [..., n / 32])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    q = np.zeros(x.shape, dtype=np.int8); sc = np.zeros(x.shape[:-1] + (x.shape[-1] // 32,), dtype=np.float32)
+    lib().po_kv_store_q8(_p(x, C.c_float), x.size, _p(q, C.c_int8), _p(sc, C.c_float))
+    return q, sc
+
+
+def np_kv_store_q8(x: np.ndarray):
+    """NumPy twin of kv_store_q8 (engine/wgsl/qwen35.js:908-946)."""
+    x = np.asarray(x, dtype=np.float32)
+    b = x.reshape(x.shape[:-1] + (x.shape[-1] // 32, 32))
+    sc = (np.abs(b).max(axis=-1) / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(sc > 0, np.float32(1.0) / sc, np.float32(0.0)).astype(np.float32)
+    q = np.clip(np.rint((b * inv[..., None]).astype(np.float32)), -127, 127).astype(np.int8)
+    return q.reshape(x.shape), sc
+
+
+def dequant_q8(q: np.ndarray, sc: np.ndarray) -> np.ndarray:
+    """value * scale in f32, the order attn_flash_q8 reads them in (engine/wgsl/qwen35.js:117-120)."""
+    return (q.astype(np.float32).reshape(sc.shape + (32,)) * sc[..., None]).astype(np.float32).reshape(q.shape)
+
+
+def attn_f64_kv32(q, k_cache, v_cache, n_heads, n_kv, hd, pos0, n_cols, gate=None):
+    """attn_f64 over float32 K/V values [rows][nKV*hd] (an f32 cache, or a dequantised int8 one)."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k_cache = np.ascontiguousarray(k_cache, dtype=np.float32); v_cache = np.ascontiguousarray(v_cache, dtype=np.float32)
+    out = np.zeros((n_cols, n_heads * hd), dtype=np.float64)
+    if gate is not None:
+        gate = np.ascontiguousarray(gate, dtype=np.float32)
+        gp, gs = _p(gate, C.c_float), gate.shape[1]
+    else:
+        gp, gs = None, 0
+    lib().po_attn_f64_kv32(_p(q, C.c_float), q.shape[1], _p(k_cache, C.c_float), _p(v_cache, C.c_float), n_heads, n_kv, hd, pos0, n_cols, gp, gs,
+                           _p(out, C.c_double), out.shape[1])
+    return out
 
 
 def threads() -> int:

@@ -77,6 +77,7 @@ class AttnConfig:
     splits: int = 0
     fast: bool = False
     link_layers: bool = True          # layers run in index order, the last one followed by the first (pa_layer_set_next)
+    kv_format: str = "f16"            # "f16" | "q8" (engine option kvQ8: int8 + a scale per 32 values) | "f32" (the dense engine's caches)
 
     @property
     def q_dim(self) -> int:
@@ -88,6 +89,7 @@ class AttnConfig:
 
 
 _ROPE = {"none": _l.PA_ROPE_NONE, "f64": _l.PA_ROPE_F64, "table": _l.PA_ROPE_TABLE}
+_KVFMT = {"f16": _l.PA_KV_F16, "q8": _l.PA_KV_Q8, "f32": _l.PA_KV_F32}
 _MODE = {"auto": _l.PA_MODE_AUTO, "decode": _l.PA_MODE_DECODE, "prefill": _l.PA_MODE_PREFILL}
 
 
@@ -125,9 +127,9 @@ class AttnEngine:
         try:
             for _ in range(cfg.n_layers):
                 lh = C.c_void_p()
-                self.L.check(self.L.pa_layer_create(self.ctx, cfg.n_seqs, cfg.max_seq, C.byref(lh)), self.ctx)
+                self.L.check(self.L.pa_layer_create_fmt(self.ctx, cfg.n_seqs, cfg.max_seq, _KVFMT[cfg.kv_format], C.byref(lh)), self.ctx)
                 self.layers.append(lh)
-            if cfg.link_layers and cfg.n_layers > 1:
+            if cfg.link_layers and cfg.n_layers > 1 and cfg.kv_format == "f16":
                 for li, lh in enumerate(self.layers):
                     self.L.check(self.L.pa_layer_set_next(lh, self.layers[(li + 1) % cfg.n_layers]), self.ctx)
         except Exception:
@@ -198,9 +200,17 @@ class AttnEngine:
         self._ck(self.L.pa_layer_set_origin(self.layers[li], origin))
 
     def cache(self, li: int, which: str) -> torch.Tensor:
-        """The K ("k") or V ("v") cache of layer li as a uint16 tensor [n_seqs, max_seq, kv_dim] (no copy)."""
+        """The K ("k") or V ("v") cache of layer li as a tensor [n_seqs, max_seq, kv_dim] (no copy): int16 words of the
+        f16 values, int8 values of a "q8" layer, float32 of an "f32" one."""
         ptr = self.L.pa_cache_ptr(self.layers[li], 0 if which == "k" else 1)
-        arr = _DevArray(ptr, (self.cfg.n_seqs, self.cfg.max_seq, self.cfg.kv_dim), "<i2")
+        ts = {"f16": "<i2", "q8": "|i1", "f32": "<f4"}[self.cfg.kv_format]
+        arr = _DevArray(ptr, (self.cfg.n_seqs, self.cfg.max_seq, self.cfg.kv_dim), ts)
+        return torch.as_tensor(arr, device=f"cuda:{self.device}")
+
+    def cache_scales(self, li: int, which: str) -> torch.Tensor:
+        """The scales of a "q8" layer's K or V cache: float32 [n_seqs, max_seq, kv_dim / 32]."""
+        ptr = self.L.pa_cache_ptr(self.layers[li], 2 if which == "k" else 3)
+        arr = _DevArray(ptr, (self.cfg.n_seqs, self.cfg.max_seq, self.cfg.kv_dim // 32), "<f4")
         return torch.as_tensor(arr, device=f"cuda:{self.device}")
 
     # ---- the path, step by step ----
@@ -364,11 +374,17 @@ class AttnEngine:
     def state_signature(self) -> dict:
         """What a saved state must match to be loaded here (stateSignature, engine/qwen35.js:143-151, attention part)."""
         c = self.cfg
-        return {"v": 1, "layers": c.n_layers, "kv": "f16", "dims": [c.kv_dim, c.n_kv_heads, c.head_dim]}
+        return {"v": 1, "layers": c.n_layers, "kv": c.kv_format, "dims": [c.kv_dim, c.n_kv_heads, c.head_dim]}
 
     def _state_parts(self, pos: int):
-        """_stateParts (engine/qwen35.js:129-141): per layer the K rows [0, pos) then the V rows [0, pos)."""
-        return [(li, which, pos * self.cfg.kv_dim * 2) for li in range(len(self.layers)) for which in (0, 1)]
+        """_stateParts (engine/qwen35.js:129-141): per layer the K rows [0, pos) then the V rows [0, pos), then (kvQ8) the K
+        and the V scales."""
+        row = self.cfg.kv_dim * {"f16": 2, "q8": 1, "f32": 4}[self.cfg.kv_format]
+        parts = [(li, which, pos * row) for li in range(len(self.layers)) for which in (0, 1)]
+        if self.cfg.kv_format == "q8":
+            parts = [x for li in range(len(self.layers)) for x in ((li, 0, pos * row), (li, 1, pos * row), (li, 2, pos * self.cfg.kv_dim // 32 * 4),
+                                                                    (li, 3, pos * self.cfg.kv_dim // 32 * 4))]
+        return parts
 
     def export_state(self, pos: int, seq: int = 0) -> dict:
         """exportState (engine/qwen35.js:153): {sig, pos, parts: [bytes]}, rows [0, pos) of every layer.  On a shard the

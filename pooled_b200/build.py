@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libpooled_attn.so")
-SOURCES = ["pa_api.cu", "pa_rope_append.cu", "pa_decode.cu", "pa_prefill.cu", "pa_noalloc.cu"]
+SOURCES = ["pa_api.cu", "pa_rope_append.cu", "pa_decode.cu", "pa_prefill.cu", "pa_kvfmt.cu", "pa_noalloc.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "--use_fast_math=false",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

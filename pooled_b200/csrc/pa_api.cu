@@ -23,6 +23,8 @@ cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t 
 int prefill_supported(const pa_ctx* ctx);
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
 cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
+cudaError_t launch_kv_store(const KvStoreParams& p, uint32_t n_cols, cudaStream_t st);
+cudaError_t launch_decode_any(const AnyDecodeParams& p, int format, dim3 grid, cudaStream_t st);
 }  // namespace pa
 
 using namespace pa;
@@ -160,6 +162,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   ctx->tune.no_fuse = getenv("POOLED_ATTN_NO_FUSE") != nullptr;
   ctx->tune.verify_mma_sync = getenv("POOLED_ATTN_VERIFY_MMA_SYNC") != nullptr;
   ctx->tune.no_merge = getenv("POOLED_ATTN_NO_MERGE") != nullptr;
+  if (const char* e = getenv("POOLED_ATTN_OWN_PREFETCH")) ctx->tune.own_prefetch = atoi(e) != 0;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -196,7 +199,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
 extern "C" int pa_destroy(pa_ctx* ctx) {
   if (!ctx) return PA_OK;
   cudaSetDevice(ctx->device);
-  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->norm_q); cudaFree(ctx->norm_k); cudaFree(ctx->q_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err); cudaFree(ctx->merge_ctr);
+  cudaFree(ctx->inv_freq); cudaFree(ctx->angles); cudaFree(ctx->norm_q); cudaFree(ctx->norm_k); cudaFree(ctx->q_rot); cudaFree(ctx->k_rot); cudaFree(ctx->part_o); cudaFree(ctx->part_ml); cudaFree(ctx->dev_err); cudaFree(ctx->merge_ctr);
   cudaFree(ctx->stage_dev);
   for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
@@ -205,37 +208,55 @@ extern "C" int pa_destroy(pa_ctx* ctx) {
   return PA_OK;
 }
 
-extern "C" int pa_layer_create(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, pa_layer** out) {
+// bytes of one cache row and of one row of scales in a layer's format
+static size_t row_bytes_of(const pa_ctx* ctx, int fmt) { return (size_t)ctx->kv_dim * (fmt == PA_KV_Q8 ? 1 : fmt == PA_KV_F32 ? 4 : 2); }
+static size_t scale_row_bytes_of(const pa_ctx* ctx, int fmt) { return fmt == PA_KV_Q8 ? (size_t)ctx->kv_dim / 32 * 4 : 0; }
+
+extern "C" int pa_layer_create_fmt(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, int kv_format, pa_layer** out) {
   if (!ctx || !out) return fail(ctx, PA_EINVAL, "pa_layer_create: null argument");
   *out = nullptr;
   if (n_seqs < 1 || max_seq < 1) return fail(ctx, PA_EINVAL, "pa_layer_create: n_seqs and max_seq must be positive");
+  if (kv_format != PA_KV_F16 && kv_format != PA_KV_Q8 && kv_format != PA_KV_F32) return fail(ctx, PA_EINVAL, "pa_layer_create: unknown cache format %d", kv_format);
+  if (kv_format != PA_KV_F16 && ctx->G > 16) return fail(ctx, PA_EUNSUPPORTED, "pa_layer_create: int8 / f32 caches take at most 16 query heads per kv head");
   const uint64_t rows = (uint64_t)n_seqs * max_seq;
   if (rows >= (1ull << 31)) return fail(ctx, PA_EUNSUPPORTED, "pa_layer_create: %llu cache rows exceed the 2^31 row limit of one layer", (unsigned long long)rows);
   pa_layer* L = new (std::nothrow) pa_layer();
   if (!L) return fail(ctx, PA_ENOMEM, "pa_layer_create: out of host memory");
-  L->ctx = ctx; L->n_seqs = n_seqs; L->max_seq = max_seq;
+  L->ctx = ctx; L->n_seqs = n_seqs; L->max_seq = max_seq; L->kv_format = kv_format;
   cudaSetDevice(ctx->device);
-  const size_t bytes = rows * ctx->kv_dim * 2;
+  const size_t bytes = rows * row_bytes_of(ctx, kv_format), sbytes = rows * scale_row_bytes_of(ctx, kv_format);
   size_t free_b = 0, total_b = 0;
   cudaMemGetInfo(&free_b, &total_b);
-  if (cudaMalloc(&L->k, bytes) != cudaSuccess || cudaMalloc(&L->v, bytes) != cudaSuccess) {
+  void *kp = nullptr, *vp = nullptr;
+  bool ok = cudaMalloc(&kp, bytes) == cudaSuccess && cudaMalloc(&vp, bytes) == cudaSuccess;
+  if (ok && sbytes) ok = cudaMalloc(&L->k_scale, sbytes) == cudaSuccess && cudaMalloc(&L->v_scale, sbytes) == cudaSuccess;
+  if (ok && kv_format != PA_KV_F16 && !ctx->k_rot) ok = cudaMalloc(&ctx->k_rot, (size_t)ctx->cfg.max_cols * ctx->kv_dim * 4) == cudaSuccess;
+  if (!ok) {
     cudaGetLastError();
-    cudaFree(L->k);
+    cudaFree(kp); cudaFree(vp); cudaFree(L->k_scale); cudaFree(L->v_scale);
     delete L;
     return fail(ctx, PA_ENOMEM, "context %u x %u sequences needs two %.0f MiB KV buffers for this layer; the device has %.0f MiB free (ask for a shorter context or fewer sequences)",
                 max_seq, n_seqs, bytes / 1048576.0, free_b / 1048576.0);
   }
-  int rc = make_cache_map(ctx, &L->tm_k64, L->k, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
-  if (!rc) rc = make_cache_map(ctx, &L->tm_v64, L->v, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
-  if (rc) { cudaFree(L->k); cudaFree(L->v); delete L; return rc; }
+  if (kv_format == PA_KV_F16) {
+    L->k = (__half*)kp; L->v = (__half*)vp;
+    int rc = make_cache_map(ctx, &L->tm_k64, L->k, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
+    if (!rc) rc = make_cache_map(ctx, &L->tm_v64, L->v, rows, ctx->kv_dim, ctx->cfg.head_dim, 64);
+    if (rc) { cudaFree(L->k); cudaFree(L->v); delete L; return rc; }
+  } else {
+    L->k_alt = kp; L->v_alt = vp;
+  }
   *out = L;
   return PA_OK;
+}
+extern "C" int pa_layer_create(pa_ctx* ctx, uint32_t n_seqs, uint32_t max_seq, pa_layer** out) {
+  return pa_layer_create_fmt(ctx, n_seqs, max_seq, PA_KV_F16, out);
 }
 
 extern "C" int pa_layer_destroy(pa_layer* L) {
   if (!L) return PA_OK;
   cudaSetDevice(L->ctx->device);
-  cudaFree(L->k); cudaFree(L->v);
+  cudaFree(L->k); cudaFree(L->v); cudaFree(L->k_alt); cudaFree(L->v_alt); cudaFree(L->k_scale); cudaFree(L->v_scale);
   delete L;
   return PA_OK;
 }
@@ -273,7 +294,13 @@ extern "C" int pa_layer_set_head_norm(pa_layer* L, const float* q_w, const float
   return PA_OK;
 }
 
-extern "C" void* pa_cache_ptr(pa_layer* L, int which) { return L ? (which ? (void*)L->v : (void*)L->k) : nullptr; }
+extern "C" void* pa_cache_ptr(pa_layer* L, int which) {
+  if (!L) return nullptr;
+  if (which == 2) return L->k_scale;
+  if (which == 3) return L->v_scale;
+  if (L->kv_format != PA_KV_F16) return which ? L->v_alt : L->k_alt;
+  return which ? (void*)L->v : (void*)L->k;
+}
 
 extern "C" int pa_sync(pa_ctx* ctx, void* stream) {
   if (!ctx) return PA_EINVAL;
@@ -429,6 +456,30 @@ static int ensure_angles(pa_ctx* ctx, uint32_t pos, uint32_t n_cols, cudaStream_
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
                             uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
                             uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false, uint64_t vcs = 0) {
+  if (L && L->kv_format != PA_KV_F16) {
+    // int8 / f32 caches: q rotated as usual; k rotated into the context's f32 scratch (the rotation kernel's q path,
+    // with the kv heads as its heads), then the format's own store kernel -- attn_glue followed by kv_store_q8
+    if (n_cols > ctx->cfg.max_cols) return fail(ctx, PA_EINVAL, "rope: %u columns exceed max_cols %u", n_cols, ctx->cfg.max_cols);
+    if (q)
+      if (int rc = rope_append_impl(nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, q_heads, q_out, q_out_cs, nullptr, nullptr, 0, cs_table, mode, in_f16, st, q_out_f16, in_layer_call))
+        return rc;
+    if (!k) return PA_OK;
+    KvStoreParams sp{};
+    sp.format = L->kv_format; sp.kv_dim = ctx->kv_dim; sp.cache_row0 = (uint64_t)seq * L->max_seq + (pos - L->origin);
+    sp.k8 = (int8_t*)L->k_alt; sp.v8 = (int8_t*)L->v_alt; sp.ks = L->k_scale; sp.vs = L->v_scale; sp.k32 = (float*)L->k_alt; sp.v32 = (float*)L->v_alt;
+    sp.v = v; sp.v_col_stride = vcs ? vcs : kvcs; sp.v_f16 = in_f16;
+    if (mode == PA_ROPE_NONE) { sp.k = k; sp.k_col_stride = kvcs; sp.k_f16 = in_f16; }
+    else {
+      if (int rc = rope_append_impl(nullptr, ctx, seq, pos, n_cols, k, kvcs, ctx->cfg.head_dim, ctx->cfg.n_kv_heads, ctx->k_rot, ctx->kv_dim, nullptr, nullptr, 0, cs_table,
+                                    mode, in_f16, st, 0, false))
+        return rc;
+      sp.k = ctx->k_rot; sp.k_col_stride = ctx->kv_dim; sp.k_f16 = 0;
+    }
+    CU_TRY(ctx, launch_kv_store(sp, n_cols, st));
+    ctx->stats.kernel_launches++;
+    ctx->inflight_layer = nullptr;
+    return PA_OK;
+  }
   RopeParams p{};
   p.q_out_f16 = q_out_f16;
   if (q_out_f16 == 2) p.q_lo_offset = (uint64_t)ctx->cfg.max_cols * ctx->q_dim;   // second half of the f32-sized q_rot buffer
@@ -570,10 +621,61 @@ struct FusedFront { const void* k; const void* v; bool append; uint32_t pos; };
 // a gathered call: the columns' row lists on the device, one list of `stride` words per column
 struct GatherLists { const uint32_t* lists; uint32_t stride; };
 
+// Decode / verify / prefill over an int8 or f32 cache: per item, blocks of columns small enough for the record buffers;
+// each block is one launch of the plain split-K kernel (a CTA per (split, kv head, column)) and one combine.
+static int decode_any_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
+                           uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, cudaStream_t st, const char* who) {
+  pa_ctx* ctx = L->ctx;
+  if (!q || !out) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
+  if (!items || n_items < 1) return fail(ctx, PA_EINVAL, "%s: no items", who);
+  cudaSetDevice(ctx->device);
+  const size_t qes = q_dtype == PA_F16 ? 2 : 4, aes = ctx->cfg.act_dtype == PA_F16 ? 2 : 4;
+  const uint32_t hd = ctx->cfg.head_dim, nH = ctx->cfg.n_heads;
+  const uint32_t block = std::max<uint32_t>(1u, (uint32_t)(ctx->part_slots / (4ull * nH)));   // columns per launch: room for four splits at least
+  uint64_t col = 0;
+  for (uint32_t i = 0; i < n_items; ++i) {
+    if (int rc = check_cols(L, items[i].seq, items[i].pos, items[i].n_cols, who)) return rc;
+    for (uint32_t c0 = 0; c0 < items[i].n_cols; c0 += block) {
+      const uint32_t nc = std::min(block, items[i].n_cols - c0);
+      const uint32_t pos0 = items[i].pos + c0;
+      const uint32_t rows = pos0 + nc - L->origin;                 // rows the block's last column sees
+      const uint32_t ns = plan_splits(ctx, rows, 1, nc, 1);
+      AnyDecodeParams a{};
+      a.q = reinterpret_cast<const uint8_t*>(q) + (col + c0) * qcs * qes; a.q_f16 = q_dtype == PA_F16; a.q_col_stride = qcs; a.q_head_stride = qhs;
+      a.k = L->k_alt; a.v = L->v_alt; a.ks = L->k_scale; a.vs = L->v_scale;
+      a.kv_dim = ctx->kv_dim; a.hd = hd; a.G = ctx->G; a.n_heads = nH; a.max_seq = L->max_seq; a.n_splits = ns;
+      a.seq = items[i].seq; a.lim0 = (int32_t)(pos0 + 1 - L->origin); a.n_rows = rows; a.col0 = 0;
+      a.part_o = ctx->part_o; a.part_ml = ctx->part_ml;
+      timing_mark(ctx, st, 0);
+      CU_TRY(ctx, launch_decode_any(a, L->kv_format, dim3(ns, ctx->cfg.n_kv_heads, nc), st));
+      timing_mark(ctx, st, 1);
+      CombineParams c{};
+      c.o = ctx->part_o; c.ml = ctx->part_ml;
+      c.o_row_stride = (uint64_t)ns * hd; c.o_part_stride = hd; c.ml_row_stride = (uint64_t)ns * 2; c.ml_part_stride = 2;
+      c.n_heads = nH; c.fixed_parts = 0; c.n_splits = ns; c.groups = 1;
+      c.gate = gate ? reinterpret_cast<const uint8_t*>(gate) + (col + c0) * gcs * aes : nullptr; c.gate_col_stride = gcs; c.gate_head_stride = ghs;
+      c.out = reinterpret_cast<uint8_t*>(out) + (col + c0) * ocs * aes; c.out_col_stride = ocs; c.act_f16 = ctx->cfg.act_dtype == PA_F16;
+      c.items.seq[0] = items[i].seq; c.items.lim0[0] = a.lim0; c.items.n_rows[0] = rows; c.items.n_cols[0] = nc; c.items.col0[0] = 0; c.n_items = 1;
+      c.err = ctx->dev_err;
+      if (!ctx->core_only) CU_TRY(ctx, launch_combine((int)hd, c, nc * nH, st));
+      ctx->stats.kernel_launches += ctx->core_only ? 1 : 2;
+      ctx->stats.kv_bytes_streamed += 2ull * rows * (row_bytes_of(ctx, L->kv_format) + scale_row_bytes_of(ctx, L->kv_format));
+    }
+    col += items[i].n_cols;
+  }
+  ctx->stats.calls++;
+  ctx->inflight_layer = nullptr;
+  return PA_OK;
+}
+
 static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, float* partial, cudaStream_t st, const char* who, bool after_own_append = false,
                        bool exchange = false, const FusedFront* fz = nullptr, const void* q_lo = nullptr, const GatherLists* gl = nullptr) {
   pa_ctx* ctx = L->ctx;
+  if (L->kv_format != PA_KV_F16) {
+    if (partial || exchange || gl) return fail(ctx, PA_EUNSUPPORTED, "%s: partial records, the peer exchange and row lists are for f16 caches", who);
+    return decode_any_impl(L, items, n_items, q, q_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, st, who);
+  }
   if (!q || (!out && !partial)) return fail(ctx, PA_EINVAL, "%s: null q or output", who);
   if ((qcs & 1) || (qhs & 1) || ((uintptr_t)q & 7)) return fail(ctx, PA_EINVAL, "%s: q strides must be even and q 8-byte aligned", who);
   DecodeParams p{};
@@ -590,7 +692,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   // One sequence with more than 8 query rows per kv head (a k-token verify block) goes to the tensor-core split-K
   // kernel; single tokens and batches of sequences stay on the streaming mma.sync kernel.
   const bool verify_tc = n_items == 1 && nt > 1 && max_rows > 0 && !ctx->tune.verify_mma_sync && !gl && ctx->cfg.head_dim >= 128;
-  const uint32_t groups = verify_tc ? 1u : (uint32_t)decode_groups(nt);   // records per split
+  const uint32_t groups = 1u;   // records per split: one, whatever the number of consumer groups
   uint32_t ns = plan_splits(ctx, max_rows, n_items, total_cols, groups);
   if (gl) {
     // the lists' lengths live on the device: the grid is sized for the longest list possible and each CTA derives its
@@ -611,6 +713,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   p.prefetch_old_rows = after_own_append ? 1u : 0u;
   p.early_limit = (after_own_append && ctx->inflight_layer == L) ? ctx->inflight_row0 : 0xffffffffu;
   p.pre_stages = (uint32_t)ctx->tune.pre_stages;
+  p.own_prefetch = ctx->tune.own_prefetch ? 1u : 0u;
   p.next_tiles = (L->next && L->next->ctx == ctx) ? (uint32_t)ctx->tune.next_tiles : 0u;
   if (fz) {
     p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
@@ -634,11 +737,17 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   // One kernel per call where the merge can be shared out among the call's own CTAs: all of them resident at once (one
   // wave at one CTA per SM), and at least half as many CTAs per (item, kv head) as there are (row, 64-dim slice) units.
   const uint32_t units = max_cols * ctx->G * (ctx->cfg.head_dim / 64);
-  const bool merge = !partial && !exchange && !verify_tc && nt <= 2 && !ctx->core_only && !ctx->tune.no_merge && max_rows > 0 &&
+  bool all_rows = true;   // on a shard an item may have no row here: its CTAs never run, so its units must be the combine kernel's
+  for (uint32_t i = 0; i < n_items; ++i) all_rows = all_rows && p.items.n_rows[i] > 0;
+  const bool merge = !partial && !verify_tc && nt <= 2 && all_rows && !ctx->core_only && !ctx->tune.no_merge && max_rows > 0 &&
                      (uint64_t)ns * ctx->cfg.n_kv_heads * n_items <= (uint64_t)ctx->sm_count && 2 * ns >= units;
   if (merge) {
     p.merge = 1; p.merge_ctr = ctx->merge_ctr;
     p.gate = gate; p.gate_col_stride = gcs; p.gate_head_stride = ghs; p.out = out; p.out_col_stride = ocs; p.act_f16 = ctx->cfg.act_dtype == PA_F16;
+    if (exchange) {
+      p.exchange = 1; p.xc = ctx->xc; p.xch_sweeps = ctx->tune.wait_polls ? ctx->tune.wait_polls : (1u << 20);
+      p.xch_units = total_cols * ctx->cfg.n_heads * (ctx->cfg.head_dim / 64);
+    }
   }
   timing_mark(ctx, st, 0);
   if (verify_tc) CU_TRY(ctx, launch_verify(L, vp, tm_k, tm_v, ctx->cfg.n_kv_heads, st));
@@ -729,6 +838,11 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
                         uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, cudaStream_t st) {
   pa_ctx* ctx = L->ctx;
   if (!q || !out) return fail(ctx, PA_EINVAL, "pa_prefill: null q or out");
+  if (L->kv_format != PA_KV_F16) {   // every column attended on its own, as the reference's kernels for these formats do
+    if (n_cols < 1 || n_cols > ctx->cfg.max_cols) return fail(ctx, PA_EINVAL, "pa_prefill: %u columns, the context was created for at most %u", n_cols, ctx->cfg.max_cols);
+    pa_item it{seq, pos, n_cols, 0};
+    return decode_any_impl(L, &it, 1, q, q_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, st, "pa_prefill");
+  }
   if (int rc = check_cols(L, seq, pos, n_cols, "pa_prefill")) return rc;
   if (!prefill_supported(ctx)) return fail(ctx, PA_EUNSUPPORTED, "pa_prefill: head_dim %u is outside the tiled prefill kernel's shapes", ctx->cfg.head_dim);
   const uint64_t qm = q_dtype == PA_F16 ? 7 : 3, om = ctx->cfg.act_dtype == PA_F16 ? 7 : 3;   // 16-byte vector accesses
@@ -835,6 +949,16 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // which the RoPE kernel writes directly: nothing is left to convert in the attention kernel's prologue.
   const bool planes = mode != PA_MODE_PREFILL && n_cols * ctx->G > 8 && n_cols * ctx->G <= (uint32_t)kMaxRows && !(ctx->cfg.flags & PA_FLAG_FAST) &&
                       !ctx->tune.verify_mma_sync && ctx->cfg.head_dim >= 128;
+  if (L->kv_format != PA_KV_F16) {
+    if (sharded) return fail(ctx, PA_EUNSUPPORTED, "pa_attn_layer_sharded: the peer exchange is for f16 caches");
+    if (n_cols > ctx->cfg.max_cols) return fail(ctx, PA_EINVAL, "pa_attn_layer: %u columns exceed max_cols %u", n_cols, ctx->cfg.max_cols);
+    if (!ctx->core_only)
+      if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kcs, cs_table, ctx->cfg.rope_mode,
+                                    ctx->cfg.act_dtype == PA_F16, st, 0, true, kvcs))
+        return rc;
+    pa_item it{seq, pos, n_cols, 0};
+    return decode_any_impl(L, &it, 1, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st, "pa_attn_layer");
+  }
   if (sharded) {
     // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
     const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
@@ -1010,15 +1134,17 @@ static int cache_copy(pa_layer* L, uint32_t seq, uint32_t pos0, uint32_t pos1, i
   pa_ctx* ctx = L->ctx;
   GUARD(ctx);
   if (rows_out) *rows_out = 0;
-  if (!host || (which != 0 && which != 1)) return fail(ctx, PA_EINVAL, "%s: null host buffer, or `which` is neither 0 (K) nor 1 (V)", who);
+  const bool scales = which == 2 || which == 3;
+  if (!host || which < 0 || which > 3 || (scales && L->kv_format != PA_KV_Q8))
+    return fail(ctx, PA_EINVAL, "%s: null host buffer, or `which` is not 0 (K), 1 (V) or, on an int8 layer, 2 / 3 (their scales)", who);
   if (seq >= L->n_seqs || pos1 < pos0) return fail(ctx, PA_EINVAL, "%s: sequence %u of %u, positions [%u, %u)", who, seq, L->n_seqs, pos0, pos1);
   uint32_t first;
   const uint32_t n = shard_span(L, pos0, pos1, &first);
   if (rows_out) *rows_out = n;
   if (!n) return PA_OK;
   cudaSetDevice(ctx->device);
-  const size_t row_bytes = (size_t)ctx->kv_dim * 2;
-  uint8_t* dev = reinterpret_cast<uint8_t*>(which ? L->v : L->k) + ((size_t)seq * L->max_seq + (first - L->origin)) * row_bytes;
+  const size_t row_bytes = scales ? scale_row_bytes_of(ctx, L->kv_format) : row_bytes_of(ctx, L->kv_format);
+  uint8_t* dev = reinterpret_cast<uint8_t*>(pa_cache_ptr(L, which)) + ((size_t)seq * L->max_seq + (first - L->origin)) * row_bytes;
   uint8_t* h = reinterpret_cast<uint8_t*>(host) + (size_t)(first - pos0) * row_bytes;
   if (to_host) CU_TRY(ctx, cudaMemcpyAsync(h, dev, (size_t)n * row_bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   else {
@@ -1047,6 +1173,7 @@ extern "C" int pa_slot_save(pa_layer* L, uint32_t seq, uint32_t pos, pa_slot** o
   pa_ctx* ctx = L->ctx;
   GUARD(ctx);
   *out = nullptr;
+  if (L->kv_format != PA_KV_F16) return fail(ctx, PA_EUNSUPPORTED, "pa_slot_save: slots are for f16 caches (use pa_cache_export / pa_cache_import)");
   if (seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "pa_slot_save: sequence %u of %u", seq, L->n_seqs);
   pa_slot* s = new (std::nothrow) pa_slot();
   if (!s) return fail(ctx, PA_ENOMEM, "pa_slot_save: out of host memory");
@@ -1070,7 +1197,8 @@ extern "C" int pa_slot_load(pa_layer* L, uint32_t seq, const pa_slot* s, uint32_
   if (!L || !s) return PA_EINVAL;
   pa_ctx* ctx = L->ctx;
   GUARD(ctx);
-  if (s->ctx != ctx || s->row_bytes != (size_t)ctx->kv_dim * 2) return fail(ctx, PA_EINVAL, "pa_slot_load: the slot was saved from another context");
+  if (s->ctx != ctx || s->row_bytes != (size_t)ctx->kv_dim * 2 || L->kv_format != PA_KV_F16)
+    return fail(ctx, PA_EINVAL, "pa_slot_load: the slot was saved from another context or cache format");
   if (seq >= L->n_seqs) return fail(ctx, PA_EINVAL, "pa_slot_load: sequence %u of %u", seq, L->n_seqs);
   uint32_t first;
   const uint32_t rows = shard_span(L, 0, s->pos, &first);
@@ -1170,6 +1298,7 @@ extern "C" int pa_decode_exchange(pa_layer* L, const pa_item* items, uint32_t n_
   if (!L) return PA_EINVAL;
   GUARD(L->ctx);
   if (!out) return fail(L->ctx, PA_EINVAL, "pa_decode_exchange: null out");
+  if (L->kv_format != PA_KV_F16) return fail(L->ctx, PA_EUNSUPPORTED, "pa_decode_exchange: the peer exchange is for f16 caches");
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
                      (cudaStream_t)stream, "pa_decode_exchange", false, true);
 }

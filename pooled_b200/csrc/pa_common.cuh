@@ -168,10 +168,11 @@ __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) 
 
 // ---- host side -----------------------------------------------------------------------------------
 
-// Consumer groups of the decode kernel for a call of nt 8-row groups of query rows.  The kernel is written for one or
-// two groups of four warps (two take alternate tiles and leave a record each); one is what runs: with two, a group
-// may ask for a slot of the shared ring before the other group's earlier tile has landed in it, and a parity wait
-// cannot tell those two phases apart.
+// Consumer groups of the decode kernel for a call of nt 8-row groups of query rows.  The kernel can run two groups of
+// four warps on alternate tiles (slots carry tile numbers, the second group's (o, m, l) is folded into the first's
+// before the record is written); measured on config 2 that is slower than one group: a group's tile goes from 1.2 to
+// 1.7 us when another group shares the SM's shared-memory bandwidth (each tile re-reads the hi and lo query fragments
+// besides K and V), and the fold adds a microsecond at the end.  One group is what runs.
 __host__ __device__ constexpr int decode_groups(int nt) { return nt >= 0 ? 1 : 2; }
 
 constexpr int kMaxItems = 32;     // items of one batched decode call
@@ -232,6 +233,7 @@ struct pa_ctx {
   const pa_layer* inflight_layer = nullptr;
   uint32_t inflight_row0 = 0;
   float* q_rot = nullptr;      // device: rotated q of the current call, f32 [max_cols][q_dim]
+  float* k_rot = nullptr;      // device: rotated k of the current call, f32 [max_cols][kv_dim] (int8 / f32 caches; made with the first such layer)
   float* part_o = nullptr;     // device: split partials, f32 [rows][splits][head_dim] of the current call
   float* part_ml = nullptr;    // device: f32 [rows][splits][2]
   uint32_t max_splits = 0;
@@ -253,9 +255,10 @@ struct pa_ctx {
   // measurement switches, read from the environment once when the context is created
   struct Tuning {
     int pre_stages = 2;          // POOLED_ATTN_PRE_STAGES: K/V tiles a decode CTA fetches ahead of its predecessor's end
-    int next_tiles = 2;          // POOLED_ATTN_NEXT_TILES: tiles of the next layer each decode CTA asks L2 to fetch at its end
+    int next_tiles = 0;          // POOLED_ATTN_NEXT_TILES: tiles of the next layer each decode CTA asks L2 to fetch at its end
     bool no_fuse = false;        // POOLED_ATTN_NO_FUSE: RoPE/append -> decode -> combine chain instead of the fused front
     bool verify_mma_sync = false;// POOLED_ATTN_VERIFY_MMA_SYNC: k-token blocks on the mma.sync kernel
+    bool own_prefetch = false;   // POOLED_ATTN_OWN_PREFETCH=1: L2 requests for a decode CTA's own later tiles at entry
     bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel
     uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)
   } tune;
@@ -268,8 +271,13 @@ struct pa_layer {
   pa_ctx* ctx = nullptr;
   uint32_t n_seqs = 0, max_seq = 0;
   uint32_t origin = 0;           // global position of cache row 0 (a shard of a longer sequence)
-  __half* k = nullptr;
+  __half* k = nullptr;           // f16 caches (PA_KV_F16) ...
   __half* v = nullptr;
+  int kv_format = PA_KV_F16;
+  void* k_alt = nullptr;         // ... or int8 / f32 caches (PA_KV_Q8 / PA_KV_F32) ...
+  void* v_alt = nullptr;
+  float* k_scale = nullptr;      // ... with one f32 scale per 32 values (PA_KV_Q8)
+  float* v_scale = nullptr;
   CUtensorMap tm_k64, tm_v64;    // 64-row boxes over all sequences' rows, for the decode kernel
   const pa_layer* next = nullptr; // the layer the engine runs after this one (pa_layer_set_next): its first tiles are
                                   // requested into L2 while this layer's call drains

@@ -43,15 +43,87 @@ __device__ __forceinline__ void fma4(float4& acc, const float4& x, float w) {
   acc.x = __fmaf_rn(x.x, w, acc.x); acc.y = __fmaf_rn(x.y, w, acc.y); acc.z = __fmaf_rn(x.z, w, acc.z); acc.w = __fmaf_rn(x.w, w, acc.w);
 }
 
+// Cross-GPU step of a merge: publish this rank's merged slice (o of 64 dims by threads 0..63, m and l by thread 64) to
+// every rank, wait (bounded) for the other ranks' slices, merge them; t and Lsum come back as the merged sums.  Every
+// value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands whole, so the receiver
+// spins on the words themselves and no flag, fence or second round trip is needed.  The last of the call's
+// `total_units` slices to get through advances the call counter.  `sync`: a barrier of the calling threads.
+template <int HD, typename Sync>
+__device__ __forceinline__ void exchange_slice(const ExchangeView& x, uint32_t prow, uint32_t slice, int tid, float& t, float M, float& Lsum, uint32_t sweeps,
+                                               uint32_t* err, uint32_t total_units, volatile unsigned int* s_epoch, Sync&& sync) {
+  const uint32_t n_slices = HD / 64, d = slice * 64 + tid;
+  if (tid == 0) *s_epoch = *reinterpret_cast<volatile unsigned int*>(x.ctr);
+  sync();
+  const uint32_t epoch = *s_epoch, parity = epoch & 1u, tag = epoch + 1u;
+  const size_t blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // entries of 8 bytes: o rows, then (m, l) per (row, slice)
+  const size_t o_idx = (size_t)prow * HD + d;
+  const size_t ml_idx = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + slice) * 2;
+  auto put = [&](uint2* dst, float v) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+  };
+  for (uint32_t r = 0; r < x.world; ++r) {
+    uint2* dst = reinterpret_cast<uint2*>(x.peer[r]) + (size_t)(parity * x.world + x.rank) * blk;
+    if (tid < 64) put(dst + o_idx, t);
+    if (tid == 64) { put(dst + ml_idx, M); put(dst + ml_idx + 1, Lsum); }
+  }
+  if (tid < 64) {
+    // every sweep requests all entries still missing at once (m, l and this thread's o of every source rank) and
+    // keeps those that carry the call's tag; bounded
+    const uint2* mine = reinterpret_cast<const uint2*>(x.peer[x.rank]);
+    float mr[8], lr[8], orr[8];
+    uint32_t pending = (1u << x.world) - 1u;
+    for (uint32_t it = 0; it < sweeps && pending; ++it) {
+      uint32_t v[8][3], tg[8][3];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (!((pending >> r) & 1u)) continue;
+        const uint2* src = mine + (size_t)(parity * x.world + r) * blk;
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][0]), "=r"(tg[r][0]) : "l"(src + ml_idx) : "memory");
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][1]), "=r"(tg[r][1]) : "l"(src + ml_idx + 1) : "memory");
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][2]), "=r"(tg[r][2]) : "l"(src + o_idx) : "memory");
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (!((pending >> r) & 1u)) continue;
+        if (tg[r][0] == tag && tg[r][1] == tag && tg[r][2] == tag) {
+          mr[r] = __uint_as_float(v[r][0]); lr[r] = __uint_as_float(v[r][1]); orr[r] = __uint_as_float(v[r][2]);
+          pending &= ~(1u << r);
+        }
+      }
+      if (pending && it > 1024) __nanosleep(64);
+    }
+    if (pending) atomicMax(err, (uint32_t)WAIT_PEER);   // a peer never published: report and carry on
+    float Mg = -3.0e38f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) if ((uint32_t)r < x.world && !((pending >> r) & 1u)) Mg = fmaxf(Mg, mr[r]);
+    float Lg = 0.f, og = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if ((uint32_t)r >= x.world || ((pending >> r) & 1u)) continue;
+      const float w = __expf(mr[r] - Mg);
+      Lg += lr[r] * w;
+      og += orr[r] * w;
+    }
+    t = og; Lsum = Lg;
+  }
+  // the last slice of the call advances the call counter (every slice read it before any could get here last)
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(x.ctr + 1, 1u) == total_units - 1) { x.ctr[1] = 0; __threadfence(); atomicAdd(x.ctr, 1u); }
+  }
+}
+
 // LSE merge of the ns split records of one query row over one 64-dim slice, gate and store, by the 128 consumer threads
 // of a decode CTA: the arithmetic of pa_combine_kernel, operation for operation and in the same order (that kernel has
 // 256 threads; thread t here does the work of its threads t and t + 128), so a call gives the same bits whether its
 // records are merged here or there.  o_rec / ml_rec: record 0 of the row; records follow one another.  Scratch: 6 KB of
 // shared memory no one else uses any more.  bar: the group's named barrier.
-struct MergeScratch { float w[512]; float red[8]; float red2[8]; float4 acc[16][16]; };
+struct MergeScratch { float w[512]; float red[8]; float red2[8]; float4 acc[16][16]; unsigned int epoch; };
+struct MergeExchange { const ExchangeView* xc; uint32_t prow, sweeps, total_units; uint32_t* err; };   // xc == nullptr: one GPU
 template <int HD>
 __device__ __forceinline__ void merge_slice_128(const float* __restrict__ o_rec, const float* __restrict__ ml_rec, uint32_t ns, uint32_t slice, int t,
-                                                MergeScratch& sc, uint32_t bar, bool gated, float gv, bool empty_is_zero, int act_f16, void* out, uint64_t oo) {
+                                                MergeScratch& sc, uint32_t bar, bool gated, float gv, bool empty_is_zero, int act_f16, void* out, uint64_t oo,
+                                                const MergeExchange& mx) {
   const int wv = t >> 5, lane = t & 31, ln = t & 15, gA = t >> 4;
   // everything is requested before the first use: one memory round trip
   float mv[4], lv[4];
@@ -120,11 +192,16 @@ __device__ __forceinline__ void merge_slice_128(const float* __restrict__ o_rec,
   }
   sc.acc[gA][ln] = accA; sc.acc[gA + 8][ln] = accB;
   named_bar_sync(bar, kConsumers);
+  float tt = 0.f;
   if (t < 64) {
     const float* sa = reinterpret_cast<const float*>(sc.acc);
-    float tt = sa[t];
+    tt = sa[t];
 #pragma unroll
     for (int i = 1; i < 16; ++i) tt = __fadd_rn(tt, sa[i * 64 + t]);
+  }
+  if (mx.xc)   // a KV-sequence shard: the other ranks' slices are merged in before the division
+    exchange_slice<HD>(*mx.xc, mx.prow, slice, t, tt, M, Lsum, mx.sweeps, mx.err, mx.total_units, &sc.epoch, [&] { named_bar_sync(bar, kConsumers); });
+  if (t < 64) {
     float rv = (empty_is_zero && Lsum == 0.f) ? 0.f : __fdiv_rn(tt, Lsum);
     if (gated) rv = __fmul_rn(rv, __fdiv_rn(1.0f, __fadd_rn(1.0f, __expf(-gv))));
     if (act_f16) reinterpret_cast<__half*>(out)[oo + t] = __float2half_rn(rv);
@@ -143,7 +220,7 @@ struct DecSmem {
   static constexpr int PP = ROWS * 2;                // P^T row pitch (bytes)
   static constexpr int Q_BYTES = ROWS * QP * (PRECISE ? 2 : 1);
   static constexpr int P_BYTES = kT * PP * (PRECISE ? 2 : 1);      // per group
-  static constexpr int MISC = NG * 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 2048 + 1024;   // + the fused front's angles and new row
+  static constexpr int MISC = NG * 4 * ROWS * 4 * 2 + kMaxStages * 4 * 8 + 64 + 2048 + 1024 + 64;   // + the fused front's angles and new row, the slots' tile numbers
   static constexpr int fixed_bytes() { return Q_BYTES + NG * P_BYTES + MISC; }
   static int stages_for(int smem_limit) {
     int s = (smem_limit - 1024 - fixed_bytes()) / (2 * SLOT);
@@ -198,6 +275,10 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   Angle* s_ang = reinterpret_cast<Angle*>(bars + 4 * kMaxStages + 8);   // [64], fused front only
   uint32_t* s_newk = reinterpret_cast<uint32_t*>(s_ang + 64);           // the token's own K / V row as f16 pairs (fused front)
   uint32_t* s_newv = s_newk + 128;
+  // which tile each K slot [0..7] and V slot [8..15] holds or is being filled with.  With two consumer groups a slot
+  // serves the groups in turn, and a group may come for its tile before the other group's earlier tile has even landed
+  // there; a parity wait alone cannot tell "not yet" from "two phases on", the tile number can.
+  volatile uint32_t* s_tile = reinterpret_cast<volatile uint32_t*>(s_newv + 128);
 
   const uint32_t kfull = smem_u32(bars), kempty = kfull + kMaxStages * 8, vfull = kempty + kMaxStages * 8,
                  vempty = vfull + kMaxStages * 8;
@@ -275,6 +356,16 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
       for (int u = 0; u < RHALF / 32; ++u) reinterpret_cast<uint2*>(s_ang)[tid + u * kConsumers] = reinterpret_cast<const uint2*>(p.rope_ang)[tid + u * kConsumers];
     }
+    if (p.merge && p.gate && p.prefetch_old_rows && tid < 4) {
+      // the gate values of the (row, slice) unit this CTA will merge at the end: into L2 ahead of the K/V traffic
+      const uint32_t u = split, n_units = live_rows * (HD / 64);
+      if (u < n_units) {
+        const uint32_t row = u / (HD / 64), slice = u % (HD / 64), c = row / G, hh = row % G;
+        const uint64_t go = (uint64_t)(p.items.col0[item] + c) * p.gate_col_stride + (uint64_t)(g * G + hh) * p.gate_head_stride + slice * 64 + tid * 16;
+        const void* a = p.act_f16 ? (const void*)(reinterpret_cast<const __half*>(p.gate) + go) : (const void*)(reinterpret_cast<const float*>(p.gate) + go);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+      }
+    }
     if (Q_IN_REGS && p.prefetch_old_rows) {   // the CTA is ahead of its predecessor: bring the q lines to L2 meanwhile
       if (fused) {
 #pragma unroll
@@ -335,6 +426,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (lane == 0) {
       *s_err = 0;
       const uint32_t full_count = g_list ? 32u : 1u;   // a TMA tile completes by bytes; a gathered one by its 32 lanes' copies
+      for (uint32_t s = 0; s < 16; ++s) s_tile[s] = 0xffffffffu;
       for (uint32_t s = 0; s < NS; ++s) {
         mbar_init(kfull + 8 * s, full_count);
         mbar_init(vfull + 8 * s, full_count);
@@ -381,7 +473,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           const uint32_t full = (which ? vfull : kfull) + 8 * s, empty = (which ? vempty : kempty) + 8 * s;
-          if (lane == 0) mbar_wait(empty, ph ^ 1, s_err, WAIT_EMPTY);
+          if (lane == 0) { mbar_wait(empty, ph ^ 1, s_err, WAIT_EMPTY); s_tile[which * 8 + s] = i; }
           __syncwarp();
           const __half* cache = which ? p.v_cache : p.k_cache;
           const uint32_t dst0 = smem_u32((which ? v_slots : k_slots) + s * SLOT);
@@ -400,6 +492,15 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     } else
     for (uint32_t i = 0; i < n_tiles; ++i) {
       if (i == pre) {
+        if (lane == 0 && p.prefetch_old_rows && p.own_prefetch) {
+          // The first tiles are on their way into the ring; the CTA's other tiles of rows nobody can be writing are
+          // asked into L2 now, while the predecessor kernel drains and this one waits for it: HBM works through the
+          // kernel boundary, and the loads that refill the ring later find their tiles in L2.
+          for (uint32_t k = pre; k < n_tiles && (tile0 + k + 1) * kT <= old_rows; ++k) {
+            tma_prefetch_3d(&tm_k, 0, y0 + (int)(k * kT), z);
+            tma_prefetch_3d(&tm_v, 0, y0 + (int)(k * kT), z);
+          }
+        }
         __syncwarp();
         named_bar_sync(3, kDecThreads);
         if (!p.prefetch_old_rows && lane == 0) pdl_wait();
@@ -408,9 +509,11 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         const uint32_t s = i % NS, ph = (i / NS) & 1;
         if (!waited && (tile0 + i + 1) * kT > old_rows) { pdl_wait(); waited = true; }
         mbar_wait(kempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
+        s_tile[s] = i;
         mbar_expect_tx(kfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s);
         mbar_wait(vempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
+        s_tile[8 + s] = i;
         mbar_expect_tx(vfull + 8 * s, SLOT);
         tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
       }
@@ -536,7 +639,27 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   named_bar_sync(5, CONS);   // q (and the token's own row) visible to both groups
 
   const uint32_t q_hi_s = smem_u32(q_hi), q_lo_s = smem_u32(q_lo), p_hi_s = smem_u32(p_hi), p_lo_s = smem_u32(p_lo);
+  // the slot is this group's turn once the producer has put the tile's number on it (bounded like every wait)
+  auto wait_tile = [&](uint32_t word, uint32_t i) {
+    if (NG == 1) return;
+    for (uint32_t k = 0; s_tile[word] != i && !*s_err; ++k) {
+      if (k > kWaitPolls) { *s_err = WAIT_KFULL; break; }
+      if (k > 16) __nanosleep(32);
+    }
+  };
 
+  // With one 8-row group the query fragments of all k-steps (hi and lo: HD/4 registers) stay in registers for the
+  // CTA's life: re-reading them from shared memory for every tile was half of the score product's fragment loads.
+  constexpr bool Q_FRAGS = NT == 1;
+  uint32_t qfh[Q_FRAGS ? HD / 32 : 1][4], qfl[Q_FRAGS ? HD / 32 : 1][4];
+  if constexpr (Q_FRAGS) {
+#pragma unroll
+    for (int k2 = 0; k2 < HD / 32; ++k2) {
+      const uint32_t qoff = (lane & 7) * QP + (4 * k2 + (lane >> 3)) * 16;
+      ldsm_x4(q_hi_s + qoff, qfh[k2][0], qfh[k2][1], qfh[k2][2], qfh[k2][3]);
+      if (PRECISE) ldsm_x4(q_lo_s + qoff, qfl[k2][0], qfl[k2][1], qfl[k2][2], qfl[k2][3]);
+    }
+  }
   for (uint32_t i = grp; i < n_tiles; i += NG) {
     const uint32_t s = i % NS, ph = (i / NS) & 1;
     const uint32_t tile_pos = (tile0 + i) * kT;
@@ -553,6 +676,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
       for (int a = 0; a < NA - 1; ++a) sacc_x[nt][a][0] = sacc_x[nt][a][1] = sacc_x[nt][a][2] = sacc_x[nt][a][3] = 0.f;
     }
+    wait_tile(s, i);
     mbar_wait(kfull + 8 * s, ph, s_err, WAIT_KFULL);
     if (own_new && i == n_tiles - 1) {
       const uint32_t rr = n_rows - 1 - tile_pos;
@@ -576,11 +700,13 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           const uint32_t addr = ks_base + (c16g >> 3) * (kT * 128) + krow * 128 + (((c16g & 7) ^ (krow & 7)) << 4);
           ldsm_x4(addr, a[buf][e][0], a[buf][e][1], a[buf][e][2], a[buf][e][3]);
         }
+        if constexpr (!Q_FRAGS) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint32_t qoff = (nt * 8 + (lane & 7)) * QP + (4 * k2 + (lane >> 3)) * 16;
-          ldsm_x4(q_hi_s + qoff, bh[buf][nt][0], bh[buf][nt][1], bh[buf][nt][2], bh[buf][nt][3]);
-          if (PRECISE) ldsm_x4(q_lo_s + qoff, bl[buf][nt][0], bl[buf][nt][1], bl[buf][nt][2], bl[buf][nt][3]);
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t qoff = (nt * 8 + (lane & 7)) * QP + (4 * k2 + (lane >> 3)) * 16;
+            ldsm_x4(q_hi_s + qoff, bh[buf][nt][0], bh[buf][nt][1], bh[buf][nt][2], bh[buf][nt][3]);
+            if (PRECISE) ldsm_x4(q_lo_s + qoff, bl[buf][nt][0], bl[buf][nt][1], bl[buf][nt][2], bl[buf][nt][3]);
+          }
         }
       };
       load_step(0, 0);
@@ -590,12 +716,14 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         if (k2 + 1 < HD / 32) load_step(k2 + 1, cur ^ 1);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          mma_16816(sacc[nt], a[cur][0][0], a[cur][0][1], a[cur][0][2], a[cur][0][3], bh[cur][nt][0], bh[cur][nt][1]);
-          mma_16816(NA >= 2 ? sacc_x[nt][0] : sacc[nt], a[cur][1][0], a[cur][1][1], a[cur][1][2], a[cur][1][3], bh[cur][nt][2], bh[cur][nt][3]);
+          const uint32_t* qh = Q_FRAGS ? qfh[k2] : bh[cur][nt];
+          const uint32_t* ql = Q_FRAGS ? qfl[k2] : bl[cur][nt];
+          mma_16816(sacc[nt], a[cur][0][0], a[cur][0][1], a[cur][0][2], a[cur][0][3], qh[0], qh[1]);
+          mma_16816(NA >= 2 ? sacc_x[nt][0] : sacc[nt], a[cur][1][0], a[cur][1][1], a[cur][1][2], a[cur][1][3], qh[2], qh[3]);
           if (PRECISE) {
-            mma_16816(NA >= 4 ? sacc_x[nt][1] : sacc[nt], a[cur][0][0], a[cur][0][1], a[cur][0][2], a[cur][0][3], bl[cur][nt][0], bl[cur][nt][1]);
+            mma_16816(NA >= 4 ? sacc_x[nt][1] : sacc[nt], a[cur][0][0], a[cur][0][1], a[cur][0][2], a[cur][0][3], ql[0], ql[1]);
             mma_16816(NA >= 4 ? sacc_x[nt][2] : (NA >= 2 ? sacc_x[nt][0] : sacc[nt]), a[cur][1][0], a[cur][1][1], a[cur][1][2], a[cur][1][3],
-                      bl[cur][nt][2], bl[cur][nt][3]);
+                      ql[2], ql[3]);
           }
         }
       }
@@ -693,6 +821,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         oacc[mt][nt][2] *= alpha[nt][0]; oacc[mt][nt][3] *= alpha[nt][1];
       }
 
+    wait_tile(8 + s, i);
     mbar_wait(vfull + 8 * s, ph, s_err, WAIT_VFULL);
     if (own_new && i == n_tiles - 1 && ltid < HD / 2) {   // made visible by the barrier below
       const uint32_t rr = n_rows - 1 - tile_pos, c16g = ltid >> 2;
@@ -787,29 +916,66 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       if (r == 0) s_l[w * ROWS + nt * 8 + 2 * j + e] = l;
     }
   named_bar_sync(gbar, kConsumers);
-  // one record per (split, group): the group's share of the split's tiles (possibly none: m = -3e38, l = 0, o = 0)
+  // ---- one record per (row, split).  The rows' o go through shared memory (the ring is idle now) so that the record
+  //      stores are whole 16-byte vectors of consecutive addresses; with two groups, the second leaves its (o, m, l)
+  //      there and the first folds it into its own: o = o0 2^(m0 - M) + o1 2^(m1 - M), likewise l ----
+  float* xo = reinterpret_cast<float*>(k_slots);       // [ROWS][HD]
+  float* xml = xo + ROWS * HD;                         // [ROWS][2]: m (log2 units), l as the second group leaves them
+  float* xml_out = xml + 2 * ROWS;                     // [ROWS][2]: the record's m and l
+  float l_row[NT][2];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const uint32_t row = nt * 8 + 2 * j + e;
-      if (row >= live_rows) continue;
-      const uint32_t c = row / G, hh = row % G;
-      const uint64_t prow = (uint64_t)(p.items.col0[item] + c) * p.n_heads + g * G + hh;
-      const uint64_t slot = (prow * p.n_splits + split) * NG + grp;
-      float* po = p.part_o + slot * HD;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const int d = (w * MT + mt) * 16 + r;
-        po[d] = oacc[mt][nt][e];
-        po[d + 8] = oacc[mt][nt][2 + e];
-      }
-      if (w == 0 && r == 0) {
-        const float l = (s_l[row] + s_l[ROWS + row]) + (s_l[2 * ROWS + row] + s_l[3 * ROWS + row]);
-        p.part_ml[slot * 2] = m_run[nt][e] * 0.6931471805599453f;
-        p.part_ml[slot * 2 + 1] = l;
-      }
+      l_row[nt][e] = (s_l[row] + s_l[ROWS + row]) + (s_l[2 * ROWS + row] + s_l[3 * ROWS + row]);
     }
+  auto put_rows = [&](bool fold, float* ml_dst) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const uint32_t row = nt * 8 + 2 * j + e;
+        float w0 = 1.f, w1 = 0.f, M = m_run[nt][e];
+        if (fold) {
+          const float m1 = xml[row * 2];
+          M = fmaxf(M, m1);
+          w0 = exp2f(m_run[nt][e] - M); w1 = exp2f(m1 - M);
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const int d = (w * MT + mt) * 16 + r;
+          float a = oacc[mt][nt][e], b = oacc[mt][nt][2 + e];
+          if (fold) { a = a * w0 + xo[row * HD + d] * w1; b = b * w0 + xo[row * HD + d + 8] * w1; }
+          xo[row * HD + d] = a; xo[row * HD + d + 8] = b;
+        }
+        if (w == 0 && r == 0) {
+          const float l = fold ? l_row[nt][e] * w0 + xml[row * 2 + 1] * w1 : l_row[nt][e];
+          ml_dst[row * 2] = M; ml_dst[row * 2 + 1] = l;
+        }
+      }
+  };
+  if constexpr (NG == 2) {
+    named_bar_sync(5, CONS);                 // both groups are past their last tile: nobody reads the ring any more
+    if (grp == 1) put_rows(false, xml);
+    named_bar_sync(5, CONS);
+    if (grp == 1) return;                    // the first group carries on alone
+    put_rows(true, xml_out);
+  } else {
+    put_rows(false, xml_out);
+  }
+  named_bar_sync(gbar, kConsumers);
+  for (uint32_t idx = ltid; idx < live_rows * (HD / 4); idx += kConsumers) {
+    const uint32_t row = idx / (HD / 4), c4 = idx % (HD / 4);
+    const uint32_t c = row / G, hh = row % G;
+    const uint64_t prow = (uint64_t)(p.items.col0[item] + c) * p.n_heads + g * G + hh;
+    const uint64_t slot = prow * p.n_splits + split;
+    reinterpret_cast<float4*>(p.part_o + slot * HD)[c4] = reinterpret_cast<const float4*>(xo + row * HD)[c4];
+    if (c4 == 0) {
+      p.part_ml[slot * 2] = xml_out[row * 2] * 0.6931471805599453f;
+      p.part_ml[slot * 2 + 1] = xml_out[row * 2 + 1];
+    }
+  }
   if constexpr (NT <= 2) if (p.merge) {
     // ---- one kernel per call: when every CTA of this (item, kv head) has left its record, the CTAs share out the
     //      merge: (query row, 64-dim slice) units, dealt round-robin; LSE merge, gate and store as pa_combine_kernel does.
@@ -854,8 +1020,9 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         uint64_t prow, go, oo; uint32_t slice;
         unit_addr(u, prow, slice, go, oo);
         const float gv = (u == split) ? gv0 : ((gated && ltid < 64) ? gate_ld(go) : 0.f);
-        const uint64_t rec0 = prow * p.n_splits * NG;
-        merge_slice_128<HD>(p.part_o + rec0 * HD, p.part_ml + rec0 * 2, ns_live * NG, slice, ltid, sc, gbar, gated, gv, p.gather != nullptr, p.act_f16, p.out, oo);
+        const uint64_t rec0 = prow * p.n_splits;
+        const MergeExchange mx{p.exchange ? &p.xc : nullptr, (uint32_t)prow, p.xch_sweeps, p.xch_units, p.err};
+        merge_slice_128<HD>(p.part_o + rec0 * HD, p.part_ml + rec0 * 2, ns_live, slice, ltid, sc, gbar, gated, gv, p.gather != nullptr, p.act_f16, p.out, oo, mx);
       }
     }
     // the last CTA to finish clears the counters for the next call (every other CTA is past its wait by then)
@@ -962,70 +1129,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     for (int i = 1; i < 16; ++i) t = __fadd_rn(t, sa[i * 64 + tid]);
   }
   if constexpr (XCH) {
-    // ---- publish this rank's record slice to every rank, wait for theirs, merge across ranks ----
-    // Every value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands whole, so
-    // the receiver spins on the words themselves and no flag, fence or second round trip is needed.
-    const ExchangeView& x = p.xc;
-    const uint32_t n_slices = HD / 64;
-    if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(x.ctr);
-    __syncthreads();
-    const uint32_t epoch = s_epoch, parity = epoch & 1u, tag = epoch + 1u;
-    const size_t blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // entries of 8 bytes: o rows, then (m, l) per (row, slice)
-    const size_t o_idx = (size_t)prow * HD + d;
-    const size_t ml_idx = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + slice) * 2;
-    auto put = [&](uint2* dst, float v) {
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-    };
-    for (uint32_t r = 0; r < x.world; ++r) {
-      uint2* dst = reinterpret_cast<uint2*>(x.peer[r]) + (size_t)(parity * x.world + x.rank) * blk;
-      if (tid < 64) put(dst + o_idx, t);
-      if (tid == 64) { put(dst + ml_idx, M); put(dst + ml_idx + 1, Lsum); }
-    }
-    if (tid < 64) {
-      // every sweep requests all entries still missing at once (m, l and this thread's o of every source rank) and
-      // keeps those that carry the call's tag; bounded
-      const uint2* mine = reinterpret_cast<const uint2*>(x.peer[x.rank]);
-      float mr[8], lr[8], orr[8];
-      uint32_t pending = (1u << x.world) - 1u;
-      for (uint32_t it = 0; it < p.xch_sweeps && pending; ++it) {
-        uint32_t v[8][3], tg[8][3];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (!((pending >> r) & 1u)) continue;
-          const uint2* src = mine + (size_t)(parity * x.world + r) * blk;
-          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][0]), "=r"(tg[r][0]) : "l"(src + ml_idx) : "memory");
-          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][1]), "=r"(tg[r][1]) : "l"(src + ml_idx + 1) : "memory");
-          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][2]), "=r"(tg[r][2]) : "l"(src + o_idx) : "memory");
-        }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (!((pending >> r) & 1u)) continue;
-          if (tg[r][0] == tag && tg[r][1] == tag && tg[r][2] == tag) {
-            mr[r] = __uint_as_float(v[r][0]); lr[r] = __uint_as_float(v[r][1]); orr[r] = __uint_as_float(v[r][2]);
-            pending &= ~(1u << r);
-          }
-        }
-        if (pending && it > 1024) __nanosleep(64);
-      }
-      if (pending) atomicMax(p.err, 7u);   // a peer never published: report and carry on
-      float Mg = -3.0e38f;
-#pragma unroll
-      for (int r = 0; r < 8; ++r) if ((uint32_t)r < x.world && !((pending >> r) & 1u)) Mg = fmaxf(Mg, mr[r]);
-      float Lg = 0.f, og = 0.f;
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if ((uint32_t)r >= x.world || ((pending >> r) & 1u)) continue;
-        const float w = __expf(mr[r] - Mg);
-        Lg += lr[r] * w;
-        og += orr[r] * w;
-      }
-      t = og; Lsum = Lg;
-    }
-    // the last CTA of the launch advances the call counter (every CTA read it before any CTA could get here last)
-    if (tid == 0) {
-      __threadfence();
-      if (atomicAdd(x.ctr + 1, 1u) == gridDim.x * gridDim.y - 1) { x.ctr[1] = 0; __threadfence(); atomicAdd(x.ctr, 1u); }
-    }
+    exchange_slice<HD>(p.xc, prow, slice, tid, t, M, Lsum, p.xch_sweeps, p.err, gridDim.x * gridDim.y, &s_epoch, [] { __syncthreads(); });
   }
   if (tid < 64) {
     if (p.partial_out) {

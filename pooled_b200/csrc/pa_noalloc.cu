@@ -82,7 +82,7 @@ extern "C" PA_API int pa_decode_static(int device, const void* k_cache, const vo
     return say(msg, msg_len, PA_EUNSUPPORTED, "pa_decode_static: n_cols * (n_heads / n_kv_heads) must be between 1 and 64");
   if ((uint64_t)pos + n_cols > cache_rows || cache_rows >= (1u << 31)) return say(msg, msg_len, PA_EINVAL, "pa_decode_static: pos + n_cols passes cache_rows");
   const int nt = (int)((n_cols * G + 7) / 8);
-  const uint32_t groups = (uint32_t)decode_groups(nt);   // the decode kernel leaves one record per (row, split, consumer group)
+  const uint32_t groups = 1;   // the decode kernel leaves one record per (row, split)
   const uint32_t rows = n_cols * n_heads;
   if (rows * groups > PA_STATIC_RECORDS) {
     char b[160];

@@ -25,6 +25,7 @@ struct DecodeParams {
   // the layer the engine runs next (pa_layer_set_next): once a CTA has requested its own last tile it asks L2 for the
   // first next_tiles tiles of the same split of that layer, so HBM keeps working across the kernel boundary
   uint32_t next_tiles, next_max_seq;
+  uint32_t own_prefetch;       // 1: with prefetch_old_rows, the CTA's tiles beyond the ring are asked into L2 at entry
   // gather mode: item i is one column attending the rows listed at gather + col0[i] * gather_stride: [0] = n, then n
   // cache rows ascending (k_cache / v_cache above are the layer's caches)
   const uint32_t* gather; uint32_t gather_stride;
@@ -32,6 +33,9 @@ struct DecodeParams {
   uint32_t merge; unsigned int* merge_ctr;
   const void* gate; uint64_t gate_col_stride, gate_head_stride;
   void* out; uint64_t out_col_stride; int act_f16;
+  // ... and, on a KV-sequence shard, exchange their merged slices with the other ranks before the division
+  uint32_t exchange, xch_sweeps, xch_units;   // xch_units: (row, slice) units of the whole call
+  ExchangeView xc;
   uint32_t* err;
   ItemList items;
 };
@@ -98,6 +102,25 @@ struct HeadNormParams {
 struct SigmoidParams {
   void* a; uint64_t a_col_stride; const void* g; uint64_t g_col_stride, g_head_stride;
   uint32_t n_heads, hd; int f16;
+};
+
+// append into an int8 (+ scales) or f32 cache: k and v rows of n columns, already rotated
+struct KvStoreParams {
+  int format;                                   // PA_KV_Q8 or PA_KV_F32
+  const void* k; const void* v; uint64_t k_col_stride, v_col_stride; int k_f16, v_f16;
+  int8_t* k8; int8_t* v8; float* ks; float* vs;  // int8 caches and their scales (one per 32 values)
+  float* k32; float* v32;                        // f32 caches
+  uint32_t kv_dim; uint64_t cache_row0;          // cache row of column 0
+};
+
+// split-K decode / verify / prefill of the columns of one item over an int8 or f32 cache
+struct AnyDecodeParams {
+  const void* q; int q_f16; uint64_t q_col_stride, q_head_stride;
+  const void* k; const void* v; const float* ks; const float* vs;
+  uint32_t kv_dim, hd, G, n_heads, max_seq, n_splits;
+  uint32_t seq; int32_t lim0; uint32_t n_rows;   // rows column 0 sees (before clamping), rows the last column sees
+  uint64_t col0;                                 // first column of the item in q and in the record buffers
+  float* part_o; float* part_ml;
 };
 
 struct PrefillParams {

@@ -6,11 +6,13 @@
 // the same time; the caches of a prefill fit the 126 MB L2, so HBM sees them once.
 //
 //   warps 0, 3  TMA producers: K tiles and V tiles (64 x head_dim f16, 128-byte swizzle), a three-slot ring each
-//   warp 1      MMA issuer (one thread): S = Q K^T into a double-buffered TMEM tile (128 x 64 f32), then
-//               O += P V into the TMEM accumulator (128 x head_dim f32).  Both A operands come from tensor memory
-//               (Q sits there for the CTA's life, P is written over its own S tile), so shared-memory bandwidth
-//               carries the K / V slices only; completion is signalled to mbarriers with tcgen05.commit
-//   warp 2      allocates / frees tensor memory
+//   warp 1      MMA issuer (one thread) of the scores: S = Q K^T into one of three TMEM tiles (128 x 64 f32)
+//   warp 2      allocates / frees tensor memory, and in between is the MMA issuer of O += P V into the TMEM
+//               accumulator (128 x head_dim f32).  Both A operands come from tensor memory (Q sits there for the
+//               CTA's life, P is written over its own S tile), so shared-memory bandwidth carries the K / V slices
+//               only; completion is signalled to mbarriers with tcgen05.commit.  Two issuers: issuing blocks while
+//               the tensor cores' queue is full, and a single thread alternating between the two products left it
+//               empty during every wait
 //   warps 4-7   softmax: thread r owns query row r (TMEM lane r): stores its Q row into TMEM as f16 pairs, then per
 //   (and 8-11)  tile tcgen05.ld of its S row, causal mask, running max / sum, P = 2^(s - m) as f16 pairs back into
 //               TMEM (tcgen05.st), and the epilogue (O / l, sigmoid gate, store).  The causal prefill runs two such
@@ -181,8 +183,9 @@ struct PfSmem {
   static constexpr int NGRP = MODE == 0 ? 2 : 1;
   static constexpr int THREADS = 128 + 128 * NGRP;   // 4 service warps (K producer, MMA, TMEM, V producer) + the softmax warps
   static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
-  static constexpr int OFF_ROW = OFF_BAR + 256;      // per-row hand-over between the softmax groups: m[128], l[2][128], l's reference[2][128]
-  static constexpr int TOTAL = 1024 + OFF_ROW + 5 * 128 * 4;
+  static constexpr int OFF_ROW = OFF_BAR + 256;      // per-row hand-over between the softmax groups: the reference maximum, m[128]
+  static constexpr int TOTAL = 1024 + OFF_ROW + 128 * 4;
+  static_assert(TOTAL <= 227 * 1024, "shared memory of one CTA");
   // tensor memory columns: the first TQC 64-dim chunks of Q (32 columns of f16 pairs each: half of the row, all of it
   // at head_dim 64) | S0 S1 S2 (64 each; P overwrites the first 32 of its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
   static constexpr int TQC = HD == 64 ? 1 : HD / 128;
@@ -203,8 +206,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 28);
   volatile uint32_t* s_err = s_tmem + 1;
   float* s_rm = reinterpret_cast<float*>(base + L::OFF_ROW);   // [128] reference maximum of each query row (scaled, log2 units)
-  float* s_rl = s_rm + 128;                                    // [2][128] each group's row sum ...
-  float* s_rr = s_rl + 256;                                    // [2][128] ... and the reference maximum it is expressed in
+  // [2][128] each group's row sum and [2][128] the reference maximum it is expressed in: exchanged once, after the
+  // last tile's scores exist, in the first K slot (every K tile has been multiplied by then)
+  float* s_rl = reinterpret_cast<float*>(base + L::OFF_K);
+  float* s_rr = s_rl + 256;
   const uint32_t bar0 = smem_u32(bars);
   enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23, Q_SENT = 24,
          M_READY = 25 /* [2]: group g has published the row maxima after its tile */ };
@@ -287,22 +292,26 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer ----
+    // ------------------------------------------------------------------ MMA issuer, scores ----
+    // S(j) = Q K(j)^T.  The whole warp runs the loop and the elected lane issues.  Issuing blocks while the tensor
+    // cores' queue is full, so one thread issuing both products of every tile spends its time in turns on each and
+    // the waits in between leave the queue empty; with the scores here and P V in warp 2 there are two queues' worth
+    // of work in front of the tensor cores.  S(j) goes into the TMEM tile of S(j - 3) / P(j - 3): once that P V has
+    // retired (PV_DONE).
     {
       const uint32_t leader = elect_one();
-      constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0), idesc_pv = umma_idesc(kBM, HD, 1);
+      constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, 0);
       // Both A operands live in tensor memory (Q for the whole CTA, P per tile), so a k-step costs shared-memory
       // bandwidth for the K or V slice only.  B descriptors are built once; a k-step adds a byte offset (>> 4).
-      uint64_t k_desc[NK], v_desc[NV];
+      uint64_t k_desc[NK];
 #pragma unroll
       for (int i = 0; i < NK; ++i) k_desc[i] = smem_desc(smem_u32(base + L::OFF_K + i * L::KV_BYTES), 16, 1024);
-#pragma unroll
-      for (int i = 0; i < NV; ++i) v_desc[i] = smem_desc(smem_u32(base + L::OFF_V + i * L::KV_BYTES), kBN * 128, 1024);
       const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
       mbar_wait(BAR(Q_FULL, 0), 0, s_err, WAIT_QFULL);
       tc_fence_after();
-      auto issue_qk = [&](uint32_t j) {
+      for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t sb = j % kSBuf, st = j % NK;
+        if (j >= (uint32_t)kSBuf) mbar_wait(BAR(PV_DONE, sb), ((j - kSBuf) / kSBuf) & 1, s_err, WAIT_MMA);
         mbar_wait(BAR(K_FULL, st), (j / NK) & 1, s_err, WAIT_KFULL);
         tc_fence_after();
         const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[NK - 1]);
@@ -318,15 +327,19 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                       kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, 1u);
         umma_commit_elected(leader, BAR(K_EMPTY, st));
         umma_commit_elected(leader, BAR(S_FULL, sb));
-      };
-      // The scores run two tiles ahead of the weights: S(j+2) is issued before P V (j), so the softmax of tile j+1
-      // never waits behind the P V of tile j-1.  S(j+2) reuses the TMEM tile of S(j-1) / P(j-1); P V (j-1) was issued
-      // earlier and one thread's MMAs retire in order.
-      issue_qk(0);
-      if (n_tiles > 1) issue_qk(1);
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ MMA issuer, P V ----
+    // O += P(j) V(j), in tile order (this thread's products retire in order, so O is always complete up to a tile)
+    {
+      const uint32_t leader = elect_one();
+      constexpr uint32_t idesc_pv = umma_idesc(kBM, HD, 1);
+      uint64_t v_desc[NV];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v_desc[i] = smem_desc(smem_u32(base + L::OFF_V + i * L::KV_BYTES), kBN * 128, 1024);
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t sb = j % kSBuf, st = j % NV;
-        if (j + 2 < n_tiles) issue_qk(j + 2);
         mbar_wait(BAR(P_FULL, sb), (j / kSBuf) & 1, s_err, WAIT_QFULL);
         mbar_wait(BAR(V_FULL, st), (j / NV) & 1, s_err, WAIT_VFULL);
         tc_fence_after();
@@ -529,9 +542,9 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ---- epilogue: O / l, gate, store ----
     if (NGRP == 2) {
       // the row sum is the two groups' shares brought to the final reference; O already is in it
-      s_rl[wg * 128 + row] = l_sum; s_rr[wg * 128 + row] = m_l;
       const uint32_t last = n_tiles - 1;
-      mbar_wait(BAR(M_READY, last & 1), (last >> 1) & 1, s_err, WAIT_MMA);
+      mbar_wait(BAR(M_READY, last & 1), (last >> 1) & 1, s_err, WAIT_MMA);   // published after S(last) was complete: the K ring is idle
+      s_rl[wg * 128 + row] = l_sum; s_rr[wg * 128 + row] = m_l;
       named_bar_sync(2, 128 * NGRP);
       const float m_fin = s_rm[row];
       l_sum = s_rl[row] * ex2_approx(s_rr[row] - m_fin) + s_rl[128 + row] * ex2_approx(s_rr[128 + row] - m_fin);
@@ -546,6 +559,14 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       const uint64_t prow = (uint64_t)(p.col0 + sk_c) * p.n_heads + head;
       const uint64_t slot = prow * p.n_splits + blockIdx.x;
       const bool writer = live && !is_lo;
+      // A lane holds a row: stored as they are, the 32 lanes of an instruction would write 16 bytes each into 32
+      // records 1 KB apart.  The rows go to shared memory first (the K ring is idle: every product has retired; rows
+      // 16 bytes apart in their bank phase), then all 128 threads write whole records, 16 consecutive bytes per
+      // thread and 512 consecutive bytes per warp instruction.
+      constexpr int RP = HD / 4 + 1;                                  // row pitch in float4
+      float4* xs = reinterpret_cast<float4*>(base + L::OFF_K);        // [rows][RP]
+      unsigned long long* xslot = reinterpret_cast<unsigned long long*>(xs + 64 * RP);   // [64] record of each row, ~0: none
+      if (!is_lo && lr < 64) xslot[lr] = writer ? (unsigned long long)slot : ~0ull;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         float o[32];
@@ -555,10 +576,15 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           for (int i = 0; i < 32; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], 1);
         }
         if (writer) {
-          float4* dst = reinterpret_cast<float4*>(p.part_o + slot * HD + c * 32);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          for (int i = 0; i < 8; ++i) xs[lr * RP + c * 8 + i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
+      }
+      named_bar_sync(1, 128);
+      for (uint32_t idx = tid - 128; idx < 64 * (HD / 4); idx += 128) {
+        const uint32_t rr = idx / (HD / 4), c4 = idx % (HD / 4);
+        const unsigned long long sl = xslot[rr];
+        if (sl != ~0ull) reinterpret_cast<float4*>(p.part_o + sl * HD)[c4] = xs[rr * RP + c4];
       }
       if (writer) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
     } else {

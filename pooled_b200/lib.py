@@ -9,6 +9,7 @@ SO_PATH = os.path.join(HERE, "libpooled_attn.so")
 
 PA_F32, PA_F16 = 0, 1
 PA_ROPE_NONE, PA_ROPE_F64, PA_ROPE_TABLE = 0, 1, 2
+PA_KV_F16, PA_KV_Q8, PA_KV_F32 = 0, 1, 2
 PA_FLAG_FAST = 1
 PA_MODE_AUTO, PA_MODE_DECODE, PA_MODE_PREFILL = 0, 1, 2
 STATUS = {0: "PA_OK", -1: "PA_EINVAL", -2: "PA_EUNSUPPORTED", -3: "PA_ENOMEM", -4: "PA_ECUDA", -5: "PA_ETIMEOUT", -6: "PA_ESTATE"}
@@ -40,6 +41,7 @@ SYMBOLS = {
     "pa_create": (_i, [_i, C.POINTER(PaConfig), C.POINTER(_vp)]),
     "pa_destroy": (_i, [_vp]),
     "pa_layer_create": (_i, [_vp, _u32, _u32, C.POINTER(_vp)]),
+    "pa_layer_create_fmt": (_i, [_vp, _u32, _u32, _i, C.POINTER(_vp)]),
     "pa_layer_destroy": (_i, [_vp]),
     "pa_layer_set_origin": (_i, [_vp, _u32]),
     "pa_layer_set_next": (_i, [_vp, _vp]),

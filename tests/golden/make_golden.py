@@ -66,6 +66,15 @@ def main():
                         shape=np.array([nH, nKV, hd, rows, nc, n_rot, pos0]), theta=np.array([theta]), K=K, V=V, q=q, g=g, out=out, out_gated=out_gated,
                         rope_in=rope_in, rope_out=rope_out, rope_full=rope_full)
 
+    # the "next" rows of the path: int8 KV (kv_store_q8, NumPy twin) and gathered attention (exact attention over listed rows)
+    x = (po.normal(201, 24 * 256) * 2.0).astype(np.float32).reshape(24, 256)
+    x[1, :32] = 0.0; x[2, 40] = 900.0; x[3, :32] = np.arange(32) - 15.5
+    q8, q8_scales = po.np_kv_store_q8(x)
+    listed = np.array([0, 3, 4, 17, 40, 41, 69], dtype=np.int32)
+    out_listed = po.np_attn_f64(q[:1], K[listed], V[listed], nH, nKV, hd, len(listed) - 1, 1)
+    np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "kvfmt_golden.npz"),
+                        x=x, q8=q8, q8_scales=q8_scales, listed=listed, out_listed=out_listed)
+
 
 if __name__ == "__main__":
     main()

@@ -9,6 +9,16 @@ from oracle import po
 from tests import util
 
 G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attn_golden.npz"))
+G2 = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kvfmt_golden.npz"))
+
+
+def test_oracle_q8_and_listed_rows_vectors():
+    q, sc = po.kv_store_q8(G2["x"])
+    assert np.array_equal(q, G2["q8"]) and np.array_equal(sc.view(np.uint32), G2["q8_scales"].view(np.uint32))
+    nH, nKV, hd = (int(x) for x in G["shape"][:3])
+    rows = G2["listed"]
+    got = po.attn_f64(G["q"][:1], G["K"][rows], G["V"][rows], nH, nKV, hd, len(rows) - 1, 1)
+    assert np.max(np.abs(got - G2["out_listed"])) < 1e-12
 
 
 def test_oracle_f16_and_lcg_vectors():
@@ -49,3 +59,22 @@ def test_library_reproduces_the_vectors():
     eng.kv_append(0, 0, 100, util.torch_dev(x), util.torch_dev(x))
     eng.sync()
     assert np.array_equal(util.read_cache(eng, 0, 0, 100, 1)[0][0, :n], G["f16_rne"][:n])
+
+
+@pytest.mark.gpu
+def test_library_reproduces_the_q8_and_listed_rows_vectors():
+    import torch
+    from pooled_b200 import AttnConfig, AttnEngine
+    nH, nKV, hd, rows, nc, n_rot, pos0 = (int(x) for x in G["shape"])
+    e8 = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=n_rot, rope_theta=1e7, max_seq=64, rope_mode="none", act_dtype=torch.float32,
+                               max_cols=32, kv_format="q8"))
+    x = util.torch_dev(G2["x"])
+    e8.kv_append(0, 0, 5, x, x)
+    e8.sync()
+    assert np.array_equal(e8.cache(0, "k")[0, 5:29].cpu().numpy(), G2["q8"])
+    assert np.array_equal(e8.cache_scales(0, "v")[0, 5:29].cpu().numpy().view(np.uint32), G2["q8_scales"].view(np.uint32))
+    eng = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=n_rot, rope_theta=1e7, max_seq=128, rope_mode="none", act_dtype=torch.float32, max_cols=8))
+    util.load_cache(eng, 0, 0, G["K"], G["V"])
+    lists = np.zeros((1, 16), dtype=np.int32); lists[0, 0] = len(G2["listed"]); lists[0, 1:1 + len(G2["listed"])] = G2["listed"]
+    got = eng.decode_gather(0, torch.from_numpy(lists).cuda(), util.torch_dev(G["q"][:1])).cpu().numpy()
+    assert util.errs(got, G2["out_listed"])[1] < util.REF_REL

@@ -178,3 +178,24 @@ def test_head_norm_c_and_numpy_twins_agree_and_normalise():
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
         u = po.head_norm_f64(x, heads, hd, np.ones(hd, np.float32), 1e-6).reshape(heads, hd).astype(np.float64)
         assert np.allclose((u * u).mean(axis=1), 1.0, atol=1e-5)
+
+
+def test_kv_store_q8_c_and_numpy_agree_and_follow_the_reference_rule():
+    # kv_store_q8 (engine/wgsl/qwen35.js:908-946): scale = max|x| / 127 per 32 values, round to nearest even, clamp
+    x = (po.normal(77, 200 * 512) * 3).astype(np.float32).reshape(200, 512)
+    x[0, :32] = 0.0; x[1, 32:64] = 1e-30; x[2, 5] = 1e6; x[3, :32] = np.arange(32) - 15.5
+    q, sc = po.kv_store_q8(x); q2, sc2 = po.np_kv_store_q8(x)
+    assert np.array_equal(q, q2) and np.array_equal(sc.view(np.uint32), sc2.view(np.uint32))
+    assert np.all(q[0, :32] == 0) and sc[0, 0] == 0.0                       # all-zero block: inv = 0
+    assert np.abs(q).max() == 127 and q.min() >= -127                        # the block maximum maps to +-127, never -128
+    b = x[3, :32]; s = np.float32(np.abs(b).max() / np.float32(127.0))
+    assert np.array_equal(q[3, :32], np.clip(np.rint(b * (np.float32(1.0) / s)), -127, 127).astype(np.int8))
+    d = po.dequant_q8(q, sc)
+    assert np.all(np.abs(d - x) <= sc.repeat(32, axis=-1) * 0.5 * 1.0001 + 1e-30)   # within half a step of every value
+
+
+def test_attn_f64_over_f32_values_is_the_same_definition():
+    K = po.np_f16_rne(po.normal(2, 100 * 512)).reshape(100, 512); V = po.np_f16_rne(po.normal(3, 100 * 512)).reshape(100, 512)
+    q = po.normal(4, 2 * 16 * 256).astype(np.float32).reshape(2, -1); g = po.normal(5, 2 * 16 * 256).astype(np.float32).reshape(2, -1)
+    a = po.attn_f64(q, K, V, 16, 2, 256, 98, 2, g); b = po.attn_f64_kv32(q, po.np_h2f(K), po.np_h2f(V), 16, 2, 256, 98, 2, g)
+    assert np.array_equal(a, b)
