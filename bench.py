@@ -136,10 +136,12 @@ class Run:
     def min_over_ranks(self, x: float) -> float:
         return -self.max_over_ranks(-x)
 
-    def timed(self, run_step, steps: int, min_total_s: float = MIN_TIMED_S, max_regions: int = 2000):
+    def timed(self, run_step, steps: int, min_total_s: float | None = None, max_regions: int = 2000):
         """Regions of exactly `steps` steps, each bracketed by barrier + synchronize and timed with CUDA events (max over
         ranks), repeated until min_total_s have been timed.  Returns the per-region milliseconds."""
         torch = self.torch
+        # shorter regions (core kernel, end to end) scale with the main one
+        min_total_s = self.args.min_time if min_total_s is None else min_total_s * self.args.min_time / MIN_TIMED_S
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         regions, total = [], 0.0
         while True:
@@ -280,9 +282,10 @@ def run_decode(R: Run, w, headline: bool):
 
     # The dominant kernel alone.  Single-sequence steps: the same K steps with only the core kernel of every layer
     # launched (a CUDA graph of `layers` core launches), back to back, between one CUDA-event pair (a pair around each
-    # 10-20 us launch would time the launch gap as well).  Batched / sharded steps: an event pair around every core launch.
+    # 10-20 us launch would time the launch gap as well); on a shard that leaves the cross-GPU exchange out, as it leaves
+    # the merge out, so the figure is the streaming kernel's own.  Batched steps: an event pair around every core launch.
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if not sharded and n_seqs == 1:
+    if n_seqs == 1 and (not sharded or args.exchange == "peer"):
         eng.set_core_only(True)
         cs2 = torch.cuda.Stream(device=dev)
         cs2.wait_stream(torch.cuda.current_stream(dev))
@@ -299,10 +302,13 @@ def run_decode(R: Run, w, headline: bool):
         eng.set_core_only(False)
         step()
     else:
+        eng.set_core_only(True)      # no merge, no exchange: the launch's duration is the streaming kernel's own
         eng.timing_begin(layers * args.steps + 8)
         for _ in range(args.steps):
             step()
         core_ms, core_n = eng.timing_end()
+        eng.set_core_only(False)
+        step()
     eng.sync()
 
     # end to end: host buffers in, host result out, every step
@@ -620,6 +626,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the decode workloads' context length (scaling probes)")
     ap.add_argument("--cols", type=int, default=0, help="override the prompt length of the prefill workload (small profiling captures)")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the dominant kernel (default: the committed capture's figure, where one exists for the workload at its full per-launch size)")
+    ap.add_argument("--min-time", type=float, default=MIN_TIMED_S, help="seconds each timed region is repeated up to (0: one region; small profiling captures)")
     ap.add_argument("--no-check", dest="check", action="store_false", help="skip the oracle check ahead of the timed regions")
     ap.add_argument("--no-sub", dest="sub", action="store_false", help="headline only: no prefill / c5 sub-records")
     args = ap.parse_args()

@@ -162,7 +162,8 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   ctx->tune.no_fuse = getenv("POOLED_ATTN_NO_FUSE") != nullptr;
   ctx->tune.verify_mma_sync = getenv("POOLED_ATTN_VERIFY_MMA_SYNC") != nullptr;
   ctx->tune.no_merge = getenv("POOLED_ATTN_NO_MERGE") != nullptr;
-  if (const char* e = getenv("POOLED_ATTN_OWN_PREFETCH")) ctx->tune.own_prefetch = atoi(e) != 0;
+  if (const char* e = getenv("POOLED_ATTN_OWN_PREFETCH")) ctx->tune.own_prefetch = atoi(e);
+  if (const char* e = getenv("POOLED_ATTN_XCH_PREFETCH")) ctx->tune.xch_prefetch = atoi(e);
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -581,10 +582,9 @@ extern "C" int pa_rope_append_items(pa_layer* L, const pa_item* items, uint32_t 
   if (p.mode == PA_ROPE_F64 && n_items * half <= 64) p.n_ang = n_items * half;
   CU_TRY(ctx, launch_rope_append(p, n_items, (cudaStream_t)stream));
   ctx->stats.kernel_launches++;
-  if (row0 != 0xffffffffu) {
-    if (ctx->inflight_layer == L && ctx->inflight_row0 < row0) row0 = ctx->inflight_row0;
-    ctx->inflight_layer = L; ctx->inflight_row0 = row0;
-  }
+  // what the kernel just launched may still be writing: rows from row0 on (none on a shard that owns no item's row)
+  if (ctx->inflight_layer == L && ctx->inflight_row0 < row0) row0 = ctx->inflight_row0;
+  ctx->inflight_layer = L; ctx->inflight_row0 = row0;
   return PA_OK;
 }
 
@@ -713,7 +713,9 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   p.prefetch_old_rows = after_own_append ? 1u : 0u;
   p.early_limit = (after_own_append && ctx->inflight_layer == L) ? ctx->inflight_row0 : 0xffffffffu;
   p.pre_stages = (uint32_t)ctx->tune.pre_stages;
-  p.own_prefetch = ctx->tune.own_prefetch ? 1u : 0u;
+  // tiles beyond the ring asked into L2 ahead of the wait: on a shard the wait spans the cross-GPU exchange of the call
+  // before, a window in which HBM would otherwise idle
+  p.own_prefetch = (uint32_t)std::max(0, exchange ? ctx->tune.xch_prefetch : ctx->tune.own_prefetch);
   p.next_tiles = (L->next && L->next->ctx == ctx) ? (uint32_t)ctx->tune.next_tiles : 0u;
   if (fz) {
     p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
@@ -736,18 +738,17 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   }
   // One kernel per call where the merge can be shared out among the call's own CTAs: all of them resident at once (one
   // wave at one CTA per SM), and at least half as many CTAs per (item, kv head) as there are (row, 64-dim slice) units.
+  // Not on a KV-sequence shard: there the combine kernel, whose small CTAs wait for the other GPUs beside the next
+  // call's decode CTAs (already fetching their first tiles), measured faster than decode CTAs that hold their SMs
+  // through the exchange.
   const uint32_t units = max_cols * ctx->G * (ctx->cfg.head_dim / 64);
   bool all_rows = true;   // on a shard an item may have no row here: its CTAs never run, so its units must be the combine kernel's
   for (uint32_t i = 0; i < n_items; ++i) all_rows = all_rows && p.items.n_rows[i] > 0;
-  const bool merge = !partial && !verify_tc && nt <= 2 && all_rows && !ctx->core_only && !ctx->tune.no_merge && max_rows > 0 &&
+  const bool merge = !partial && !exchange && !verify_tc && nt <= 2 && all_rows && !ctx->core_only && !ctx->tune.no_merge && max_rows > 0 &&
                      (uint64_t)ns * ctx->cfg.n_kv_heads * n_items <= (uint64_t)ctx->sm_count && 2 * ns >= units;
   if (merge) {
     p.merge = 1; p.merge_ctr = ctx->merge_ctr;
     p.gate = gate; p.gate_col_stride = gcs; p.gate_head_stride = ghs; p.out = out; p.out_col_stride = ocs; p.act_f16 = ctx->cfg.act_dtype == PA_F16;
-    if (exchange) {
-      p.exchange = 1; p.xc = ctx->xc; p.xch_sweeps = ctx->tune.wait_polls ? ctx->tune.wait_polls : (1u << 20);
-      p.xch_units = total_cols * ctx->cfg.n_heads * (ctx->cfg.head_dim / 64);
-    }
   }
   timing_mark(ctx, st, 0);
   if (verify_tc) CU_TRY(ctx, launch_verify(L, vp, tm_k, tm_v, ctx->cfg.n_kv_heads, st));
@@ -782,8 +783,10 @@ extern "C" int pa_decode(pa_layer* L, const pa_item* items, uint32_t n_items, co
   if (!q) {   // the rotated q a preceding pa_rope_append / pa_rope_append_items left in the context (q_rot = NULL there)
     q = L->ctx->q_rot; q_dtype = PA_F32; q_col_stride = L->ctx->q_dim; q_head_stride = L->ctx->cfg.head_dim;
   }
+  // straight after this library's own append into the layer (the kernel before this one on the stream), rows older
+  // than the appended ones may be fetched while that kernel still runs
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
-                     (cudaStream_t)stream, "pa_decode");
+                     (cudaStream_t)stream, "pa_decode", L->ctx->inflight_layer == L);
 }
 
 extern "C" int pa_decode_gather(pa_layer* L, uint32_t seq, uint32_t n_cols, const uint32_t* row_lists, uint32_t list_stride, const void* q, int q_dtype,
@@ -973,10 +976,11 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
     const uint32_t c_lo = pos >= s_lo ? 0u : (uint32_t)std::min<uint64_t>(s_lo - pos, n_cols);
     const uint32_t c_hi = (uint64_t)pos + n_cols <= s_hi ? n_cols : (pos >= s_hi ? 0u : (uint32_t)(s_hi - pos));
     const bool some = c_lo < c_hi, straddles = some && !owns;
-    if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
-                                  owns ? v : nullptr, kcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, planes ? 2 : 0, true, kvcs))
-      return rc;
-    if (straddles) {
+    if (!ctx->core_only)
+      if (int rc = rope_append_impl(owns ? L : nullptr, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, owns ? k : nullptr,
+                                    owns ? v : nullptr, kcs, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, st, planes ? 2 : 0, true, kvcs))
+        return rc;
+    if (straddles && !ctx->core_only) {
       const size_t es = ctx->cfg.act_dtype == PA_F16 ? 2 : 4;
       const uint8_t* k2 = reinterpret_cast<const uint8_t*>(k) + (size_t)c_lo * kcs * es;
       const uint8_t* v2 = reinterpret_cast<const uint8_t*>(v) + (size_t)c_lo * kvcs * es;
@@ -1300,7 +1304,7 @@ extern "C" int pa_decode_exchange(pa_layer* L, const pa_item* items, uint32_t n_
   if (!out) return fail(L->ctx, PA_EINVAL, "pa_decode_exchange: null out");
   if (L->kv_format != PA_KV_F16) return fail(L->ctx, PA_EUNSUPPORTED, "pa_decode_exchange: the peer exchange is for f16 caches");
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
-                     (cudaStream_t)stream, "pa_decode_exchange", false, true);
+                     (cudaStream_t)stream, "pa_decode_exchange", L->ctx->inflight_layer == L, true);
 }
 
 extern "C" int pa_attn_layer_sharded(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t q_col_stride,

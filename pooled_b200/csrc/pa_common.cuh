@@ -258,7 +258,8 @@ struct pa_ctx {
     int next_tiles = 0;          // POOLED_ATTN_NEXT_TILES: tiles of the next layer each decode CTA asks L2 to fetch at its end
     bool no_fuse = false;        // POOLED_ATTN_NO_FUSE: RoPE/append -> decode -> combine chain instead of the fused front
     bool verify_mma_sync = false;// POOLED_ATTN_VERIFY_MMA_SYNC: k-token blocks on the mma.sync kernel
-    bool own_prefetch = false;   // POOLED_ATTN_OWN_PREFETCH=1: L2 requests for a decode CTA's own later tiles at entry
+    int own_prefetch = 0;        // POOLED_ATTN_OWN_PREFETCH=n: L2 requests for n of a decode CTA's own later tiles at entry
+    int xch_prefetch = 0;        // POOLED_ATTN_XCH_PREFETCH=n: the same for calls that end in a cross-GPU exchange
     bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel
     uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)
   } tune;

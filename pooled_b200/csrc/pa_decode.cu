@@ -43,73 +43,113 @@ __device__ __forceinline__ void fma4(float4& acc, const float4& x, float w) {
   acc.x = __fmaf_rn(x.x, w, acc.x); acc.y = __fmaf_rn(x.y, w, acc.y); acc.z = __fmaf_rn(x.z, w, acc.z); acc.w = __fmaf_rn(x.w, w, acc.w);
 }
 
-// Cross-GPU step of a merge: publish this rank's merged slice (o of 64 dims by threads 0..63, m and l by thread 64) to
-// every rank, wait (bounded) for the other ranks' slices, merge them; t and Lsum come back as the merged sums.  Every
-// value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands whole, so the receiver
-// spins on the words themselves and no flag, fence or second round trip is needed.  The last of the call's
-// `total_units` slices to get through advances the call counter.  `sync`: a barrier of the calling threads.
-template <int HD, typename Sync>
-__device__ __forceinline__ void exchange_slice(const ExchangeView& x, uint32_t prow, uint32_t slice, int tid, float& t, float M, float& Lsum, uint32_t sweeps,
-                                               uint32_t* err, uint32_t total_units, volatile unsigned int* s_epoch, Sync&& sync) {
-  const uint32_t n_slices = HD / 64, d = slice * 64 + tid;
-  if (tid == 0) *s_epoch = *reinterpret_cast<volatile unsigned int*>(x.ctr);
-  sync();
-  const uint32_t epoch = *s_epoch, parity = epoch & 1u, tag = epoch + 1u;
-  const size_t blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // entries of 8 bytes: o rows, then (m, l) per (row, slice)
-  const size_t o_idx = (size_t)prow * HD + d;
-  const size_t ml_idx = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + slice) * 2;
-  auto put = [&](uint2* dst, float v) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-  };
-  for (uint32_t r = 0; r < x.world; ++r) {
-    uint2* dst = reinterpret_cast<uint2*>(x.peer[r]) + (size_t)(parity * x.world + x.rank) * blk;
-    if (tid < 64) put(dst + o_idx, t);
-    if (tid == 64) { put(dst + ml_idx, M); put(dst + ml_idx + 1, Lsum); }
+// Cross-GPU step of a merge.  Every rank publishes its merged slice of a query row (64 dims of o, and m, l) into every
+// rank's buffer, waits (bounded) for the other ranks' slices and merges them in rank order, so every rank ends with the
+// same bits.  Every value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands
+// whole, so the receiver spins on the words themselves and no flag, fence or second round trip is needed.  The buffers
+// alternate with the call counter's parity; the last of the call's slices to get through advances the counter.
+// A thread owns NV dims of the slice (dd[]: dims within the slice).  `epoch`: the call counter, read by the caller at
+// any time between the end of the previous kernel and its own slice's xch_done (it cannot move in between).
+template <int HD>
+struct XchSlot {
+  size_t blk, o_idx, ml_idx;
+  uint32_t parity, tag;
+  // d0: first dim of the unit (a multiple of 32); (m, l) are kept per 64-dim slice
+  __device__ __forceinline__ XchSlot(const ExchangeView& x, uint32_t epoch, uint32_t prow, uint32_t d0) {
+    constexpr uint32_t n_slices = HD / 64;
+    parity = epoch & 1u; tag = epoch + 1u;
+    blk = (size_t)x.max_rows * (HD + 2 * n_slices);   // entries of 8 bytes: o rows, then (m, l) per (row, slice)
+    o_idx = (size_t)prow * HD + d0;
+    ml_idx = (size_t)x.max_rows * HD + ((size_t)prow * n_slices + d0 / 64) * 2;
   }
-  if (tid < 64) {
-    // every sweep requests all entries still missing at once (m, l and this thread's o of every source rank) and
-    // keeps those that carry the call's tag; bounded
-    const uint2* mine = reinterpret_cast<const uint2*>(x.peer[x.rank]);
-    float mr[8], lr[8], orr[8];
-    uint32_t pending = (1u << x.world) - 1u;
-    for (uint32_t it = 0; it < sweeps && pending; ++it) {
-      uint32_t v[8][3], tg[8][3];
+};
+__device__ __forceinline__ void xch_store(uint2* dst, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+// o values of this thread's dims (n_o of them: 0 for a thread that only carries m and l) and, from one thread, (m, l)
+template <int HD, int NV>
+__device__ __forceinline__ void xch_put(const ExchangeView& x, const XchSlot<HD>& a, const uint32_t (&dd)[NV], const float (&t)[NV], bool with_o, bool with_ml,
+                                        float M, float Lsum) {
+  for (uint32_t r = 0; r < x.world; ++r) {
+    uint2* dst = reinterpret_cast<uint2*>(x.peer[r]) + (size_t)(a.parity * x.world + x.rank) * a.blk;
+    if (with_o) {
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if (!((pending >> r) & 1u)) continue;
-        const uint2* src = mine + (size_t)(parity * x.world + r) * blk;
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][0]), "=r"(tg[r][0]) : "l"(src + ml_idx) : "memory");
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][1]), "=r"(tg[r][1]) : "l"(src + ml_idx + 1) : "memory");
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][2]), "=r"(tg[r][2]) : "l"(src + o_idx) : "memory");
-      }
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if (!((pending >> r) & 1u)) continue;
-        if (tg[r][0] == tag && tg[r][1] == tag && tg[r][2] == tag) {
-          mr[r] = __uint_as_float(v[r][0]); lr[r] = __uint_as_float(v[r][1]); orr[r] = __uint_as_float(v[r][2]);
-          pending &= ~(1u << r);
-        }
-      }
-      if (pending && it > 1024) __nanosleep(64);
+      for (int k = 0; k < NV; ++k) xch_store(dst + a.o_idx + dd[k], t[k], a.tag);
     }
-    if (pending) atomicMax(err, (uint32_t)WAIT_PEER);   // a peer never published: report and carry on
-    float Mg = -3.0e38f;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) if ((uint32_t)r < x.world && !((pending >> r) & 1u)) Mg = fmaxf(Mg, mr[r]);
-    float Lg = 0.f, og = 0.f;
+    if (with_ml) { xch_store(dst + a.ml_idx, M, a.tag); xch_store(dst + a.ml_idx + 1, Lsum, a.tag); }
+  }
+}
+// every sweep requests all entries still missing at once (m, l and this thread's o of every source rank) and keeps
+// those that carry the call's tag; bounded.  t and Lsum come back as the merged sums over all ranks.
+template <int HD, int NV>
+__device__ __forceinline__ void xch_get(const ExchangeView& x, const XchSlot<HD>& a, const uint32_t (&dd)[NV], float (&t)[NV], float& Lsum, uint32_t sweeps,
+                                        uint32_t* err) {
+  const uint2* mine = reinterpret_cast<const uint2*>(x.peer[x.rank]);
+  float mr[8], lr[8], orr[8][NV];
+  uint32_t pending = (1u << x.world) - 1u;
+  for (uint32_t it = 0; it < sweeps && pending; ++it) {
+    uint32_t v[8][2 + NV], tg[8][2 + NV];
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-      if ((uint32_t)r >= x.world || ((pending >> r) & 1u)) continue;
-      const float w = __expf(mr[r] - Mg);
-      Lg += lr[r] * w;
-      og += orr[r] * w;
+      if (!((pending >> r) & 1u)) continue;
+      const uint2* src = mine + (size_t)(a.parity * x.world + r) * a.blk;
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][0]), "=r"(tg[r][0]) : "l"(src + a.ml_idx) : "memory");
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][1]), "=r"(tg[r][1]) : "l"(src + a.ml_idx + 1) : "memory");
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[r][2 + k]), "=r"(tg[r][2 + k]) : "l"(src + a.o_idx + dd[k]) : "memory");
     }
-    t = og; Lsum = Lg;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (!((pending >> r) & 1u)) continue;
+      bool all = tg[r][0] == a.tag && tg[r][1] == a.tag;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) all = all && tg[r][2 + k] == a.tag;
+      if (all) {
+        mr[r] = __uint_as_float(v[r][0]); lr[r] = __uint_as_float(v[r][1]);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) orr[r][k] = __uint_as_float(v[r][2 + k]);
+        pending &= ~(1u << r);
+      }
+    }
+    if (pending && it > 1024) __nanosleep(64);
   }
-  // the last slice of the call advances the call counter (every slice read it before any could get here last)
-  if (tid == 0) {
-    __threadfence();
-    if (atomicAdd(x.ctr + 1, 1u) == total_units - 1) { x.ctr[1] = 0; __threadfence(); atomicAdd(x.ctr, 1u); }
+  if (pending) atomicMax(err, (uint32_t)WAIT_PEER);   // a peer never published: report and carry on
+  float Mg = -3.0e38f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) if ((uint32_t)r < x.world && !((pending >> r) & 1u)) Mg = fmaxf(Mg, mr[r]);
+  float Lg = 0.f, og[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) og[k] = 0.f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    if ((uint32_t)r >= x.world || ((pending >> r) & 1u)) continue;
+    const float w = __expf(mr[r] - Mg);
+    Lg = __fmaf_rn(lr[r], w, Lg);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) og[k] = __fmaf_rn(orr[r][k], w, og[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k) t[k] = og[k];
+  Lsum = Lg;
+}
+// one thread per slice, after its own xch_get: the last slice of the call advances the call counter
+__device__ __forceinline__ void xch_done(const ExchangeView& x, uint32_t total_units) {
+  __threadfence();
+  if (atomicAdd(x.ctr + 1, 1u) == total_units - 1) { x.ctr[1] = 0; __threadfence(); atomicAdd(x.ctr, 1u); }
+}
+// the three steps for a slice held by threads 0..63 (one dim each) with m and l in thread 64
+template <int HD>
+__device__ __forceinline__ void exchange_slice(const ExchangeView& x, uint32_t prow, uint32_t slice, int tid, float& t, float M, float& Lsum, uint32_t sweeps,
+                                               uint32_t* err, uint32_t total_units, uint32_t epoch) {
+  const XchSlot<HD> a(x, epoch, prow, slice * 64);
+  const uint32_t dd[1] = {(uint32_t)tid & 63u};
+  float tv[1] = {t};
+  xch_put<HD, 1>(x, a, dd, tv, tid < 64, tid == 64, M, Lsum);
+  if (tid < 64) {
+    xch_get<HD, 1>(x, a, dd, tv, Lsum, sweeps, err);
+    t = tv[0];
+    if (tid == 0) xch_done(x, total_units);
   }
 }
 
@@ -118,12 +158,10 @@ __device__ __forceinline__ void exchange_slice(const ExchangeView& x, uint32_t p
 // 256 threads; thread t here does the work of its threads t and t + 128), so a call gives the same bits whether its
 // records are merged here or there.  o_rec / ml_rec: record 0 of the row; records follow one another.  Scratch: 6 KB of
 // shared memory no one else uses any more.  bar: the group's named barrier.
-struct MergeScratch { float w[512]; float red[8]; float red2[8]; float4 acc[16][16]; unsigned int epoch; };
-struct MergeExchange { const ExchangeView* xc; uint32_t prow, sweeps, total_units; uint32_t* err; };   // xc == nullptr: one GPU
+struct MergeScratch { float w[512]; float red[8]; float red2[8]; float4 acc[16][16]; };
 template <int HD>
 __device__ __forceinline__ void merge_slice_128(const float* __restrict__ o_rec, const float* __restrict__ ml_rec, uint32_t ns, uint32_t slice, int t,
-                                                MergeScratch& sc, uint32_t bar, bool gated, float gv, bool empty_is_zero, int act_f16, void* out, uint64_t oo,
-                                                const MergeExchange& mx) {
+                                                MergeScratch& sc, uint32_t bar, bool gated, float gv, bool empty_is_zero, int act_f16, void* out, uint64_t oo) {
   const int wv = t >> 5, lane = t & 31, ln = t & 15, gA = t >> 4;
   // everything is requested before the first use: one memory round trip
   float mv[4], lv[4];
@@ -199,8 +237,6 @@ __device__ __forceinline__ void merge_slice_128(const float* __restrict__ o_rec,
 #pragma unroll
     for (int i = 1; i < 16; ++i) tt = __fadd_rn(tt, sa[i * 64 + t]);
   }
-  if (mx.xc)   // a KV-sequence shard: the other ranks' slices are merged in before the division
-    exchange_slice<HD>(*mx.xc, mx.prow, slice, t, tt, M, Lsum, mx.sweeps, mx.err, mx.total_units, &sc.epoch, [&] { named_bar_sync(bar, kConsumers); });
   if (t < 64) {
     float rv = (empty_is_zero && Lsum == 0.f) ? 0.f : __fdiv_rn(tt, Lsum);
     if (gated) rv = __fmul_rn(rv, __fdiv_rn(1.0f, __fadd_rn(1.0f, __expf(-gv))));
@@ -252,7 +288,22 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   const uint32_t ns_eff = min(p.n_splits, max(1u, tiles / 2));
   const uint32_t tps = (tiles + ns_eff - 1) / max(ns_eff, 1u);  // tiles per split
   const uint32_t tile0 = split * tps;
-  if (tile0 >= tiles) return;
+  if (tile0 >= tiles) {
+    if constexpr (NT <= 2) {
+      // a call that merges its own records has no combine kernel behind it to give an empty list its zeros
+      if (p.merge && g_list && tiles == 0 && split == 0) {
+        pdl_wait();
+        const uint32_t G = p.G;
+        for (uint32_t idx = threadIdx.x; idx < n_cols * G * HD; idx += blockDim.x) {
+          const uint32_t row = idx / HD, d = idx % HD, c = row / G, hh = row % G;
+          const uint64_t oo = (uint64_t)(p.items.col0[item] + c) * p.out_col_stride + (uint64_t)(g * G + hh) * HD + d;
+          if (p.act_f16) reinterpret_cast<__half*>(p.out)[oo] = __float2half_rn(0.f);
+          else reinterpret_cast<float*>(p.out)[oo] = 0.f;
+        }
+      }
+    }
+    return;
+  }
   const uint32_t tile1 = min(tiles, tile0 + tps);
   const uint32_t n_tiles = tile1 - tile0;
   const uint32_t NS = p.n_stages;
@@ -496,7 +547,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           // The first tiles are on their way into the ring; the CTA's other tiles of rows nobody can be writing are
           // asked into L2 now, while the predecessor kernel drains and this one waits for it: HBM works through the
           // kernel boundary, and the loads that refill the ring later find their tiles in L2.
-          for (uint32_t k = pre; k < n_tiles && (tile0 + k + 1) * kT <= old_rows; ++k) {
+          for (uint32_t k = pre; k < n_tiles && k < pre + p.own_prefetch && (tile0 + k + 1) * kT <= old_rows; ++k) {
             tma_prefetch_3d(&tm_k, 0, y0 + (int)(k * kT), z);
             tma_prefetch_3d(&tm_v, 0, y0 + (int)(k * kT), z);
           }
@@ -1021,8 +1072,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         unit_addr(u, prow, slice, go, oo);
         const float gv = (u == split) ? gv0 : ((gated && ltid < 64) ? gate_ld(go) : 0.f);
         const uint64_t rec0 = prow * p.n_splits;
-        const MergeExchange mx{p.exchange ? &p.xc : nullptr, (uint32_t)prow, p.xch_sweeps, p.xch_units, p.err};
-        merge_slice_128<HD>(p.part_o + rec0 * HD, p.part_ml + rec0 * 2, ns_live, slice, ltid, sc, gbar, gated, gv, p.gather != nullptr, p.act_f16, p.out, oo, mx);
+        merge_slice_128<HD>(p.part_o + rec0 * HD, p.part_ml + rec0 * 2, ns_live, slice, ltid, sc, gbar, gated, gv, p.gather != nullptr, p.act_f16, p.out, oo);
       }
     }
     // the last CTA to finish clears the counters for the next call (every other CTA is past its wait by then)
@@ -1046,6 +1096,8 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_wait();      // the partial records belong to the kernel before this one
   pdl_trigger();
+  uint32_t xepoch = 0;   // the exchange's call counter: requested with everything else
+  if constexpr (XCH) xepoch = *reinterpret_cast<volatile unsigned int*>(p.xc.ctr);
   uint32_t ns = p.fixed_parts;
   if (ns == 0) {
     uint32_t it = 0;
@@ -1120,7 +1172,6 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
   }
   s_acc[grp][ln] = acc;
   __syncthreads();
-  __shared__ unsigned int s_epoch;
   float t = 0.f;
   if (tid < 64) {
     const float* sa = reinterpret_cast<const float*>(s_acc);
@@ -1129,7 +1180,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     for (int i = 1; i < 16; ++i) t = __fadd_rn(t, sa[i * 64 + tid]);
   }
   if constexpr (XCH) {
-    exchange_slice<HD>(p.xc, prow, slice, tid, t, M, Lsum, p.xch_sweeps, p.err, gridDim.x * gridDim.y, &s_epoch, [] { __syncthreads(); });
+    exchange_slice<HD>(p.xc, prow, slice, tid, t, M, Lsum, p.xch_sweeps, p.err, gridDim.x * gridDim.y, xepoch);
   }
   if (tid < 64) {
     if (p.partial_out) {

@@ -25,7 +25,7 @@ struct DecodeParams {
   // the layer the engine runs next (pa_layer_set_next): once a CTA has requested its own last tile it asks L2 for the
   // first next_tiles tiles of the same split of that layer, so HBM keeps working across the kernel boundary
   uint32_t next_tiles, next_max_seq;
-  uint32_t own_prefetch;       // 1: with prefetch_old_rows, the CTA's tiles beyond the ring are asked into L2 at entry
+  uint32_t own_prefetch;       // n: with prefetch_old_rows, n of the CTA's tiles beyond the early ones are asked into L2 at entry
   // gather mode: item i is one column attending the rows listed at gather + col0[i] * gather_stride: [0] = n, then n
   // cache rows ascending (k_cache / v_cache above are the layer's caches)
   const uint32_t* gather; uint32_t gather_stride;
@@ -33,9 +33,6 @@ struct DecodeParams {
   uint32_t merge; unsigned int* merge_ctr;
   const void* gate; uint64_t gate_col_stride, gate_head_stride;
   void* out; uint64_t out_col_stride; int act_f16;
-  // ... and, on a KV-sequence shard, exchange their merged slices with the other ranks before the division
-  uint32_t exchange, xch_sweeps, xch_units;   // xch_units: (row, slice) units of the whole call
-  ExchangeView xc;
   uint32_t* err;
   ItemList items;
 };

@@ -43,12 +43,20 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
     if (threadIdx.x < p.n_ang * 2) reinterpret_cast<uint4*>(s_ang)[threadIdx.x] = reinterpret_cast<const uint4*>(p.ang)[threadIdx.x];
     __syncthreads();
   }
+  // an angle this thread evaluates itself needs nothing of the predecessor's: ahead of the wait
+  const uint32_t pos_c = p.n_items ? p.item_pos[col] : p.pos + col;
+  Angle g_own;
+  const bool own_angle = p.mode == PA_ROPE_F64 && !p.n_ang && !p.angles && pr < half && (p.q || p.k);
+  if (own_angle) {
+    double s, c;
+    sincos(__dmul_rn((double)pos_c, p.inv_freq[pr]), &s, &c);
+    g_own = make_angle(c, s);
+  }
   pdl_wait();
   if (!p.trigger_early) pdl_trigger();
   if (pr >= hd / 2) return;
   const uint32_t nq = p.q ? p.q_heads : 0, nk = p.k ? p.kv_heads : 0;
   uint32_t slot = blockIdx.y;
-  const uint32_t pos_c = p.n_items ? p.item_pos[col] : p.pos + col;
   const uint64_t row_c = p.n_items ? p.item_row[col] : p.cache_row0 + col;
   if (slot >= nq && row_c == ~0ull) return;   // an item whose row another shard holds: nothing to append
   if (slot >= nq + nk) {
@@ -75,11 +83,7 @@ __global__ void __launch_bounds__(128) pa_rope_append_kernel(const RopeParams p)
       Angle g;
       if (p.n_ang) g = s_ang[col * half + pr];
       else if (p.angles) g = p.angles[(uint64_t)col * half + pr];
-      else {
-        double s, c;
-        sincos(__dmul_rn((double)pos_c, p.inv_freq[pr]), &s, &c);
-        g = make_angle(c, s);
-      }
+      else g = g_own;
       ra = rot_exact(a, b, g, true);     // a cos - b sin
       rb = rot_exact(b, a, g, false);    // b cos + a sin
     } else {

@@ -85,5 +85,13 @@ def test_empty_list_and_bad_arguments():
     assert np.all(out[0] == 0.0)
     ref = po.attn_f64(q.cpu().numpy()[1:2], K[[2, 5, 9]], K[[2, 5, 9]], nH, nKV, hd, 2, 1)
     assert util.errs(out[1:2], ref)[1] < util.REF_REL
+    # lists wide enough for the call to merge its own records (no combine kernel behind it): the empty column still
+    # reads zero, over whatever the output held before
+    wide = torch.full((2, nH * hd), 7.0, dtype=torch.float32, device="cuda")
+    eng.decode_gather(0, _lists([np.arange(0), np.array([2, 5, 9])], 2052), q, out=wide)
+    eng.sync()
+    wide = wide.cpu().numpy()
+    assert np.all(wide[0] == 0.0)
+    assert np.array_equal(wide[1], out[1])
     with pytest.raises(PaError):
         eng.decode_gather(0, torch.zeros((2, 1), dtype=torch.int32, device="cuda"), q)      # no room for a row
