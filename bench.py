@@ -243,10 +243,11 @@ def run_decode(R: Run, w, headline: bool):
         else:
             items = [(s, pos, 1) for s in range(n_seqs)]
 
+            sp = [(s, pos) for s in range(n_seqs)]
+
             def step():
                 for li in range(layers):
-                    q_rot = eng.rope_append_items(li, [(s, pos) for s in range(n_seqs)], dq[li], dk[li], dv[li])   # all sequences, one launch
-                    eng.decode(li, items, q_rot, gate(dg, li), dout[li])
+                    eng.encode_items(li, sp, dq[li], dk[li], dv[li], gate(dg, li), dout[li])   # all sequences, one call per layer
         kernel_bytes = 2 * (pos + n_cols) * kvd * 2 * n_seqs
         bytes_per_step = layers * kernel_bytes
 

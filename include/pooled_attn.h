@@ -295,6 +295,21 @@ PA_API int pa_attn_layer_sharded(pa_layer* layer, uint32_t seq, uint32_t pos, ui
                                  uint64_t gate_head_stride, const float* cs_table, void* out, uint64_t out_col_stride,
                                  void* stream);
 
+/* One decode token of each of several sequences through a whole attention layer in one call: what the batched engine
+ * dispatches per layer as attnPrep followed by the multi-column decode (engine/qwen4exp_batch.js:282-296,
+ * engine/wgsl/qwen4exp_batch.js:590-641), i.e. pa_rope_append_items + pa_decode (or pa_decode_exchange) as one call.
+ * items: one column each (item i = column i of q / k / v / gate / out, at its own sequence and position).
+ * exchange != 0: KV-sequence shards (pa_layer_set_origin + pa_exchange_init; positions global; the rank that holds an
+ * item's position appends its row; every rank ends with the full result; same call, same order, on every rank).
+ * For the shapes of the decode kernel's fused front (head_dim 256 with 64 rotary dims, or head_dim 128 rotated in full,
+ * at most 8 heads per kv head, PA_ROPE_F64) no RoPE/append kernel runs: each CTA rotates its item's q, and the CTA on an
+ * item's last tile rotates k, rounds k / v to f16 and appends the row.  Same results, bit for bit, as the two-call form.
+ * f16 caches only. */
+PA_API int pa_attn_items(pa_layer* layer, const pa_item* items, uint32_t n_items, const void* q, uint64_t q_col_stride,
+                         uint64_t q_head_stride, const void* k, const void* v, uint64_t kv_col_stride, const void* gate,
+                         uint64_t gate_col_stride, uint64_t gate_head_stride, void* out, uint64_t out_col_stride,
+                         int exchange, void* stream);
+
 /* Tiled causal prefill of n_cols columns of one sequence starting at pos (their K/V already appended).
  * Replaces attn_flash_tile + attn_combine_tile + sigmoid_mul_mc (engine/wgsl/attn_tile.js:108-193,
  * engine/wgsl/qwen35.js:877-887) as dispatched by _encAttnCore (engine/qwen35.js:2489-2493, :2516). */

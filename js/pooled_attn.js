@@ -56,6 +56,7 @@ export const SYMBOLS = {
   pa_shared_close: { parameters: [P, P], result: I32 },
   pa_exchange_init: { parameters: [P, U32, U32, BUF, U32], result: I32 },
   pa_decode_exchange: { parameters: [P, BUF, U32, P, I32, U64, U64, P, U64, U64, P, U64, P], result: I32 },
+  pa_attn_items: { parameters: [P, P, U32, P, U64, U64, P, P, U64, P, U64, U64, P, U64, I32, P], result: I32 },
   pa_attn_layer_sharded: { parameters: [P, U32, U32, U32, P, U64, U64, P, P, U64, P, U64, U64, P, P, U64, P], result: I32 },
   pa_prefill: { parameters: [P, U32, U32, U32, P, I32, U64, U64, P, U64, U64, P, U64, P], result: I32 },
   pa_sigmoid_mul: { parameters: [P, P, U64, P, U64, U64, U32, P], result: I32 },
@@ -158,12 +159,12 @@ export class NativeAttention {
     check(await this.S.pa_attn_step_host(new Uint8Array(lp.buffer), this.layers.length, seq, pos, nCols, mode, qFull, BigInt(nCols * qc), BigInt(qc), hs, k, v,
       BigInt(nCols * kvDim), BigInt(kvDim), gate, BigInt(nCols * qc), BigInt(qc), hs, out, BigInt(nCols * qDim), BigInt(qDim), stream), this.ctx);
   }
-  // A batch of sequences decoding one token each (engine/qwen4exp_batch.js:268-296): items = [[seq, pos], ...]
-  decodeBatch(li, items, q, k, v, gate, out, stream = null) {
+  // A batch of sequences decoding one token each (engine/qwen4exp_batch.js:268-296): items = [[seq, pos], ...];
+  // one library call per layer (RoPE, append, decode, gate); sharded = KV-sequence shards with the peer exchange
+  decodeBatch(li, items, q, k, v, gate, out, { sharded = false, stream = null } = {}) {
     const { hd, qDim, kvDim } = this.dims, it = paItems(items.map(([s, p]) => [s, p, 1]));
-    check(this.S.pa_rope_append_items(this.layers[li], new Uint8Array(it.buffer), items.length, q, BigInt(qDim), BigInt(hd), k, v, BigInt(kvDim), null, stream), this.ctx);
-    // the rotated q stays in the context; a null q_rot above means "use it" in the decode that follows
-    check(this.S.pa_decode(this.layers[li], new Uint8Array(it.buffer), items.length, null, PA_F32, BigInt(qDim), BigInt(hd), gate, BigInt(qDim), BigInt(hd), out, BigInt(qDim), stream), this.ctx);
+    check(this.S.pa_attn_items(this.layers[li], new Uint8Array(it.buffer), items.length, q, BigInt(qDim), BigInt(hd), k, v, BigInt(kvDim), gate, BigInt(qDim), BigInt(hd),
+      out, BigInt(qDim), sharded ? 1 : 0, stream), this.ctx);
   }
   async sync(stream = null) { check(await this.S.pa_sync(this.ctx, stream), this.ctx); }
   reset() { check(this.S.pa_reset(this.ctx), this.ctx); }   // after a failed step every call rejects until here (engine/qwen35.js:111-119)

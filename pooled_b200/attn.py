@@ -243,6 +243,20 @@ class AttnEngine:
                                              q_head_stride or self.cfg.head_dim, self._p(k), self._p(v), k.stride(0), self._p(q_rot), self._st()))
         return q_rot
 
+    def encode_items(self, li: int, seqs_pos, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None, sharded: bool = False, q_head_stride: int | None = None,
+                     gate_head_stride: int | None = None) -> torch.Tensor:
+        """One decode token of each of several sequences through the layer in one C-ABI call: seqs_pos = [(seq, pos)],
+        row i of q / k / v / gate / out belongs to item i.  sharded: KV-sequence shards with the peer exchange."""
+        n = len(seqs_pos)
+        if out is None:
+            out = torch.empty((n, self.cfg.q_dim), dtype=self.cfg.act_dtype, device=q.device)
+        gp, gcs, ghs = self._gate(gate, gate_head_stride)
+        self._ck(self.L.pa_attn_items(self.layers[li], self._items([(s, p, 1) for s, p in seqs_pos]), n, self._p(q), q.stride(0),
+                                      q_head_stride or self.cfg.head_dim, self._p(k), self._p(v), k.stride(0), gp, gcs, ghs, self._p(out),
+                                      out.stride(0), 1 if sharded else 0, self._st()))
+        return out
+
     def _items(self, items):
         arr = (_l.PaItem * len(items))()
         for i, (seq, pos, n_cols) in enumerate(items):

@@ -545,11 +545,9 @@ extern "C" int pa_rope_append(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t 
                           kv_col_stride, cs_table, ctx->cfg.rope_mode, ctx->cfg.act_dtype == PA_F16, (cudaStream_t)stream);
 }
 
-extern "C" int pa_rope_append_items(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, uint64_t q_col_stride, uint64_t q_head_stride,
-                                    const void* k, const void* v, uint64_t kv_col_stride, float* q_rot, void* stream) {
-  if (!L) return PA_EINVAL;
+static int rope_append_items_impl(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, uint64_t q_col_stride, uint64_t q_head_stride,
+                                  const void* k, const void* v, uint64_t kv_col_stride, uint64_t v_col_stride, float* q_rot, void* stream) {
   pa_ctx* ctx = L->ctx;
-  GUARD(ctx);
   if (!q || !k || !v || !items) return fail(ctx, PA_EINVAL, "pa_rope_append_items: null q, k, v or items");
   if (n_items < 1 || n_items > 32) return fail(ctx, PA_EINVAL, "pa_rope_append_items: 1 to 32 items per call");
   if (n_items > ctx->cfg.max_cols && !q_rot) return fail(ctx, PA_EINVAL, "pa_rope_append_items: %u items exceed max_cols %u", n_items, ctx->cfg.max_cols);
@@ -558,7 +556,7 @@ extern "C" int pa_rope_append_items(pa_layer* L, const pa_item* items, uint32_t 
   RopeParams p{};
   p.q = q; p.q_col_stride = q_col_stride; p.q_head_stride = q_head_stride; p.q_heads = ctx->cfg.n_heads;
   p.q_out = q_rot ? q_rot : ctx->q_rot; p.q_out_col_stride = ctx->q_dim;
-  p.k = k; p.v = v; p.kv_col_stride = kv_col_stride; p.v_col_stride = kv_col_stride; p.kv_heads = ctx->cfg.n_kv_heads;
+  p.k = k; p.v = v; p.kv_col_stride = kv_col_stride; p.v_col_stride = v_col_stride; p.kv_heads = ctx->cfg.n_kv_heads;
   p.k_cache = L->k; p.v_cache = L->v;
   p.hd = ctx->cfg.head_dim; p.n_rot = ctx->cfg.n_rot; p.mode = ctx->cfg.rope_mode; p.in_f16 = ctx->cfg.act_dtype == PA_F16;
   p.inv_freq = ctx->inv_freq;
@@ -588,6 +586,14 @@ extern "C" int pa_rope_append_items(pa_layer* L, const pa_item* items, uint32_t 
   return PA_OK;
 }
 
+extern "C" int pa_rope_append_items(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, uint64_t q_col_stride, uint64_t q_head_stride,
+                                    const void* k, const void* v, uint64_t kv_col_stride, float* q_rot, void* stream) {
+  if (!L) return PA_EINVAL;
+  GUARD(L->ctx);
+  if (L->kv_format != PA_KV_F16) return fail(L->ctx, PA_EUNSUPPORTED, "pa_rope_append_items: f16 caches only; use pa_rope_append per sequence");
+  return rope_append_items_impl(L, items, n_items, q, q_col_stride, q_head_stride, k, v, kv_col_stride, kv_col_stride, q_rot, stream);
+}
+
 static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, ItemList* il, uint32_t* total_cols, uint32_t* max_rows, uint32_t* max_cols,
                        uint64_t* kv_bytes, const char* who, bool sharded_ok) {
   pa_ctx* ctx = L->ctx;
@@ -601,7 +607,7 @@ static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, Item
                   items[i].n_cols, ctx->G, kMaxRows);
     const int64_t end = (int64_t)items[i].pos + items[i].n_cols - (int64_t)L->origin;
     const uint32_t rows = (uint32_t)(end < 0 ? 0 : end > (int64_t)L->max_seq ? L->max_seq : end);
-    il->seq[i] = items[i].seq; il->n_cols[i] = items[i].n_cols; il->col0[i] = cols;
+    il->seq[i] = items[i].seq; il->n_cols[i] = items[i].n_cols; il->col0[i] = cols; il->pos[i] = items[i].pos;
     il->lim0[i] = (int32_t)((int64_t)items[i].pos + 1 - (int64_t)L->origin); il->n_rows[i] = rows;
     cols += items[i].n_cols;
     if (rows > mr) mr = rows;
@@ -615,8 +621,9 @@ static int build_items(pa_layer* L, const pa_item* items, uint32_t n_items, Item
 }
 
 
-// the token's unrotated k / v row for the fused front of the decode kernel
-struct FusedFront { const void* k; const void* v; bool append; uint32_t pos; };
+// the tokens' unrotated k / v rows for the fused front of the decode kernel: one item at `pos` (cos / sin from the
+// host), or one token of each of several items (kv_stride elements between their rows; cos / sin on the device)
+struct FusedFront { const void* k; const void* v; uint32_t append_mask; uint32_t pos; uint64_t k_stride = 0, v_stride = 0; bool device_angles = false; };
 
 // a gathered call: the columns' row lists on the device, one list of `stride` words per column
 struct GatherLists { const uint32_t* lists; uint32_t stride; };
@@ -718,9 +725,10 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   p.own_prefetch = (uint32_t)std::max(0, exchange ? ctx->tune.xch_prefetch : ctx->tune.own_prefetch);
   p.next_tiles = (L->next && L->next->ctx == ctx) ? (uint32_t)ctx->tune.next_tiles : 0u;
   if (fz) {
-    p.fused = 1; p.append = fz->append ? 1u : 0u; p.k_new = fz->k; p.v_new = fz->v;
+    p.fused = fz->device_angles ? 2u : 1u; p.append = fz->append_mask; p.k_new = fz->k; p.v_new = fz->v;
+    p.k_new_stride = fz->k_stride; p.v_new_stride = fz->v_stride; p.inv_freq = ctx->inv_freq;
     p.k_cache = L->k; p.v_cache = L->v;
-    memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), (size_t)(ctx->cfg.n_rot / 2) * sizeof(Angle));
+    if (!fz->device_angles) memcpy(p.rope_ang, host_angles(ctx, fz->pos, 1), (size_t)(ctx->cfg.n_rot / 2) * sizeof(Angle));
   }
   CUtensorMap tm_k, tm_v;
   PrefillParams vp{};
@@ -770,8 +778,12 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   if (!ctx->core_only && !merge) CU_TRY(ctx, launch_combine((int)ctx->cfg.head_dim, c, total_cols * ctx->cfg.n_heads, st));
   ctx->stats.kernel_launches += (ctx->core_only || merge) ? 1 : 2; ctx->stats.kv_bytes_streamed += kv_bytes; ctx->stats.calls++;
   // this call's kernel waited for everything before it; what it appends itself is what may still be in flight
-  if (fz && fz->append) { ctx->inflight_layer = L; ctx->inflight_row0 = max_rows ? max_rows - 1 : 0; }
-  else ctx->inflight_layer = nullptr;
+  if (fz && fz->append_mask) {
+    uint32_t r0 = 0xffffffffu;
+    for (uint32_t i = 0; i < n_items; ++i)
+      if ((fz->append_mask >> i) & 1u) r0 = std::min(r0, p.items.n_rows[i] ? p.items.n_rows[i] - 1 : 0u);
+    ctx->inflight_layer = L; ctx->inflight_row0 = r0;
+  } else ctx->inflight_layer = nullptr;
   return PA_OK;
 }
 
@@ -966,7 +978,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
     // this rank appends only if the new rows fall into its shard; every rank rotates q and decodes what it holds
     const bool owns = pos >= L->origin && (uint64_t)pos + n_cols <= (uint64_t)L->origin + L->max_seq;
     if (can_fuse_front(ctx, n_cols, q, qcs, qhs, k, v)) {
-      FusedFront fz{k, v, owns, pos};
+      FusedFront fz{k, v, owns ? 1u : 0u, pos};
       pa_item it{seq, pos, 1, 0};
       return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer_sharded", true, true, &fz);
     }
@@ -999,7 +1011,7 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
   // (the reference takes the tiled kernel on full-width non-verify passes, engine/qwen35.js:2489)
   const bool prefill = mode == PA_MODE_PREFILL || (mode == PA_MODE_AUTO && n_cols * ctx->G > (uint32_t)kMaxRows);
   if (!prefill && can_fuse_front(ctx, n_cols, q, qcs, qhs, k, v)) {
-    FusedFront fz{k, v, true, pos};
+    FusedFront fz{k, v, 1u, pos};
     pa_item it{seq, pos, 1, 0};
     return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", true, false, &fz);
   }
@@ -1305,6 +1317,53 @@ extern "C" int pa_decode_exchange(pa_layer* L, const pa_item* items, uint32_t n_
   if (L->kv_format != PA_KV_F16) return fail(L->ctx, PA_EUNSUPPORTED, "pa_decode_exchange: the peer exchange is for f16 caches");
   return decode_impl(L, items, n_items, q, q_dtype, q_col_stride, q_head_stride, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
                      (cudaStream_t)stream, "pa_decode_exchange", L->ctx->inflight_layer == L, true);
+}
+
+// One token of each of several sequences through a whole layer: the fused front of the decode kernel for every item
+// (each CTA rotates its item's q, the CTA on an item's last tile rotates and appends its k / v row), or the
+// RoPE/append kernel for all items followed by the decode, where the fused front does not apply.
+extern "C" int pa_attn_items(pa_layer* L, const pa_item* items, uint32_t n_items, const void* q, uint64_t q_col_stride, uint64_t q_head_stride,
+                             const void* k, const void* v, uint64_t kv_col_stride, const void* gate, uint64_t gate_col_stride, uint64_t gate_head_stride,
+                             void* out, uint64_t out_col_stride, int exchange, void* stream) {
+  if (!L) return PA_EINVAL;
+  pa_ctx* ctx = L->ctx;
+  GUARD(ctx);
+  if (!q || !k || !v || !out || !items) return fail(ctx, PA_EINVAL, "pa_attn_items: null q, k, v, out or items");
+  if (n_items < 1 || n_items > (uint32_t)kMaxItems) return fail(ctx, PA_EINVAL, "pa_attn_items: 1 to %d items per call", kMaxItems);
+  if (n_items > ctx->cfg.max_cols) return fail(ctx, PA_EINVAL, "pa_attn_items: %u items exceed max_cols %u", n_items, ctx->cfg.max_cols);
+  if (L->kv_format != PA_KV_F16) return fail(ctx, PA_EUNSUPPORTED, "pa_attn_items: f16 caches only; use pa_attn_layer per sequence");
+  if (ctx->cfg.rope_mode == PA_ROPE_TABLE) return fail(ctx, PA_EUNSUPPORTED, "pa_attn_items: PA_ROPE_TABLE takes one table per call; use pa_attn_layer per sequence");
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t mask = 0;
+  for (uint32_t i = 0; i < n_items; ++i) {
+    if (items[i].n_cols != 1) return fail(ctx, PA_EINVAL, "pa_attn_items: item %u has %u columns; one token per item", i, items[i].n_cols);
+    if (int rc = check_cols(L, items[i].seq, items[i].pos, 1, "pa_attn_items", !exchange)) return rc;
+    if (items[i].pos >= L->origin && items[i].pos - L->origin < L->max_seq) mask |= 1u << i;
+  }
+  cudaSetDevice(ctx->device);
+  uint64_t qcs = q_col_stride, qhs = q_head_stride, kcs = kv_col_stride;
+  if (L->qnorm_w && !ctx->core_only) {   // QK head-norm first, item i as column i (as pa_attn_layer does for its columns)
+    HeadNormParams hp{};
+    hp.x = q; hp.x_col_stride = qcs; hp.x_head_stride = qhs; hp.y = ctx->norm_q; hp.y_col_stride = ctx->q_dim; hp.y_head_stride = ctx->cfg.head_dim;
+    hp.w = L->qnorm_w; hp.n_first = ctx->cfg.n_heads;
+    hp.x2 = k; hp.x2_col_stride = kv_col_stride; hp.x2_head_stride = ctx->cfg.head_dim; hp.y2 = ctx->norm_k; hp.y2_col_stride = ctx->kv_dim;
+    hp.y2_head_stride = ctx->cfg.head_dim; hp.w2 = L->knorm_w;
+    hp.eps = L->norm_eps; hp.hd = ctx->cfg.head_dim; hp.f16 = ctx->cfg.act_dtype == PA_F16;
+    CU_TRY(ctx, launch_head_norm(hp, n_items, ctx->cfg.n_heads + ctx->cfg.n_kv_heads, st));
+    ctx->stats.kernel_launches++;
+    q = ctx->norm_q; qcs = ctx->q_dim; qhs = ctx->cfg.head_dim;
+    k = ctx->norm_k; kcs = ctx->kv_dim;
+  }
+  if (can_fuse_front(ctx, 1, q, qcs, qhs, k, v) && !(kcs & 1) && !(kv_col_stride & 1)) {
+    // one item: cos / sin from the host's libm, as pa_attn_layer; several: each CTA evaluates its own item's
+    FusedFront fz{k, v, mask, items[0].pos, kcs, kv_col_stride, n_items > 1};
+    return decode_impl(L, items, n_items, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr, st,
+                       "pa_attn_items", true, exchange != 0, &fz);
+  }
+  if (!ctx->core_only)
+    if (int rc = rope_append_items_impl(L, items, n_items, q, qcs, qhs, k, v, kcs, kv_col_stride, ctx->q_rot, st)) return rc;
+  return decode_impl(L, items, n_items, ctx->q_rot, PA_F32, ctx->q_dim, ctx->cfg.head_dim, gate, gate_col_stride, gate_head_stride, out, out_col_stride, nullptr,
+                     st, "pa_attn_items", true, exchange != 0);
 }
 
 extern "C" int pa_attn_layer_sharded(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t q_col_stride,

@@ -195,6 +195,7 @@ struct ItemList {
   uint32_t n_rows[kMaxItems];  // cache rows the last column sees: clamp(pos + n_cols - origin, 0, max_seq)
   uint32_t n_cols[kMaxItems];
   uint32_t col0[kMaxItems];    // first column of the item in q / gate / out
+  uint32_t pos[kMaxItems];     // position of the item's first column
 };
 
 // Peer exchange of merged (o, m, l) records between the GPUs of one box.  Every rank owns one buffer that all ranks

@@ -265,6 +265,8 @@ struct DecSmem {
   static int total_bytes(int stages) { return 1024 + stages * 2 * SLOT + fixed_bytes(); }
 };
 
+static_assert(sizeof(DecodeParams) + 4 * sizeof(CUtensorMap) <= 4096, "the decode kernel's launch parameters must fit 4 KB");
+
 template <int HD, int NT, bool PRECISE>
 __global__ void __launch_bounds__(DecSmem<HD, NT, PRECISE>::THREADS, 1)
 pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kn,
@@ -388,7 +390,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   constexpr int RIT = CAN_FUSE ? ROWS * IPR / kConsumers : 1;   // rotated items per thread (1 or 2)
   constexpr int PPR = (HD - NRD) / 2;                 // unrotated pairs per row (96 or 0)
   const bool fused = CAN_FUSE && p.fused;
-  const bool own_new = fused && p.append && tile1 == tiles;
+  const bool own_new = fused && ((p.append >> item) & 1u) && tile1 == tiles;
   float2 kx = make_float2(0.f, 0.f), vx = make_float2(0.f, 0.f), kxb = make_float2(0.f, 0.f);
   uint32_t k_new2 = 0, v_new2 = 0, k_new2b = 0;       // head_dim 128: lanes of warp 0 carry K words t and t + 32
   auto rotate = [&](float2 x) {   // warp 0 only, all lanes
@@ -404,8 +406,17 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     // Threads that index launch parameters differently are served one address at a time, each a miss of the constant
     // cache: far too slow for the critical path.  The angles go to shared memory while the predecessor still runs.
     if (fused) {
+      if (p.fused == 2) {
+        // several items, each at its own position: the CTA evaluates its item's angles while the predecessor still runs
+        if (tid < RHALF) {
+          double sn, cs;
+          sincos(__dmul_rn((double)p.items.pos[item], p.inv_freq[tid]), &sn, &cs);
+          s_ang[tid] = make_angle(cs, sn);
+        }
+      } else {
 #pragma unroll
-      for (int u = 0; u < RHALF / 32; ++u) reinterpret_cast<uint2*>(s_ang)[tid + u * kConsumers] = reinterpret_cast<const uint2*>(p.rope_ang)[tid + u * kConsumers];
+        for (int u = 0; u < RHALF / 32; ++u) reinterpret_cast<uint2*>(s_ang)[tid + u * kConsumers] = reinterpret_cast<const uint2*>(p.rope_ang)[tid + u * kConsumers];
+      }
     }
     if (p.merge && p.gate && p.prefetch_old_rows && tid < 4) {
       // the gate values of the (row, slice) unit this CTA will merge at the end: into L2 ahead of the K/V traffic
@@ -456,11 +467,12 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           else x = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(src) + off);
           return x;
         };
-        const uint64_t so = (uint64_t)g * HD + 2 * tid;
-        if (HD == 256) { kx = ld2(p.k_new, so); vx = ld2(p.v_new, so); }
+        const uint64_t so = (uint64_t)p.items.col0[item] * p.k_new_stride + (uint64_t)g * HD + 2 * tid;
+        const uint64_t sv = (uint64_t)p.items.col0[item] * p.v_new_stride + (uint64_t)g * HD + 2 * tid;
+        if (HD == 256) { kx = ld2(p.k_new, so); vx = ld2(p.v_new, sv); }
         else {
           if (tid < 32) { kx = ld2(p.k_new, so); kxb = ld2(p.k_new, so + RHALF); }
-          if (tid < HD / 2) vx = ld2(p.v_new, so);
+          if (tid < HD / 2) vx = ld2(p.v_new, sv);
         }
       }
     } else {

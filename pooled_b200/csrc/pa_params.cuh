@@ -14,8 +14,13 @@ struct DecodeParams {
   uint32_t n_heads, G, max_seq, n_stages;
   // fused front (one token; head_dim 256 with 64 rotary dims, or head_dim 128 rotated in full): q arrives unrotated and the consumers rotate
   // it; the CTA that walks the sequence's last tile also rotates k, converts v and appends the token's row
-  uint32_t fused, append;       // append: this cache holds the new row (false on another rank's shard)
-  const void* k_new; const void* v_new;               // the token's k / v row, [n_kv * hd], dtype as q
+  // fused: 1 = one item, cos / sin in rope_ang; 2 = one token of each of several items, each CTA evaluates its own
+  // item's cos / sin (float64 sincos of pos * inv_freq, ahead of its wait).  append: bit i set = this cache holds item
+  // i's new row (clear on another rank's shard)
+  uint32_t fused, append;
+  const void* k_new; const void* v_new;               // the tokens' k / v rows, [items][n_kv * hd], dtype as q
+  uint64_t k_new_stride, v_new_stride;                // elements between the rows of consecutive items
+  const double* inv_freq;                             // theta^(-2i/n_rot), i < n_rot/2 (fused == 2)
   __half* k_cache; __half* v_cache;                   // caches of the layer
   Angle rope_ang[64];       // cos / sin of pos * theta^(-2i/n_rot), i < n_rot/2, evaluated by the host in float64
   uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends

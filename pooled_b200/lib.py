@@ -82,6 +82,7 @@ SYMBOLS = {
     "pa_shared_close": (_i, [_vp, _vp]),
     "pa_exchange_init": (_i, [_vp, _u32, _u32, C.POINTER(_vp), _u32]),
     "pa_decode_exchange": (_i, [_vp, C.POINTER(PaItem), _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
+    "pa_attn_items": (_i, [_vp, _vp, _u32, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _u64, C.c_int, _vp]),
     "pa_attn_layer_sharded": (_i, [_vp, _u32, _u32, _u32, _vp, _u64, _u64, _vp, _vp, _u64, _vp, _u64, _u64, _vp, _vp, _u64, _vp]),
     "pa_prefill": (_i, [_vp, _u32, _u32, _u32, _vp, _i, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _vp]),
     "pa_sigmoid_mul": (_i, [_vp, _vp, _u64, _vp, _u64, _u64, _u32, _vp]),

@@ -65,6 +65,8 @@ class ShardedDecoder:
         n = len(seqs_pos)
         if self.exchange == "peer" and n == 1:      # one sequence: the whole layer step is one library call
             return eng.encode_layer_sharded(li, seqs_pos[0][1], q, k, v, gate, out, seq=seqs_pos[0][0])
+        if self.exchange == "peer" and hasattr(eng, "encode_items"):   # ... and so is a batch of sequences
+            return eng.encode_items(li, seqs_pos, q, k, v, gate, out, sharded=True)
         if n > 1 and hasattr(eng, "rope_append_items"):
             # every sequence's token in one launch; rows of other shards get their q rotated only
             q_rot = eng.rope_append_items(li, seqs_pos, q, k, v)

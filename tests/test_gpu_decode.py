@@ -373,6 +373,53 @@ def test_fused_front_equals_the_three_kernel_chain_bit_for_bit(act, nH, nKV, hd,
     assert np.array_equal(caches["fused"][0], wk) and np.array_equal(caches["fused"][1], po.f16_rne(v))
 
 
+@pytest.mark.parametrize("nH,nKV,hd,n_rot,theta", [(16, 2, 256, 64, 1e7), (16, 8, 128, 128, 1e6)])
+@pytest.mark.parametrize("act", ["f16", "f32"])
+def test_batched_layer_call_equals_append_items_then_decode_bit_for_bit(act, nH, nKV, hd, n_rot, theta):
+    # pa_attn_items: one token of each of several sequences, every one at its own position, in ONE call per step (the
+    # decode kernel's fused front per item) against pa_rope_append_items + pa_decode: same cache rows, same output bits,
+    # step after step on one layer without synchronisation; the last step against the float64 oracle.
+    import torch
+    n_seqs, steps = 5, 12
+    ctx0 = [700, 64, 1, 1290, 333]      # ragged: a sequence whose new row opens a tile, one of a single row
+    td = torch.float16 if act == "f16" else torch.float32
+    rng = np.random.default_rng(23)
+    K0 = [util.normal_f16(31 + s, (ctx0[s], nKV * hd)) for s in range(n_seqs)]
+    V0 = [util.normal_f16(41 + s, (ctx0[s], nKV * hd)) for s in range(n_seqs)]
+    mk = lambda n: rng.standard_normal((steps, n_seqs, n)).astype(np.float32)
+    q, k, v, g = mk(nH * hd), mk(nKV * hd), mk(nKV * hd), mk(nH * hd)
+    if act == "f16":
+        q, k, v, g = (po.h2f(po.f16_rne(x)) for x in (q, k, v, g))
+    outs, caches = {}, {}
+    for mode in ("one_call", "two_calls"):
+        eng = _engine(nH, nKV, hd, max(ctx0) + steps + 8, act=act, n_seqs=n_seqs, n_rot=n_rot, theta=theta)
+        for s in range(n_seqs):
+            util.load_cache(eng, 0, s, po.f16_rne(K0[s]), po.f16_rne(V0[s]))
+        dq, dk, dv, dg = (util.torch_dev(x, td) for x in (q, k, v, g))
+        out = torch.empty((steps, n_seqs, nH * hd), dtype=td, device="cuda")
+        for t in range(steps):
+            sp = [(s, ctx0[s] + t) for s in range(n_seqs)]
+            if mode == "one_call":
+                eng.encode_items(0, sp, dq[t], dk[t], dv[t], dg[t], out[t])
+            else:
+                q_rot = eng.rope_append_items(0, sp, dq[t], dk[t], dv[t])
+                eng.decode(0, [(s, p, 1) for s, p in sp], q_rot, dg[t], out[t])
+        eng.sync()
+        outs[mode] = out.float().cpu().numpy()
+        caches[mode] = [util.read_cache(eng, 0, s, 0, ctx0[s] + steps) for s in range(n_seqs)]
+    for s in range(n_seqs):
+        assert np.array_equal(caches["one_call"][s][0], caches["two_calls"][s][0]) and np.array_equal(caches["one_call"][s][1], caches["two_calls"][s][1])
+    assert np.array_equal(outs["one_call"].view(np.uint32), outs["two_calls"].view(np.uint32))
+    t = steps - 1
+    for s in range(n_seqs):
+        Kc, Vc = caches["one_call"][s]
+        qr = po.rope_neox_f64(q[t, s], nH, hd, n_rot, ctx0[s] + t, theta).astype(np.float32)[None]
+        ref = po.attn_f64(qr, Kc, Vc, nH, nKV, hd, ctx0[s] + t, 1, gate=g[t, s][None])
+        util.assert_close(outs["one_call"][t, s][None], ref, f"sequence {s}")
+        wk = po.f16_rne(po.rope_neox_f64(k[t, s], nKV, hd, n_rot, ctx0[s] + t, theta))
+        assert np.array_equal(caches["one_call"][s][0][ctx0[s] + t], wk)
+
+
 @pytest.mark.parametrize("n_cols,mode", [(1, "decode"), (5, "decode"), (160, "prefill")])
 def test_layer_call_with_head_norm_is_attn_glue_kv_plus_core_plus_gate(n_cols, mode):
     # engine/wgsl/layer_fuse.js:87-146 + attn core + gate in one call: q_full (q and gate interleaved per head) and k go in

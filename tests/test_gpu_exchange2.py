@@ -44,6 +44,36 @@ def _worker(rank, world, port, ret):
                 Vf = np.concatenate([Vf, Vc[pos][None]])
                 ref = po.attn_f64(po.rope_neox_f64(q[0], nH, hd, 64, pos, 1e7)[None], Kf, Vf, nH, nKV, hd, pos, 1, g)
                 errs.append(float(np.abs(out - ref).max()))
+        # a batch of three sequences, one token each per step: one whose rows all sit on rank 0's shard (rank 1 holds
+        # nothing of it), two that have grown into rank 1's; the peer form is one library call per step
+        totals, n_seqs = [300, chunk + 77, chunk + 1900], 3
+        eng2 = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=64, rope_theta=1e7, max_seq=chunk, n_seqs=n_seqs, act_dtype=torch.float16),
+                          device=rank)
+        eng2.exchange_setup(rank, world, dist, max_rows=64)
+        Ks = [util.normal_f16(10 + s, (totals[s] + 2 * steps, nKV * hd)) for s in range(n_seqs)]
+        Vs = [util.normal_f16(20 + s, (totals[s] + 2 * steps, nKV * hd)) for s in range(n_seqs)]
+        full = [[po.np_f16_rne(Ks[s][:totals[s]]), po.np_f16_rne(Vs[s][:totals[s]])] for s in range(n_seqs)]
+        for s in range(n_seqs):
+            lo, hi = rank * chunk, min(totals[s], (rank + 1) * chunk)
+            if hi > lo:
+                eng2.cache(0, "k")[s, :hi - lo] = torch.from_numpy(full[s][0][lo:hi].view(np.int16)).cuda()
+                eng2.cache(0, "v")[s, :hi - lo] = torch.from_numpy(full[s][1][lo:hi].view(np.int16)).cuda()
+        t0 = 0
+        for mode in ("peer", "nccl"):
+            sd = ShardedDecoder(eng2, ShardPlan(world, chunk), rank, dist, exchange=mode)
+            for t in range(t0, t0 + steps):
+                sp = [(s, totals[s] + t) for s in range(n_seqs)]
+                q = util.normal_f16(300 + t, (n_seqs, nH * hd)); g = util.normal_f16(400 + t, (n_seqs, nH * hd))
+                kn = np.stack([Ks[s][totals[s] + t] for s in range(n_seqs)]); vn = np.stack([Vs[s][totals[s] + t] for s in range(n_seqs)])
+                d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.float16).cuda()
+                out = sd.step(0, sp, d(q), d(kn), d(vn), d(g)).float().cpu().numpy()
+                eng2.sync()
+                for s, pos in sp:
+                    full[s][0] = np.concatenate([full[s][0], po.f16_rne(po.rope_neox_f64(kn[s], nKV, hd, 64, pos, 1e7))[None]])
+                    full[s][1] = np.concatenate([full[s][1], po.np_f16_rne(vn[s])[None]])
+                    ref = po.attn_f64(po.rope_neox_f64(q[s], nH, hd, 64, pos, 1e7)[None], full[s][0], full[s][1], nH, nKV, hd, pos, 1, g[s:s + 1])
+                    errs.append(float(np.abs(out[s:s + 1] - ref).max()))
+            t0 += steps
         ret[rank] = max(errs)
     finally:
         dist.destroy_process_group()
