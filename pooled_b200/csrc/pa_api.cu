@@ -164,6 +164,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   ctx->tune.no_merge = getenv("POOLED_ATTN_NO_MERGE") != nullptr;
   if (const char* e = getenv("POOLED_ATTN_OWN_PREFETCH")) ctx->tune.own_prefetch = atoi(e);
   if (const char* e = getenv("POOLED_ATTN_XCH_PREFETCH")) ctx->tune.xch_prefetch = atoi(e);
+  if (const char* e = getenv("POOLED_ATTN_KV_EVICT_FIRST")) ctx->tune.kv_evict_first = atoi(e) != 0;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -720,6 +721,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   p.prefetch_old_rows = after_own_append ? 1u : 0u;
   p.early_limit = (after_own_append && ctx->inflight_layer == L) ? ctx->inflight_row0 : 0xffffffffu;
   p.pre_stages = (uint32_t)ctx->tune.pre_stages;
+  p.kv_evict_first = ctx->tune.kv_evict_first ? 1u : 0u;
   // tiles beyond the ring asked into L2 ahead of the wait: on a shard the wait spans the cross-GPU exchange of the call
   // before, a window in which HBM would otherwise idle
   p.own_prefetch = (uint32_t)std::max(0, exchange ? ctx->tune.xch_prefetch : ctx->tune.own_prefetch);
@@ -739,7 +741,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
     vp.q = q; vp.q_f16 = q_dtype == PA_F16; vp.q_col_stride = qcs; vp.q_head_stride = qhs; vp.q_lo = q_lo;
     vp.n_cols = items[0].n_cols; vp.n_heads = ctx->cfg.n_heads; vp.G = ctx->G; vp.max_seq = L->max_seq;
     vp.scale_log2 = p.scale_log2; vp.err = ctx->dev_err;
-    vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit; vp.pre_stages = p.pre_stages;
+    vp.prefetch_old_rows = after_own_append ? 1u : 0u; vp.early_limit = p.early_limit; vp.pre_stages = p.pre_stages; vp.kv_evict_first = p.kv_evict_first;
     vp.part_o = ctx->part_o; vp.part_ml = ctx->part_ml; vp.n_splits = ns; vp.lim0 = p.items.lim0[0]; vp.n_rows = max_rows; vp.col0 = 0;
     const uint64_t am = q_dtype == PA_F16 ? 7 : 3;
     if ((qcs & am) || (qhs & am) || ((uintptr_t)q & 15)) return fail(ctx, PA_EINVAL, "%s: a multi-column block needs q strides that are multiples of 16 bytes and q 16-byte aligned", who);

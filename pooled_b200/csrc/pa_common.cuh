@@ -69,6 +69,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+// The same with an L2 eviction policy for the lines it brings in.  A KV stream is read once per call: marking its
+// lines "evict first" leaves what is re-read from L2 (instructions, q, records, the next call's early tiles) in place.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, int x, int y, int z, int w, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
@@ -261,6 +274,7 @@ struct pa_ctx {
     bool verify_mma_sync = false;// POOLED_ATTN_VERIFY_MMA_SYNC: k-token blocks on the mma.sync kernel
     int own_prefetch = 0;        // POOLED_ATTN_OWN_PREFETCH=n: L2 requests for n of a decode CTA's own later tiles at entry
     int xch_prefetch = 0;        // POOLED_ATTN_XCH_PREFETCH=n: the same for calls that end in a cross-GPU exchange
+    bool kv_evict_first = true;  // POOLED_ATTN_KV_EVICT_FIRST=0: decode / verify K and V tiles enter L2 with the default policy instead of evict-first
     bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel
     uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)
   } tune;

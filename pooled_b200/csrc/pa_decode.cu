@@ -515,6 +515,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     // rows below the ones this call's columns added, and below whatever the call before may still be writing
     const uint32_t old_rows = min(n_rows - min(n_rows, n_cols), p.early_limit);
     bool waited = !p.prefetch_old_rows;
+    const uint64_t kv_policy = l2_policy_evict_first();
     if (lane == 0) {
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
@@ -574,11 +575,13 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         mbar_wait(kempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
         s_tile[s] = i;
         mbar_expect_tx(kfull + 8 * s, SLOT);
-        tma_load_3d(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s);
+        if (p.kv_evict_first) tma_load_3d_hint(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s, kv_policy);
+        else tma_load_3d(smem_u32(k_slots + s * SLOT), &tm_k, 0, y0 + (int)(i * kT), z, kfull + 8 * s);
         mbar_wait(vempty + 8 * s, ph ^ 1, s_err, WAIT_EMPTY);
         s_tile[8 + s] = i;
         mbar_expect_tx(vfull + 8 * s, SLOT);
-        tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
+        if (p.kv_evict_first) tma_load_3d_hint(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s, kv_policy);
+        else tma_load_3d(smem_u32(v_slots + s * SLOT), &tm_v, 0, y0 + (int)(i * kT), z, vfull + 8 * s);
       }
     }
     if (!g_list && n_tiles <= pre) { __syncwarp(); named_bar_sync(3, kDecThreads); }   // keeps the barrier balanced

@@ -25,6 +25,7 @@ struct DecodeParams {
   Angle rope_ang[64];       // cos / sin of pos * theta^(-2i/n_rot), i < n_rot/2, evaluated by the host in float64
   uint32_t prefetch_old_rows;  // 1: K/V tiles below the call's own new rows may be fetched before the predecessor kernel ends
   uint32_t pre_stages;         // ... but only this many per CTA before the q loads are in flight
+  uint32_t kv_evict_first;     // 1: the K / V tiles enter L2 as evict-first lines (they are read once)
   uint32_t early_limit;        // ... and only rows below this one (the call before may still be writing its own row)
   float scale_log2;         // log2(e) / sqrt(head_dim)
   // the layer the engine runs next (pa_layer_set_next): once a CTA has requested its own last tile it asks L2 for the
@@ -138,6 +139,7 @@ struct PrefillParams {
   uint32_t prefetch_old_rows;   // split-K form: K/V tiles wholly below the call's new rows may be fetched before the predecessor ends
   uint32_t early_limit;         // ... and below this row (the call before may still be writing its own row)
   uint32_t pre_stages;          // ... and only this many K tiles (one fewer V tiles) before the q loads are in flight
+  uint32_t kv_evict_first;      // split-K: 1 = the K / V tiles enter L2 as evict-first lines
 };
 
 }  // namespace pa

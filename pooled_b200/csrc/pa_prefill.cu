@@ -179,8 +179,9 @@ struct PfSmem {
   static constexpr int X_BYTES = 0;
   // softmax warpgroups: the causal prefill runs two, which take alternate KV tiles of the CTA's 128 query rows (the
   // exponentials of one tile take about as long as its two products on the tensor cores, so one group leaves the
-  // tensor pipe idle half of the time); the split-K form keeps one
-  static constexpr int NGRP = MODE == 0 ? 2 : 1;
+  // tensor pipe idle half of the time); the split-K form does the same: with one group the softmax of a tile, not the
+  // arrival of the tile from HBM, set the pace of its seven-tile loop
+  static constexpr int NGRP = 2;
   static constexpr int THREADS = 128 + 128 * NGRP;   // 4 service warps (K producer, MMA, TMEM, V producer) + the softmax warps
   static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
   static constexpr int OFF_ROW = OFF_BAR + 256;      // per-row hand-over between the softmax groups: the reference maximum, m[128]
@@ -238,8 +239,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     for (int i = 0; i < kSBuf; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
     mbar_init(BAR(Q_FULL, 0), 128 * NGRP);
-    mbar_init(BAR(Q_ISSUED, 0), 128);
-    mbar_init(BAR(Q_SENT, 0), 128);
+    mbar_init(BAR(Q_ISSUED, 0), HD >= 256 ? 128 * NGRP : 128);   // every thread that reads the staging area, after its last read
+    mbar_init(BAR(Q_SENT, 0), 128 * NGRP);
     mbar_init(BAR(M_READY, 0), 128); mbar_init(BAR(M_READY, 1), 128);
     fence_barrier_init();
   }
@@ -273,7 +274,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (SK && j == 2) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);
         mbar_wait(BAR(K_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         mbar_expect_tx(BAR(K_FULL, st), L::KV_BYTES);
-        tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(K_FULL, st));
+        if (SK && p.kv_evict_first) tma_load_3d_hint(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(K_FULL, st), l2_policy_evict_first());
+        else tma_load_3d(smem_u32(base + L::OFF_K + st * L::KV_BYTES), &tm_k, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(K_FULL, st));
       }
     }
   } else if (warp == 3) {
@@ -288,7 +290,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (SK && j == 1) mbar_wait(BAR(Q_ISSUED, 0), 0, s_err, WAIT_QFULL);   // slot 1 stages query rows until then
         mbar_wait(BAR(V_EMPTY, st), (u & 1) ^ 1, s_err, WAIT_EMPTY);
         mbar_expect_tx(BAR(V_FULL, st), L::KV_BYTES);
-        tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(V_FULL, st));
+        if (SK && p.kv_evict_first) tma_load_3d_hint(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(V_FULL, st), l2_policy_evict_first());
+        else tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(V_FULL, st));
       }
     }
   } else if (warp == 1) {
@@ -364,6 +367,12 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t sk_c = lr / p.G, sk_hh = lr % p.G;
     const uint32_t head = SK ? g * p.G + sk_hh : h;
     const bool live = SK ? (lr < p.n_cols * p.G && (PREC || !is_lo)) : row < rows_valid;
+    // keys [0, lim) are visible to this row
+    const uint32_t lim = SK ? (uint32_t)min(max(p.lim0 + (int32_t)min(sk_c, p.n_cols - 1), 0), (int32_t)p.n_rows) : p0 + row + 1;
+    // m_st: the row's reference maximum (the weights of a tile are 2^(s - m_st); it moves only when a tile's maximum
+    // passes it by more than 2^8).  With two softmax groups it travels with the tiles: the group that took tile j - 1
+    // publishes it in s_rm, the group that takes tile j picks it up there.  l_sum: this group's share of the row sum,
+    // expressed in the reference m_l.  (split-K: a split may hold no visible key of a row, hence the finite start.)
     // ---- split-K: the few query rows are fetched by all 128 threads at once, 16 bytes per request, straight into
     //      shared memory (cp.async: no registers held, every request in flight together), into the K and the V slot
     //      the producers leave alone until Q_ISSUED (32 rows each); a row's chunks are XOR-swizzled so that the
@@ -380,8 +389,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     if (early) pdl_wait();
     pdl_trigger();
     if (SK) {
-      const uint32_t pairs = p.n_cols * p.G, st_tid = tid - 128, total = pairs * q_ch;   // (one softmax group in this form)
-      for (uint32_t idx = st_tid; idx < total; idx += 128) {
+      const uint32_t pairs = p.n_cols * p.G, st_tid = tid - 128, total = pairs * q_ch;
+      for (uint32_t idx = st_tid; idx < total; idx += 128 * NGRP) {
         const uint32_t pr = idx / q_ch, c = idx % q_ch;
         const uint32_t half_ch = HD * 2 / 16;
         const bool lo_plane = planes && c >= half_ch;
@@ -394,7 +403,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       asm volatile("cp.async.commit_group;" ::: "memory");
       mbar_arrive(BAR(Q_SENT, 0));
       asm volatile("cp.async.wait_group 0;" ::: "memory");
-      named_bar_sync(1, 128);
+      named_bar_sync(1, 128 * NGRP);
     }
     const uint8_t* my_stage = stage_row(lr & 63u);
     auto stage_ld = [&](uint32_t c) { return *reinterpret_cast<const uint4*>(my_stage + ((c ^ (lr & 7u)) << 4)); };
@@ -435,9 +444,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             w[2 * i] = pack_h2(x.x, x.y); w[2 * i + 1] = pack_h2(x.z, x.w);
           }
         }
-        if (c2 == ROUNDS - 1) {
-          // this thread is done with the staging area: the producers may fetch into it (and may send the tiles they
-          // held back so that the early burst would not queue in front of the q requests)
+        if (c2 == ROUNDS - 1 || (NGRP == 2 && ROUNDS == 2)) {
+          // this thread is done with the staging area (with two groups and two rounds, each thread reads one round):
+          // the producers may fetch into it (and may send the tiles they held back so that the early burst would not
+          // queue in front of the q requests)
           fence_proxy_async();
           mbar_arrive(BAR(Q_ISSUED, 0));
         }
@@ -462,12 +472,6 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       tc_fence_before();
       mbar_arrive(BAR(Q_FULL, 0));
     }
-    // keys [0, lim) are visible to this row
-    const uint32_t lim = SK ? (uint32_t)min(max(p.lim0 + (int32_t)min(sk_c, p.n_cols - 1), 0), (int32_t)p.n_rows) : p0 + row + 1;
-    // m_st: the row's reference maximum (the weights of a tile are 2^(s - m_st); it moves only when a tile's maximum
-    // passes it by more than 2^8).  With two softmax groups it travels with the tiles: the group that took tile j - 1
-    // publishes it in s_rm, the group that takes tile j picks it up there.  l_sum: this group's share of the row sum,
-    // expressed in the reference m_l.  (split-K: a split may hold no visible key of a row, hence the finite start.)
     float m_st = SK ? -1.0e30f : -INFINITY, l_sum = 0.f, m_l = m_st;
     for (uint32_t j = wg; j < n_tiles; j += NGRP) {
       const uint32_t b = j % kSBuf, u = j / kSBuf, kv0 = (tile0 + j) * kBN;
@@ -564,11 +568,12 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       // 16 bytes apart in their bank phase), then all 128 threads write whole records, 16 consecutive bytes per
       // thread and 512 consecutive bytes per warp instruction.
       constexpr int RP = HD / 4 + 1;                                  // row pitch in float4
-      float4* xs = reinterpret_cast<float4*>(base + L::OFF_K);        // [rows][RP]
+      float4* xs = reinterpret_cast<float4*>(base + L::OFF_K + 2048);   // [rows][RP], behind the groups' row sums (s_rl, s_rr)
       unsigned long long* xslot = reinterpret_cast<unsigned long long*>(xs + 64 * RP);   // [64] record of each row, ~0: none
-      if (!is_lo && lr < 64) xslot[lr] = writer ? (unsigned long long)slot : ~0ull;
+      if (!is_lo && lr < 64 && wg == 0) xslot[lr] = writer ? (unsigned long long)slot : ~0ull;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
+        if (NGRP == 2 && (uint32_t)(c & 1) != wg) continue;   // the groups share the columns out
         float o[32];
         tmem_ld32(t_o + c * 32 + lane_addr, o);
         if (PREC) {
@@ -580,13 +585,13 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
           for (int i = 0; i < 8; ++i) xs[lr * RP + c * 8 + i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
       }
-      named_bar_sync(1, 128);
-      for (uint32_t idx = tid - 128; idx < 64 * (HD / 4); idx += 128) {
+      named_bar_sync(1, 128 * NGRP);
+      for (uint32_t idx = tid - 128; idx < 64 * (HD / 4); idx += 128 * NGRP) {
         const uint32_t rr = idx / (HD / 4), c4 = idx % (HD / 4);
         const unsigned long long sl = xslot[rr];
         if (sl != ~0ull) reinterpret_cast<float4*>(p.part_o + sl * HD)[c4] = xs[rr * RP + c4];
       }
-      if (writer) { p.part_ml[slot * 2] = m_st * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
+      if (writer && wg == 0) { p.part_ml[slot * 2] = (NGRP == 2 ? s_rm[row] : m_st) * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
     } else {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
