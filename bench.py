@@ -57,7 +57,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (same per-launch shape as the bench's; the captures only use fewer layers)
-CAPTURED_TRAFFIC = {"c2": 67.32e6 + 0.62e6, "c4": 67.34e6 + 1.56e6}
+CAPTURED_TRAFFIC = {"c2": 67.36e6 + 0.74e6, "c4": 67.35e6 + 1.27e6}
 MIN_TIMED_S = 0.5
 
 
