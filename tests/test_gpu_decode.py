@@ -290,6 +290,16 @@ def test_unsupported_shapes_are_refused_with_a_message():
         eng.decode(0, [(0, 100, 9)], q)     # 9 columns x 8 heads = 72 query rows per kv head
     assert e.value.code == -2 and "pa_prefill" in str(e.value)
     assert eng.stats()["calls"] == 0
+    # the batched layer call: one sequence past the layer's rows, and more items than the context was created for
+    eng2 = _engine(16, 2, 256, 1024, act="f32", n_seqs=2, max_cols=2)
+    z = lambda n, w: torch.zeros((n, w), device="cuda")
+    with pytest.raises(PaError) as e:
+        eng2.encode_items(0, [(0, 10), (1, 1024)], z(2, 4096), z(2, 512), z(2, 512))
+    assert "max_seq" in str(e.value)
+    with pytest.raises(PaError) as e:
+        eng2.encode_items(0, [(0, 10), (1, 11), (0, 12)], z(3, 4096), z(3, 512), z(3, 512))
+    assert "max_cols" in str(e.value)
+    assert eng2.stats()["calls"] == 0
 
 
 def test_host_buffer_entry_points_match_the_device_path():
