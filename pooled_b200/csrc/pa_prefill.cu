@@ -160,7 +160,6 @@ __device__ __forceinline__ void umma_commit_elected(uint32_t leader, uint32_t ba
       ::"r"(bar), "r"(leader) : "memory");
 }
 
-constexpr int kSBuf = 3;     // S / P tiles in tensor memory: S(j+2) is formed while softmax(j) runs and P(j-1) is consumed
 
 // MODE 0: causal prefill, one CTA per (128 query columns, q head).
 // MODE 1 / 2: split-K form for a k-token verify block: one CTA per (split of the KV sequence, kv head); the rows of the
@@ -172,25 +171,39 @@ constexpr int kSBuf = 3;     // S / P tiles in tensor memory: S(j+2) is formed w
 
 template <int HD, int MODE>
 struct PfSmem {
-  static constexpr int NK = 3, NV = MODE == 0 ? 3 : 2;   // K ring and V ring depth (the scores run two tiles ahead); split-K
-                                                         // leaves 32 KB free so that its CTAs can join SMs that still run a small kernel
+  // S / P tiles in tensor memory.  The loop S(j) -> softmax(j) -> P V(j) -> S(j + SBUF) is a cycle of fixed length
+  // (about 2.9 us at head_dim 256): the tile rate is SBUF tiles per cycle.  The causal prefill at head_dim 256 takes
+  // four (Q then comes from shared memory only: as an A operand in tensor memory it was no faster, and its 64 columns
+  // are the fourth tile); the other forms keep three and the lower half of Q in tensor memory.
+  static constexpr int SBUF = (MODE == 0 && HD == 256) ? 4 : 3;
+  // K ring and V ring depth (the scores run SBUF - 1 tiles ahead).  Split-K leaves 32 KB free so that its CTAs can
+  // join SMs that still run a small kernel; the four-tile prefill gives a V slot to the other half of Q.
+  static constexpr int NK = 3, NV = (MODE != 0 || SBUF == 4) ? 2 : 3;
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
-  static constexpr int QS_BYTES = HD * 128;         // upper half of the head dims of Q: [HD/128][128 rows][128 B]
+  // tensor memory columns: the first TQC 64-dim chunks of Q (32 columns of f16 pairs each) | S tiles (64 each; P
+  // overwrites the first 32 of its S) | O (HD).  HD 256: 64 + 192 + 256, or 0 + 256 + 256 = 512.
+  static constexpr int TQC = SBUF == 4 ? 0 : (HD == 64 ? 1 : HD / 128);
+  static constexpr int QS_BYTES = (HD / 64 - TQC > 0 ? HD / 64 - TQC : 1) * 128 * 128;   // the chunks of Q not in tensor memory: [chunk][128 rows][128 B]
   static constexpr int X_BYTES = 0;
   // softmax warpgroups: the causal prefill runs two, which take alternate KV tiles of the CTA's 128 query rows (the
   // exponentials of one tile take about as long as its two products on the tensor cores, so one group leaves the
   // tensor pipe idle half of the time); the split-K form does the same: with one group the softmax of a tile, not the
   // arrival of the tile from HBM, set the pace of its seven-tile loop
   static constexpr int NGRP = 2;
-  static constexpr int THREADS = 128 + 128 * NGRP;   // 4 service warps (K producer, MMA, TMEM, V producer) + the softmax warps
+  // 4 service warps (K producer, scores issuer, TMEM allocator + P V issuer, V producer) + the softmax warps + a second
+  // scores issuer (the last warp).  A score product is HD/16 instructions of 128 x 64 x 16 each: 32 cycles of tensor
+  // work apiece against about twice that to issue one, so a single issuing thread, not the tensor cores, set the
+  // loop's pace; two threads take alternate tiles (a tile's instructions stay in one thread: the order of its sums is
+  // fixed).
+  static constexpr int QK_ISSUERS = MODE == 0 ? 2 : 1;   // (the split-K form's 168 registers leave no room for a 13th warp)
+  static constexpr int THREADS = 128 + 128 * NGRP + 32 * (QK_ISSUERS - 1);
+  static constexpr int QK2_WARP = 4 + 4 * NGRP;      // the second scores issuer
   static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
   static constexpr int OFF_ROW = OFF_BAR + 256;      // per-row hand-over between the softmax groups: the reference maximum, m[128]
   static constexpr int TOTAL = 1024 + OFF_ROW + 128 * 4;
   static_assert(TOTAL <= 227 * 1024, "shared memory of one CTA");
-  // tensor memory columns: the first TQC 64-dim chunks of Q (32 columns of f16 pairs each: half of the row, all of it
-  // at head_dim 64) | S0 S1 S2 (64 each; P overwrites the first 32 of its S) | O (HD).  HD 256: 64 + 192 + 256 = 512.
-  static constexpr int TQC = HD == 64 ? 1 : HD / 128;
-  static constexpr int T_Q = 0, T_S = TQC * 32, T_O = TQC * 32 + kSBuf * kBN;
+  static constexpr int T_Q = 0, T_S = TQC * 32, T_O = TQC * 32 + SBUF * kBN;
+  static_assert(T_O + HD <= 512, "tensor memory columns");
   static constexpr int TMEM_COLS = 512;
 };
 
@@ -200,11 +213,11 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
   constexpr bool SK = MODE != 0, PREC = MODE == 2;
-  constexpr int NK = L::NK, NV = L::NV, NGRP = L::NGRP;
+  constexpr int NK = L::NK, NV = L::NV, NGRP = L::NGRP, kSBuf = L::SBUF;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::OFF_BAR);
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 28);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(bars + 31);
   volatile uint32_t* s_err = s_tmem + 1;
   float* s_rm = reinterpret_cast<float*>(base + L::OFF_ROW);   // [128] reference maximum of each query row (scaled, log2 units)
   // [2][128] each group's row sum and [2][128] the reference maximum it is expressed in: exchanged once, after the
@@ -212,8 +225,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   float* s_rl = reinterpret_cast<float*>(base + L::OFF_K);
   float* s_rr = s_rl + 256;
   const uint32_t bar0 = smem_u32(bars);
-  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 15, PV_DONE = 18, O_DONE = 21, Q_FULL = 22, Q_ISSUED = 23, Q_SENT = 24,
-         M_READY = 25 /* [2]: group g has published the row maxima after its tile */ };
+  enum { K_FULL = 0, K_EMPTY = 3, V_FULL = 6, V_EMPTY = 9, S_FULL = 12, P_FULL = 12 + kSBuf, PV_DONE = 12 + 2 * kSBuf, O_DONE = 12 + 3 * kSBuf,
+         Q_FULL = O_DONE + 1, Q_ISSUED = O_DONE + 2, Q_SENT = O_DONE + 3,
+         M_READY = O_DONE + 4 /* [2]: group g has published the row maxima after its tile */ };
+  static_assert(M_READY + 2 <= 31, "barrier slots");
   uint8_t* q_s = base + L::OFF_Q;
   auto BAR = [&](int which, int idx) { return bar0 + 8u * (uint32_t)(which + idx); };
 
@@ -294,8 +309,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         else tma_load_3d(smem_u32(base + L::OFF_V + st * L::KV_BYTES), &tm_v, 0, (int)((tile0 + j) * kBN), (int)(g * CH), BAR(V_FULL, st));
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer, scores ----
+  } else if (warp == 1 || (L::QK_ISSUERS == 2 && warp == L::QK2_WARP)) {
+    // ------------------------------------------------------------------ MMA issuers, scores ----
     // S(j) = Q K(j)^T.  The whole warp runs the loop and the elected lane issues.  Issuing blocks while the tensor
     // cores' queue is full, so one thread issuing both products of every tile spends its time in turns on each and
     // the waits in between leave the queue empty; with the scores here and P V in warp 2 there are two queues' worth
@@ -312,7 +327,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
       mbar_wait(BAR(Q_FULL, 0), 0, s_err, WAIT_QFULL);
       tc_fence_after();
-      for (uint32_t j = 0; j < n_tiles; ++j) {
+      for (uint32_t j = (warp == 1 ? 0u : 1u); j < n_tiles; j += L::QK_ISSUERS) {
         const uint32_t sb = j % kSBuf, st = j % NK;
         if (j >= (uint32_t)kSBuf) mbar_wait(BAR(PV_DONE, sb), ((j - kSBuf) / kSBuf) & 1, s_err, WAIT_MMA);
         mbar_wait(BAR(K_FULL, st), (j / NK) & 1, s_err, WAIT_KFULL);
@@ -327,7 +342,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 #pragma unroll
         for (int ks = TS_STEPS; ks < HD / 16; ++ks)
           umma_f16_ss(leader, ts, q_desc + (uint64_t)(((((ks - TS_STEPS) >> 2)) * (kBM * 128) + (ks & 3) * 32) >> 4),
-                      kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, 1u);
+                      kd + (uint64_t)(((ks >> 2) * (kBN * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0 ? 1u : 0u);
         umma_commit_elected(leader, BAR(K_EMPTY, st));
         umma_commit_elected(leader, BAR(S_FULL, sb));
       }
