@@ -118,6 +118,21 @@ def test_config3_shape_reduced(n_cols, act, gate):
     print(f"prefill {n_cols} {act}: max-abs {ma:.2e} max-rel {mr:.2e}")
 
 
+@pytest.mark.parametrize("nH,nKV,hd", [(24, 4, 256), (16, 8, 128)])
+def test_prefill_gives_the_same_bits_twice(nH, nKV, hd):
+    # two threads issue the score products of alternate tiles and two softmax groups take alternate tiles: the order of
+    # every sum is fixed all the same, so a repeated pass over the same cache carries the same bits
+    import torch
+    n_cols = 1500
+    eng = _engine(nH, nKV, hd, n_cols + 8, act="f16", max_cols=n_cols, rope_mode="f64")
+    q, k, v, g = _inputs(5, nH, nKV, hd, n_cols)
+    d = lambda a: util.torch_dev(a, torch.float16)
+    dq, dk, dv, dg = d(q), d(k), d(v), d(g)
+    outs = [eng.encode_layer(0, 0, dq, dk, dv, dg, mode="prefill").cpu().numpy().view(np.uint16) for _ in range(3)]
+    eng.sync()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+
+
 def test_chunked_prefill_and_prefill_vs_decode():
     # a second chunk against the first chunk's rows; every column also equals the decode kernel's answer at its position
     import torch
