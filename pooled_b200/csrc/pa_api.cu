@@ -21,7 +21,7 @@ cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStre
 cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st);
 cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t n_heads, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
-cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
+cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q, cudaStream_t st);
 cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
 cudaError_t launch_kv_store(const KvStoreParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_decode_any(const AnyDecodeParams& p, int format, dim3 grid, cudaStream_t st);
@@ -165,6 +165,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   if (const char* e = getenv("POOLED_ATTN_OWN_PREFETCH")) ctx->tune.own_prefetch = atoi(e);
   if (const char* e = getenv("POOLED_ATTN_XCH_PREFETCH")) ctx->tune.xch_prefetch = atoi(e);
   if (const char* e = getenv("POOLED_ATTN_KV_EVICT_FIRST")) ctx->tune.kv_evict_first = atoi(e) != 0;
+  if (const char* e = getenv("POOLED_ATTN_NO_Q_TMA")) ctx->tune.no_q_tma = atoi(e) != 0;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -879,8 +880,15 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   const uint64_t seq_off = (uint64_t)seq * L->max_seq * ctx->kv_dim;
   if (int rc = make_cache_map(ctx, &tm_k, L->k + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
   if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
+  // f16 query rows at head_dim 256 travel by TMA: a map of q as [n_cols][q_col_stride] in 64-element chunks, the same
+  // shape of map as a cache's (rows past n_cols read as zeros)
+  CUtensorMap tm_q = tm_k;
+  if (q_dtype == PA_F16 && ctx->cfg.head_dim == 256 && !(qcs & 63) && !(qhs & 63) && !ctx->tune.no_q_tma) {
+    if (int rc = make_cache_map(ctx, &tm_q, const_cast<void*>(q), n_cols, (uint32_t)qcs, ctx->cfg.head_dim, 128)) return rc;
+    p.q_tma = 1;
+  }
   timing_mark(ctx, st, 0);
-  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, st));
+  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, tm_q, st));
   timing_mark(ctx, st, 1);
   ctx->stats.kernel_launches++; ctx->stats.calls++;
   ctx->stats.kv_bytes_streamed += 2ull * (pos + n_cols) * ctx->kv_dim * 2;

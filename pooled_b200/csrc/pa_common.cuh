@@ -274,6 +274,7 @@ struct pa_ctx {
     bool verify_mma_sync = false;// POOLED_ATTN_VERIFY_MMA_SYNC: k-token blocks on the mma.sync kernel
     int own_prefetch = 0;        // POOLED_ATTN_OWN_PREFETCH=n: L2 requests for n of a decode CTA's own later tiles at entry
     int xch_prefetch = 0;        // POOLED_ATTN_XCH_PREFETCH=n: the same for calls that end in a cross-GPU exchange
+    bool no_q_tma = false;       // POOLED_ATTN_NO_Q_TMA=1: the prefill kernel's query rows through the softmax threads' registers
     bool kv_evict_first = true;  // POOLED_ATTN_KV_EVICT_FIRST=0: decode / verify K and V tiles enter L2 with the default policy instead of evict-first
     bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel
     uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)

@@ -209,7 +209,8 @@ struct PfSmem {
 
 template <int HD, int MODE>
 __global__ void __launch_bounds__(PfSmem<HD, MODE>::THREADS, 1)
-pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
+                  const PrefillParams p) {
   using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
   constexpr bool SK = MODE != 0, PREC = MODE == 2;
@@ -247,13 +248,16 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     n_tiles = min(tiles, tile0 + tps) - tile0;
   }
 
+  // prefill at head_dim 256 with f16 q: the 128 query rows (64 KB) land in shared memory, in the layout the score
+  // products read, by one TMA copy issued at once, instead of through the softmax threads' registers
+  const bool q_by_tma = MODE == 0 && L::TQC == 0 && p.q_tma;
   if (warp == 1 && lane == 0) {
     *s_err = 0;
     for (int i = 0; i < NK; ++i) { mbar_init(BAR(K_FULL, i), 1); mbar_init(BAR(K_EMPTY, i), 1); }
     for (int i = 0; i < NV; ++i) { mbar_init(BAR(V_FULL, i), 1); mbar_init(BAR(V_EMPTY, i), 1); }
     for (int i = 0; i < kSBuf; ++i) { mbar_init(BAR(S_FULL, i), 1); mbar_init(BAR(P_FULL, i), 128); mbar_init(BAR(PV_DONE, i), 1); }
     mbar_init(BAR(O_DONE, 0), 1);
-    mbar_init(BAR(Q_FULL, 0), 128 * NGRP);
+    mbar_init(BAR(Q_FULL, 0), q_by_tma ? 1 : 128 * NGRP);
     mbar_init(BAR(Q_ISSUED, 0), HD >= 256 ? 128 * NGRP : 128);   // every thread that reads the staging area, after its last read
     mbar_init(BAR(Q_SENT, 0), 128 * NGRP);
     mbar_init(BAR(M_READY, 0), 128); mbar_init(BAR(M_READY, 1), 128);
@@ -278,6 +282,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ------------------------------------------------------------------ TMA producer, K ----
     if (lane == 0) {
       prefetch_tmap(&tm_k);
+      if (q_by_tma) {
+        mbar_expect_tx(BAR(Q_FULL, 0), (HD / 64) * kBM * 128);
+        tma_load_3d(smem_u32(q_s), &tm_q, 0, (int)c0, (int)(h * (p.q_head_stride / 64)), BAR(Q_FULL, 0));
+      }
       bool waited = !early;
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t st = j % NK, u = j / NK;
@@ -423,7 +431,7 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint8_t* my_stage = stage_row(lr & 63u);
     auto stage_ld = [&](uint32_t c) { return *reinterpret_cast<const uint4*>(my_stage + ((c ^ (lr & 7u)) << 4)); };
     // ---- this thread's Q row -> f16 pairs: lower half of the dims to tensor memory, upper half to shared memory ----
-    {
+    if (!q_by_tma) {
       const uint64_t off = (uint64_t)(SK ? p.col0 + (live ? sk_c : 0) : c0 + (live ? row : 0)) * p.q_col_stride + (uint64_t)head * p.q_head_stride;
       // ER elements per round (the loads of a round are all in flight together), in 64-dim chunks: the first TQC chunks
       // of the row go to tensor memory (32 columns each), the others to shared memory (one 128-byte row chunk each)
@@ -651,7 +659,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ctx->cfg.head_dim == 128 || ctx->cfg.head_dim == 64; }
 
 template <int HD, int MODE>
-static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, dim3 grid, cudaStream_t st) {
+static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q, dim3 grid,
+                             cudaStream_t st) {
   static bool attr_set[64] = {};
   const int dev = L->ctx->device & 63;
   if (!attr_set[dev]) {
@@ -660,18 +669,19 @@ static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CU
     attr_set[dev] = true;
   }
   if (MODE == 0) {
-    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, p);
+    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, tm_q, p);
     return cudaGetLastError();
   }
-  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, p);
+  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, tm_q, p);
 }
 
-cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
+cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
+                           cudaStream_t st) {
   const dim3 grid((p.n_cols + kBM - 1) / kBM, p.n_heads);
   switch (L->ctx->cfg.head_dim) {
-    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, grid, st);
-    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, grid, st);
-    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, grid, st);
+    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, tm_q, grid, st);
+    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, tm_q, grid, st);
+    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, tm_q, grid, st);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -681,8 +691,8 @@ cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUten
   const dim3 grid(p.n_splits, n_kv);
   const bool precise = !(L->ctx->cfg.flags & PA_FLAG_FAST);
   if (L->ctx->cfg.head_dim == 256)
-    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, grid, st);
-  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, grid, st);
+    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, tm_k, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, tm_k, grid, st);   // (no map of q in this form)
+  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, tm_k, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, tm_k, grid, st);
 }
 
 }  // namespace pa
