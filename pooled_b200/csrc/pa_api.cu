@@ -21,7 +21,8 @@ cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStre
 cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st);
 cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t n_heads, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
-cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q, cudaStream_t st);
+cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
+                           const CUtensorMap& tm_o, cudaStream_t st);
 cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
 cudaError_t launch_kv_store(const KvStoreParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_decode_any(const AnyDecodeParams& p, int format, dim3 grid, cudaStream_t st);
@@ -166,6 +167,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   if (const char* e = getenv("POOLED_ATTN_XCH_PREFETCH")) ctx->tune.xch_prefetch = atoi(e);
   if (const char* e = getenv("POOLED_ATTN_KV_EVICT_FIRST")) ctx->tune.kv_evict_first = atoi(e) != 0;
   if (const char* e = getenv("POOLED_ATTN_NO_Q_TMA")) ctx->tune.no_q_tma = atoi(e) != 0;
+  if (const char* e = getenv("POOLED_ATTN_NO_OUT_TMA")) ctx->tune.no_out_tma = atoi(e) != 0;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
     pa_destroy(ctx);
@@ -887,8 +889,14 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
     if (int rc = make_cache_map(ctx, &tm_q, const_cast<void*>(q), n_cols, (uint32_t)qcs, ctx->cfg.head_dim, 128)) return rc;
     p.q_tma = 1;
   }
+  // ... and f16 output tiles leave by TMA (any head_dim the kernel takes; gate, if any, f16 with 16-byte aligned rows)
+  CUtensorMap tm_o = tm_k;
+  if (ctx->cfg.act_dtype == PA_F16 && !(ocs & 63) && !ctx->tune.no_out_tma && (!gate || (!(gcs & 7) && !(ghs & 7) && !((uintptr_t)gate & 15)))) {
+    if (int rc = make_cache_map(ctx, &tm_o, out, n_cols, (uint32_t)ocs, ctx->cfg.head_dim, 128)) return rc;
+    p.out_tma = 1;
+  }
   timing_mark(ctx, st, 0);
-  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, tm_q, st));
+  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, tm_q, tm_o, st));
   timing_mark(ctx, st, 1);
   ctx->stats.kernel_launches++; ctx->stats.calls++;
   ctx->stats.kv_bytes_streamed += 2ull * (pos + n_cols) * ctx->kv_dim * 2;

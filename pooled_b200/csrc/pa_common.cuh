@@ -82,6 +82,14 @@ __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
       : "memory");
 }
+// 3-D tiled TMA store from this CTA's shared memory (rows and chunks outside the tensor are not written), as a bulk
+// group of the issuing thread; tma_store_wait_read returns once the group's shared-memory reads are done.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(src) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, int x, int y, int z, int w, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
@@ -275,6 +283,7 @@ struct pa_ctx {
     int own_prefetch = 0;        // POOLED_ATTN_OWN_PREFETCH=n: L2 requests for n of a decode CTA's own later tiles at entry
     int xch_prefetch = 0;        // POOLED_ATTN_XCH_PREFETCH=n: the same for calls that end in a cross-GPU exchange
     bool no_q_tma = false;       // POOLED_ATTN_NO_Q_TMA=1: the prefill kernel's query rows through the softmax threads' registers
+    bool no_out_tma = false;     // POOLED_ATTN_NO_OUT_TMA=1: ... and its output rows by per-thread stores
     bool kv_evict_first = true;  // POOLED_ATTN_KV_EVICT_FIRST=0: decode / verify K and V tiles enter L2 with the default policy instead of evict-first
     bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel
     uint32_t wait_polls = 0;     // pa_set_wait_limit: limit of the cross-GPU exchange wait (0: the built-in limit)

@@ -141,6 +141,7 @@ struct PrefillParams {
   uint32_t pre_stages;          // ... and only this many K tiles (one fewer V tiles) before the q loads are in flight
   uint32_t kv_evict_first;      // split-K: 1 = the K / V tiles enter L2 as evict-first lines
   uint32_t q_tma;               // prefill, head_dim 256, f16 q: the CTA's 128 query rows come by one TMA copy (tm_q)
+  uint32_t out_tma;             // prefill, f16 out: the CTA's output tile leaves through shared memory by one TMA store (tm_o)
 };
 
 }  // namespace pa

@@ -210,7 +210,7 @@ struct PfSmem {
 template <int HD, int MODE>
 __global__ void __launch_bounds__(PfSmem<HD, MODE>::THREADS, 1)
 pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
-                  const PrefillParams p) {
+                  const __grid_constant__ CUtensorMap tm_o, const PrefillParams p) {
   using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
   constexpr bool SK = MODE != 0, PREC = MODE == 2;
@@ -615,6 +615,46 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (sl != ~0ull) reinterpret_cast<float4*>(p.part_o + sl * HD)[c4] = xs[rr * RP + c4];
       }
       if (writer && wg == 0) { p.part_ml[slot * 2] = (NGRP == 2 ? s_rm[row] : m_st) * 0.6931471805599453f; p.part_ml[slot * 2 + 1] = l_sum; }
+    } else if (MODE == 0 && p.out_tma) {
+      // The output tile leaves as the query tile came: through shared memory in the TMA layout ([64-dim chunk][row][128 B],
+      // 16-byte pieces XOR-swizzled by the row), one bulk tensor store for the CTA.  The K ring is idle (every product
+      // has retired); the tile sits behind the row sums the groups have just exchanged there.  Rows past the prompt's
+      // end are not written: the map ends at n_cols.  (A lane storing its own row issues 16-byte stores 12 KB apart.)
+      uint8_t* o_s = base + L::OFF_K + 2048;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        if (NGRP == 2 && (uint32_t)(c & 1) != wg) continue;   // the groups share the columns out
+        float o[32];
+        tmem_ld32(t_o + c * 32 + lane_addr, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= inv_l;
+        if (p.gate && row < rows_valid) {
+          const uint64_t go = (uint64_t)col * p.gate_col_stride + (uint64_t)h * p.gate_head_stride + c * 32;
+          const uint4* gp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.gate) + go);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 gq = gp[i];
+            const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 gv = __half22float2(*reinterpret_cast<const __half2*>(&gw[k]));
+              o[8 * i + 2 * k] *= 1.0f / (1.0f + __expf(-gv.x));
+              o[8 * i + 2 * k + 1] *= 1.0f / (1.0f + __expf(-gv.y));
+            }
+          }
+        }
+        uint8_t* dst = o_s + (c >> 1) * (kBM * 128) + row * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + i) ^ (row & 7)) << 4)) =
+              make_uint4(pack_h2(o[8 * i], o[8 * i + 1]), pack_h2(o[8 * i + 2], o[8 * i + 3]), pack_h2(o[8 * i + 4], o[8 * i + 5]), pack_h2(o[8 * i + 6], o[8 * i + 7]));
+      }
+      fence_proxy_async();
+      named_bar_sync(1, 128 * NGRP);
+      if (tid == 128) {
+        tma_store_3d(&tm_o, 0, (int)c0, (int)(h * (HD / 64)), smem_u32(o_s));
+        tma_store_wait_read();
+      }
     } else {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
@@ -659,8 +699,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ctx->cfg.head_dim == 128 || ctx->cfg.head_dim == 64; }
 
 template <int HD, int MODE>
-static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q, dim3 grid,
-                             cudaStream_t st) {
+static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
+                             const CUtensorMap& tm_o, dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {};
   const int dev = L->ctx->device & 63;
   if (!attr_set[dev]) {
@@ -669,19 +709,19 @@ static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CU
     attr_set[dev] = true;
   }
   if (MODE == 0) {
-    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, tm_q, p);
+    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, tm_q, tm_o, p);
     return cudaGetLastError();
   }
-  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, tm_q, p);
+  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, tm_q, tm_o, p);
 }
 
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
-                           cudaStream_t st) {
+                           const CUtensorMap& tm_o, cudaStream_t st) {
   const dim3 grid((p.n_cols + kBM - 1) / kBM, p.n_heads);
   switch (L->ctx->cfg.head_dim) {
-    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, tm_q, grid, st);
-    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, tm_q, grid, st);
-    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, tm_q, grid, st);
+    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, tm_q, tm_o, grid, st);
+    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, tm_q, tm_o, grid, st);
+    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, tm_q, tm_o, grid, st);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -691,8 +731,8 @@ cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUten
   const dim3 grid(p.n_splits, n_kv);
   const bool precise = !(L->ctx->cfg.flags & PA_FLAG_FAST);
   if (L->ctx->cfg.head_dim == 256)
-    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, tm_k, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, tm_k, grid, st);   // (no map of q in this form)
-  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, tm_k, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, tm_k, grid, st);
+    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st);   // (no maps of q and out in this form)
+  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st);
 }
 
 }  // namespace pa
