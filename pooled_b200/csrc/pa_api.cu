@@ -19,10 +19,11 @@ cudaError_t launch_combine(int head_dim, const CombineParams& p, uint32_t rows, 
 cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st);
+bool rope_vec_applies(const RopeParams& p, uint32_t n_cols);
 cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t n_heads, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
-                           const CUtensorMap& tm_o, cudaStream_t st);
+                           const CUtensorMap& tm_o, const CUtensorMap& tm_q2, cudaStream_t st);
 cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, uint32_t n_kv, cudaStream_t st);
 cudaError_t launch_kv_store(const KvStoreParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_decode_any(const AnyDecodeParams& p, int format, dim3 grid, cudaStream_t st);
@@ -460,7 +461,8 @@ static int ensure_angles(pa_ctx* ctx, uint32_t pos, uint32_t n_cols, cudaStream_
 
 static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, uint64_t qcs, uint64_t qhs,
                             uint32_t q_heads, void* q_out, uint64_t q_out_cs, const void* k, const void* v, uint64_t kvcs, const float* cs_table,
-                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false, uint64_t vcs = 0) {
+                            uint32_t mode, int in_f16, cudaStream_t st, int q_out_f16 = 0, bool in_layer_call = false, uint64_t vcs = 0,
+                            bool* q_rot_only = nullptr) {   // in: write only the rotated dims of q if the kernel can; out: whether it will
   if (L && L->kv_format != PA_KV_F16) {
     // int8 / f32 caches: q rotated as usual; k rotated into the context's f32 scratch (the rotation kernel's q path,
     // with the kv heads as its heads), then the format's own store kernel -- attn_glue followed by kv_store_q8
@@ -505,6 +507,10 @@ static int rope_append_impl(pa_layer* L, pa_ctx* ctx, uint32_t seq, uint32_t pos
       if (int rc = ensure_angles(ctx, pos, n_cols, st)) return rc;
       p.angles = ctx->angles;
     }
+  }
+  if (q_rot_only) {
+    *q_rot_only = *q_rot_only && rope_vec_applies(p, n_cols);
+    p.q_rot_only = *q_rot_only ? 1u : 0u;
   }
   CU_TRY(ctx, launch_rope_append(p, n_cols, st));
   ctx->stats.kernel_launches++;
@@ -854,8 +860,15 @@ extern "C" int pa_merge(pa_ctx* ctx, const float* parts, uint32_t n_parts, uint3
   return PA_OK;
 }
 
+// the caller's own (unrotated) f16 q of a layer call whose RoPE kernel wrote only the rotated dims of the rotated q
+struct PlainQ { const void* q; uint64_t cs, hs; };
+
+static bool q_tma_ok(const pa_ctx* ctx, int q_dtype, uint64_t qcs, uint64_t qhs, const void* q) {
+  return q_dtype == PA_F16 && ctx->cfg.head_dim == 256 && !(qcs & 63) && !(qhs & 63) && !((uintptr_t)q & 15) && !ctx->tune.no_q_tma;
+}
+
 static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, const void* q, int q_dtype, uint64_t qcs, uint64_t qhs, const void* gate,
-                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, cudaStream_t st) {
+                        uint64_t gcs, uint64_t ghs, void* out, uint64_t ocs, cudaStream_t st, const PlainQ* plain = nullptr) {
   pa_ctx* ctx = L->ctx;
   if (!q || !out) return fail(ctx, PA_EINVAL, "pa_prefill: null q or out");
   if (L->kv_format != PA_KV_F16) {   // every column attended on its own, as the reference's kernels for these formats do
@@ -884,8 +897,14 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
   if (int rc = make_cache_map(ctx, &tm_v, L->v + seq_off, (uint64_t)p.pos + n_cols, ctx->kv_dim, ctx->cfg.head_dim, 64)) return rc;
   // f16 query rows at head_dim 256 travel by TMA: a map of q as [n_cols][q_col_stride] in 64-element chunks, the same
   // shape of map as a cache's (rows past n_cols read as zeros)
-  CUtensorMap tm_q = tm_k;
-  if (q_dtype == PA_F16 && ctx->cfg.head_dim == 256 && !(qcs & 63) && !(qhs & 63) && !ctx->tune.no_q_tma) {
+  CUtensorMap tm_q = tm_k, tm_q2 = tm_k;
+  if (plain) {
+    // the rotated chunks of a head from the rotated q, the others from the caller's q (the caller checked q_tma_ok for both)
+    const uint32_t rot = ctx->cfg.n_rot;
+    if (int rc = make_cache_map(ctx, &tm_q, const_cast<void*>(q), n_cols, (uint32_t)qcs, rot, 128)) return rc;
+    if (int rc = make_cache_map(ctx, &tm_q2, const_cast<void*>(plain->q), n_cols, (uint32_t)plain->cs, ctx->cfg.head_dim - rot, 128)) return rc;
+    p.q_tma = 2; p.q_rot_chunks = rot / 64; p.q2_head_stride = plain->hs;
+  } else if (q_tma_ok(ctx, q_dtype, qcs, qhs, q)) {
     if (int rc = make_cache_map(ctx, &tm_q, const_cast<void*>(q), n_cols, (uint32_t)qcs, ctx->cfg.head_dim, 128)) return rc;
     p.q_tma = 1;
   }
@@ -896,7 +915,7 @@ static int prefill_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols
     p.out_tma = 1;
   }
   timing_mark(ctx, st, 0);
-  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, tm_q, tm_o, st));
+  CU_TRY(ctx, launch_prefill(L, p, tm_k, tm_v, tm_q, tm_o, tm_q2, st));
   timing_mark(ctx, st, 1);
   ctx->stats.kernel_launches++; ctx->stats.calls++;
   ctx->stats.kv_bytes_streamed += 2ull * (pos + n_cols) * ctx->kv_dim * 2;
@@ -1033,13 +1052,20 @@ static int layer_impl(pa_layer* L, uint32_t seq, uint32_t pos, uint32_t n_cols, 
     pa_item it{seq, pos, 1, 0};
     return decode_impl(L, &it, 1, q, (int)ctx->cfg.act_dtype, qcs, qhs, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", true, false, &fz);
   }
-  // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic)
+  // the prefill kernel feeds q to the tensor cores as f16, so its rotated q is stored as f16 (half the traffic); and
+  // where that kernel fetches its query rows by TMA, the dims no rotation touches (192 of 256 in the hybrid models)
+  // are not copied at all: the kernel takes those chunks from the caller's q and only the rotated chunk from q_rot
+  const uint32_t rot = ctx->cfg.n_rot;
+  bool rot_only = prefill && !ctx->core_only && ctx->cfg.act_dtype == PA_F16 && ctx->cfg.rope_mode == PA_ROPE_F64 && rot >= 64 && rot % 64 == 0 &&
+                  rot < ctx->cfg.head_dim && q_tma_ok(ctx, PA_F16, qcs, qhs, q) && q_tma_ok(ctx, PA_F16, ctx->q_dim, ctx->cfg.head_dim, ctx->q_rot);
   if (!ctx->core_only)
     if (int rc = rope_append_impl(L, ctx, seq, pos, n_cols, q, qcs, qhs, ctx->cfg.n_heads, ctx->q_rot, ctx->q_dim, k, v, kcs, cs_table, ctx->cfg.rope_mode,
-                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : (planes ? 2 : 0), true, kvcs))
+                                  ctx->cfg.act_dtype == PA_F16, st, prefill ? 1 : (planes ? 2 : 0), true, kvcs, &rot_only))
       return rc;
-  if (prefill)
-    return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st);
+  if (prefill) {
+    const PlainQ plain{q, qcs, qhs};
+    return prefill_impl(L, seq, pos, n_cols, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, st, rot_only ? &plain : nullptr);
+  }
   pa_item it{seq, pos, n_cols, 0};
   if (planes)
     return decode_impl(L, &it, 1, ctx->q_rot, PA_F16, ctx->q_dim, ctx->cfg.head_dim, gate, gcs, ghs, out, ocs, nullptr, st, "pa_attn_layer", true, false, nullptr,

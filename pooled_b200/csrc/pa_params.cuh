@@ -68,6 +68,7 @@ struct RopeParams {
   const void* q; uint64_t q_col_stride, q_head_stride; uint32_t q_heads;   // q == nullptr: skip
   void* q_out; uint64_t q_out_col_stride; int q_out_f16;                    // f32 (or f16), heads packed [q_heads][hd]
   uint64_t q_lo_offset;    // q_out_f16 == 2: f16 high parts at q_out, f16 low parts (x - fl16(x)) this many halves later
+  uint32_t q_rot_only;     // 1 (vectorised kernel): only the rotated dims of q are written; the reader takes the rest from q itself
   const void* k; const void* v; uint64_t kv_col_stride, v_col_stride; uint32_t kv_heads;  // k == nullptr: skip; kv_col_stride is k's
   __half* k_cache; __half* v_cache; uint64_t cache_row0;                    // row of column 0
   uint32_t hd, n_rot, pos, mode;
@@ -140,7 +141,10 @@ struct PrefillParams {
   uint32_t early_limit;         // ... and below this row (the call before may still be writing its own row)
   uint32_t pre_stages;          // ... and only this many K tiles (one fewer V tiles) before the q loads are in flight
   uint32_t kv_evict_first;      // split-K: 1 = the K / V tiles enter L2 as evict-first lines
-  uint32_t q_tma;               // prefill, head_dim 256, f16 q: the CTA's 128 query rows come by one TMA copy (tm_q)
+  uint32_t q_tma;               // prefill, head_dim 256, f16 q: the CTA's 128 query rows come by TMA (tm_q); 2: the first
+                                // q_rot_chunks 64-dim chunks of a head from tm_q (the rotated q), the others from tm_q2
+                                // (the caller's own q, head stride q2_head_stride: unrotated dims are not copied anywhere)
+  uint32_t q_rot_chunks; uint64_t q2_head_stride;
   uint32_t out_tma;             // prefill, f16 out: the CTA's output tile leaves through shared memory by one TMA store (tm_o)
 };
 

@@ -210,7 +210,7 @@ struct PfSmem {
 template <int HD, int MODE>
 __global__ void __launch_bounds__(PfSmem<HD, MODE>::THREADS, 1)
 pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
-                  const __grid_constant__ CUtensorMap tm_o, const PrefillParams p) {
+                  const __grid_constant__ CUtensorMap tm_o, const __grid_constant__ CUtensorMap tm_q2, const PrefillParams p) {
   using L = PfSmem<HD, MODE>;
   constexpr int CH = HD / 64;
   constexpr bool SK = MODE != 0, PREC = MODE == 2;
@@ -285,6 +285,8 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       if (q_by_tma) {
         mbar_expect_tx(BAR(Q_FULL, 0), (HD / 64) * kBM * 128);
         tma_load_3d(smem_u32(q_s), &tm_q, 0, (int)c0, (int)(h * (p.q_head_stride / 64)), BAR(Q_FULL, 0));
+        if (p.q_tma == 2)   // the chunks no rotation touches come straight from the caller's q
+          tma_load_3d(smem_u32(q_s + p.q_rot_chunks * (kBM * 128)), &tm_q2, 0, (int)c0, (int)(h * (p.q2_head_stride / 64) + p.q_rot_chunks), BAR(Q_FULL, 0));
       }
       bool waited = !early;
       for (uint32_t j = 0; j < n_tiles; ++j) {
@@ -700,7 +702,7 @@ int prefill_supported(const pa_ctx* ctx) { return ctx->cfg.head_dim == 256 || ct
 
 template <int HD, int MODE>
 static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
-                             const CUtensorMap& tm_o, dim3 grid, cudaStream_t st) {
+                             const CUtensorMap& tm_o, const CUtensorMap& tm_q2, dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {};
   const int dev = L->ctx->device & 63;
   if (!attr_set[dev]) {
@@ -709,19 +711,19 @@ static cudaError_t launch_pf(const pa_layer* L, const PrefillParams& p, const CU
     attr_set[dev] = true;
   }
   if (MODE == 0) {
-    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, tm_q, tm_o, p);
+    pa_prefill_kernel<HD, MODE><<<grid, PfSmem<HD, MODE>::THREADS, PfSmem<HD, MODE>::TOTAL, st>>>(tm_k, tm_v, tm_q, tm_o, tm_q2, p);
     return cudaGetLastError();
   }
-  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, tm_q, tm_o, p);
+  return launch_pdl(pa_prefill_kernel<HD, MODE>, grid, dim3(PfSmem<HD, MODE>::THREADS), (size_t)PfSmem<HD, MODE>::TOTAL, st, tm_k, tm_v, tm_q, tm_o, tm_q2, p);
 }
 
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
-                           const CUtensorMap& tm_o, cudaStream_t st) {
+                           const CUtensorMap& tm_o, const CUtensorMap& tm_q2, cudaStream_t st) {
   const dim3 grid((p.n_cols + kBM - 1) / kBM, p.n_heads);
   switch (L->ctx->cfg.head_dim) {
-    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, tm_q, tm_o, grid, st);
-    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, tm_q, tm_o, grid, st);
-    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, tm_q, tm_o, grid, st);
+    case 256: return launch_pf<256, 0>(L, p, tm_k, tm_v, tm_q, tm_o, tm_q2, grid, st);
+    case 128: return launch_pf<128, 0>(L, p, tm_k, tm_v, tm_q, tm_o, tm_q2, grid, st);
+    case 64: return launch_pf<64, 0>(L, p, tm_k, tm_v, tm_q, tm_o, tm_q2, grid, st);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -731,8 +733,8 @@ cudaError_t launch_verify(const pa_layer* L, const PrefillParams& p, const CUten
   const dim3 grid(p.n_splits, n_kv);
   const bool precise = !(L->ctx->cfg.flags & PA_FLAG_FAST);
   if (L->ctx->cfg.head_dim == 256)
-    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st);   // (no maps of q and out in this form)
-  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, tm_k, tm_k, grid, st);
+    return precise ? launch_pf<256, 2>(L, p, tm_k, tm_v, tm_k, tm_k, tm_k, grid, st) : launch_pf<256, 1>(L, p, tm_k, tm_v, tm_k, tm_k, tm_k, grid, st);   // (no maps of q and out in this form)
+  return precise ? launch_pf<128, 2>(L, p, tm_k, tm_v, tm_k, tm_k, tm_k, grid, st) : launch_pf<128, 1>(L, p, tm_k, tm_v, tm_k, tm_k, tm_k, grid, st);
 }
 
 }  // namespace pa

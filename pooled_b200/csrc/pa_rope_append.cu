@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParam
   // ---- everything else: 16-byte vectors of the unrotated dims of q and k, and all of v ----
   {
     const uint32_t cv = (hd - p.n_rot) / 8, vv = hd / 8;
-    const uint32_t nq = nqh * cv, nk = nkh * cv, nv = p.v ? p.kv_heads * vv : 0, total = nq + nk + nv;
+    const uint32_t nq = p.q_rot_only ? 0u : nqh * cv, nk = nkh * cv, nv = p.v ? p.kv_heads * vv : 0, total = nq + nk + nv;
     for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * blockDim.x) {
       uint4 A[4]; __half* dst[4]; int kind[4];
 #pragma unroll
@@ -350,12 +350,16 @@ __global__ void __launch_bounds__(256) pa_sigmoid_mul_kernel(const SigmoidParams
   }
 }
 
-cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
+// whether a call goes to the vectorised kernel (the only one that knows q_rot_only)
+bool rope_vec_applies(const RopeParams& p, uint32_t n_cols) {
   auto al16 = [](const void* x) { return ((uintptr_t)x & 15) == 0; };
-  const bool vec = n_cols >= 16 && p.mode == PA_ROPE_F64 && (p.angles || p.n_ang) && p.in_f16 && p.n_rot % 16 == 0 && p.n_rot <= 256 && p.hd % 8 == 0 &&
-                   (!p.q || (p.q_out_f16 == 1 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
-                   (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0 && p.v_col_stride % 8 == 0));
-  if (vec && !p.n_items) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
+  return !p.n_items && n_cols >= 16 && p.mode == PA_ROPE_F64 && (p.angles || p.n_ang) && p.in_f16 && p.n_rot % 16 == 0 && p.n_rot <= 256 && p.hd % 8 == 0 &&
+         (!p.q || (p.q_out_f16 == 1 && al16(p.q) && al16(p.q_out) && p.q_col_stride % 8 == 0 && p.q_head_stride % 8 == 0 && p.q_out_col_stride % 8 == 0)) &&
+         (!p.k || (p.v && al16(p.k) && al16(p.v) && p.kv_col_stride % 8 == 0 && p.v_col_stride % 8 == 0));
+}
+
+cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_t st) {
+  if (rope_vec_applies(p, n_cols)) return launch_pdl(pa_rope_append_vec_kernel, dim3(n_cols), dim3(256), 0, st, p);
   if (n_cols >= 16 && !p.n_items) return launch_pdl(pa_rope_append_cols_kernel, dim3(n_cols), dim3(256), 0, st, p);
   const uint32_t slots = (p.q ? p.q_heads : 0) + (p.k ? p.kv_heads : 0) + (p.v ? p.kv_heads : 0);
   return launch_pdl(pa_rope_append_kernel, dim3(n_cols, slots), dim3(128), 0, st, p);
