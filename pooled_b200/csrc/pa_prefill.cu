@@ -176,9 +176,14 @@ struct PfSmem {
   // four (Q then comes from shared memory only: as an A operand in tensor memory it was no faster, and its 64 columns
   // are the fourth tile); the other forms keep three and the lower half of Q in tensor memory.
   static constexpr int SBUF = (MODE == 0 && HD == 256) ? 4 : 3;
-  // K ring and V ring depth (the scores run SBUF - 1 tiles ahead).  Split-K leaves 32 KB free so that its CTAs can
-  // join SMs that still run a small kernel; the four-tile prefill gives a V slot to the other half of Q.
-  static constexpr int NK = 3, NV = (MODE != 0 || SBUF == 4) ? 2 : 3;
+  // K ring and V ring depth.  Split-K: three K slots (the scores run two tiles ahead) and two V slots, which leaves
+  // 32 KB free so that its CTAs can join SMs that still run a small kernel.  Prefill: one K slot per scores issuer,
+  // tile j in slot j % 2, so that the fills of a slot are consumed by ONE thread, in order.  (With three slots shared by
+  // two issuers a parity wait can be passed two fills early: the issuer of the odd tiles comes for tile 3 in slot 0
+  // before tile 0 has landed there -- TMA copies finish out of order under the burst of a kernel's start -- the barrier
+  // is still in its first phase, and a wait for "parity 1" takes that for fill 1 done.  The second arrival on the
+  // slot's empty barrier that follows ends in a trap, once in some hundred launches.)
+  static constexpr int NK = MODE == 0 ? 2 : 3, NV = MODE == 0 ? 3 : 2;
   static constexpr int KV_BYTES = HD * 128;         // [HD/64][64 rows][128 B]
   // tensor memory columns: the first TQC 64-dim chunks of Q (32 columns of f16 pairs each) | S tiles (64 each; P
   // overwrites the first 32 of its S) | O (HD).  HD 256: 64 + 192 + 256, or 0 + 256 + 256 = 512.
@@ -196,6 +201,7 @@ struct PfSmem {
   // loop's pace; two threads take alternate tiles (a tile's instructions stay in one thread: the order of its sums is
   // fixed).
   static constexpr int QK_ISSUERS = MODE == 0 ? 2 : 1;   // (the split-K form's 168 registers leave no room for a 13th warp)
+  static_assert(QK_ISSUERS == 1 || (NK % QK_ISSUERS == 0 && SBUF >= 3), "a K slot belongs to one scores issuer");
   static constexpr int THREADS = 128 + 128 * NGRP + 32 * (QK_ISSUERS - 1);
   static constexpr int QK2_WARP = 4 + 4 * NGRP;      // the second scores issuer
   static constexpr int OFF_K = 0, OFF_V = NK * KV_BYTES, OFF_Q = (NK + NV) * KV_BYTES, OFF_X = OFF_Q + QS_BYTES, OFF_BAR = OFF_X + X_BYTES;
@@ -620,8 +626,10 @@ pa_prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     } else if (MODE == 0 && p.out_tma) {
       // The output tile leaves as the query tile came: through shared memory in the TMA layout ([64-dim chunk][row][128 B],
       // 16-byte pieces XOR-swizzled by the row), one bulk tensor store for the CTA.  The K ring is idle (every product
-      // has retired); the tile sits behind the row sums the groups have just exchanged there.  Rows past the prompt's
-      // end are not written: the map ends at n_cols.  (A lane storing its own row issues 16-byte stores 12 KB apart.)
+      // has retired, and so is the V ring that follows it: the tile may reach into it); the tile sits behind the row sums
+      // the groups have just exchanged there.  Rows past the prompt's end are not written: the map ends at n_cols.
+      // (A lane storing its own row issues 16-byte stores 12 KB apart.)
+      static_assert(2048 + (HD / 64) * kBM * 128 <= (L::NK + L::NV) * L::KV_BYTES, "the output tile fits the idle rings");
       uint8_t* o_s = base + L::OFF_K + 2048;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
