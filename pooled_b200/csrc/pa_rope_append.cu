@@ -213,8 +213,12 @@ __global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParam
   if (p.trigger_early) pdl_trigger();
   pdl_wait();
   if (!p.trigger_early) pdl_trigger();
-  for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) s_g[i] = p.n_ang ? p.ang[col * half + i] : p.angles[(uint64_t)col * half + i];
-  __syncthreads();
+  // the column's angles are requested now and go to shared memory after the first items' loads have been requested
+  // too: one memory round trip for both (half <= 128 <= blockDim.x)
+  Angle my_g;
+  const bool has_g = threadIdx.x < half;
+  if (has_g) my_g = p.n_ang ? p.ang[col * half + threadIdx.x] : p.angles[(uint64_t)col * half + threadIdx.x];
+  bool g_staged = false;
   const uint32_t kvd = p.kv_heads * hd;
   const __half* qs = reinterpret_cast<const __half*>(p.q) + (uint64_t)col * p.q_col_stride;
   const __half* ks = reinterpret_cast<const __half*>(p.k) + (uint64_t)col * p.kv_col_stride;
@@ -228,7 +232,8 @@ __global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParam
   //      head, so every lane of a warp carries the same four rotations ----
   {
     const uint32_t per = half / 2, total = (nqh + nkh) * per;
-    for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 2 * blockDim.x) {
+    for (uint32_t base = 0; base < total; base += 2 * blockDim.x) {   // (the same trips for every thread: a barrier sits inside)
+      const uint32_t w0 = base + threadIdx.x;
       uint32_t A[2], B[2]; const __half* src[2]; __half* dst[2]; uint32_t dd[2]; int kind[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -242,6 +247,11 @@ __global__ void __launch_bounds__(256) pa_rope_append_vec_kernel(const RopeParam
         dst[u] = (is_q ? qd + (uint64_t)head * hd : kd + (uint64_t)(head - nqh) * hd) + d;
         A[u] = *reinterpret_cast<const uint32_t*>(src[u]);
         B[u] = *reinterpret_cast<const uint32_t*>(src[u] + half);
+      }
+      if (!g_staged) {
+        if (has_g) s_g[threadIdx.x] = my_g;
+        __syncthreads();
+        g_staged = true;
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
