@@ -168,6 +168,7 @@ extern "C" int pa_create(int device, const pa_config* cfg, pa_ctx** out) {
   if (const char* e = getenv("POOLED_ATTN_XCH_PREFETCH")) ctx->tune.xch_prefetch = atoi(e);
   if (const char* e = getenv("POOLED_ATTN_KV_EVICT_FIRST")) ctx->tune.kv_evict_first = atoi(e) != 0;
   if (const char* e = getenv("POOLED_ATTN_NO_Q_TMA")) ctx->tune.no_q_tma = atoi(e) != 0;
+  if (const char* e = getenv("POOLED_ATTN_OLD_TAIL")) ctx->tune.old_tail = atoi(e) != 0;
   if (const char* e = getenv("POOLED_ATTN_NO_OUT_TMA")) ctx->tune.no_out_tma = atoi(e) != 0;
   auto bail = [&](int code, const char* what, cudaError_t e) {
     std::string msg = std::string("pa_create: ") + what + ": " + cudaGetErrorString(e);
@@ -766,7 +767,7 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   const bool merge = !partial && !exchange && !verify_tc && nt <= 2 && all_rows && !ctx->core_only && !ctx->tune.no_merge && max_rows > 0 &&
                      (uint64_t)ns * ctx->cfg.n_kv_heads * n_items <= (uint64_t)ctx->sm_count && 2 * ns >= units;
   if (merge) {
-    p.merge = 1; p.merge_ctr = ctx->merge_ctr;
+    p.merge = ctx->tune.old_tail ? 1u : 2u; p.merge_ctr = ctx->merge_ctr;
     p.gate = gate; p.gate_col_stride = gcs; p.gate_head_stride = ghs; p.out = out; p.out_col_stride = ocs; p.act_f16 = ctx->cfg.act_dtype == PA_F16;
   }
   timing_mark(ctx, st, 0);

@@ -1068,18 +1068,26 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       unit_addr(split, prow, slice, go, oo);
       gv0 = gate_ld(go);
     }
-    __threadfence();                       // this thread's record stores, device-wide
+    // The group's record stores are ordered before its count by the barrier and ONE fence (cumulative: what the
+    // barrier makes visible to thread 0 is covered by thread 0's fence), not by a fence in each of the 128 threads.
+    // A CTA that holds no merge unit counts itself in and leaves at once: its SM is free for the next kernel's CTA.
+    const bool lean = p.merge == 2;        // (1: a fence in every thread and every CTA waits, for comparison)
+    const bool has_units = split < n_units || !lean;
+    if (!lean) __threadfence();
     named_bar_sync(gbar, kConsumers);
     if (ltid == 0) {
+      if (lean) __threadfence();
       atomicAdd(ctr, 1u);
-      uint32_t polls = 0;
-      while (*reinterpret_cast<volatile unsigned int*>(ctr) < ns_live && !*s_err) {
-        if (++polls > (1u << 20)) { *s_err = WAIT_MERGE; break; }
-        if (polls > 8) __nanosleep(64);
+      if (has_units) {
+        uint32_t polls = 0;
+        while (*reinterpret_cast<volatile unsigned int*>(ctr) < ns_live && !*s_err) {
+          if (++polls > (1u << 20)) { *s_err = WAIT_MERGE; break; }
+          if (polls > 8) __nanosleep(64);
+        }
+        __threadfence();
       }
-      __threadfence();
     }
-    named_bar_sync(gbar, kConsumers);
+    if (has_units) named_bar_sync(gbar, kConsumers);
     MergeScratch& sc = *reinterpret_cast<MergeScratch*>(k_slots);   // the ring is idle: every tile has been consumed
     if (!*s_err) {
       for (uint32_t u = split; u < n_units; u += ns_live) {
