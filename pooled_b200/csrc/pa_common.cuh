@@ -283,7 +283,7 @@ struct pa_ctx {
     int own_prefetch = 0;        // POOLED_ATTN_OWN_PREFETCH=n: L2 requests for n of a decode CTA's own later tiles at entry
     int xch_prefetch = 0;        // POOLED_ATTN_XCH_PREFETCH=n: the same for calls that end in a cross-GPU exchange
     bool no_q_tma = false;       // POOLED_ATTN_NO_Q_TMA=1: the prefill kernel's query rows through the softmax threads' registers
-    bool old_tail = false;       // POOLED_ATTN_OLD_TAIL=1: in-kernel merge with a fence per thread and every CTA waiting for the records
+    bool old_tail = false;       // POOLED_ATTN_OLD_TAIL=1: in-kernel merge with every CTA waiting for the records (unit-less ones too)
     bool no_out_tma = false;     // POOLED_ATTN_NO_OUT_TMA=1: ... and its output rows by per-thread stores
     bool kv_evict_first = true;  // POOLED_ATTN_KV_EVICT_FIRST=0: decode / verify K and V tiles enter L2 with the default policy instead of evict-first
     bool no_merge = false;       // POOLED_ATTN_NO_MERGE: always merge the split records in the combine kernel

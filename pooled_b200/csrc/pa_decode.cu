@@ -1068,15 +1068,13 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       unit_addr(split, prow, slice, go, oo);
       gv0 = gate_ld(go);
     }
-    // The group's record stores are ordered before its count by the barrier and ONE fence (cumulative: what the
-    // barrier makes visible to thread 0 is covered by thread 0's fence), not by a fence in each of the 128 threads.
-    // A CTA that holds no merge unit counts itself in and leaves at once: its SM is free for the next kernel's CTA.
-    const bool lean = p.merge == 2;        // (1: a fence in every thread and every CTA waits, for comparison)
-    const bool has_units = split < n_units || !lean;
-    if (!lean) __threadfence();
+    // A CTA that holds no merge unit counts itself in and leaves at once: its SM is free for the next kernel's CTA
+    // (p.merge == 1: every CTA waits for the records, for comparison).  The fence stays in every thread: a single one
+    // in the counting thread behind the barrier measured slower.
+    const bool has_units = split < n_units || p.merge == 1;
+    __threadfence();                       // this thread's record stores, device-wide
     named_bar_sync(gbar, kConsumers);
     if (ltid == 0) {
-      if (lean) __threadfence();
       atomicAdd(ctr, 1u);
       if (has_units) {
         uint32_t polls = 0;

@@ -36,6 +36,7 @@ struct DecodeParams {
   // cache rows ascending (k_cache / v_cache above are the layer's caches)
   const uint32_t* gather; uint32_t gather_stride;
   // merge != 0: no combine kernel follows; the CTAs of each (item, kv head) merge their own records, gate and store
+  // (2: CTAs without a merge unit leave as soon as their record is counted; 1: they wait like the others)
   uint32_t merge; unsigned int* merge_ctr;
   const void* gate; uint64_t gate_col_stride, gate_head_stride;
   void* out; uint64_t out_col_stride; int act_f16;
