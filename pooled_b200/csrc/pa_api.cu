@@ -20,6 +20,7 @@ cudaError_t launch_rope_append(const RopeParams& p, uint32_t n_cols, cudaStream_
 cudaError_t launch_sigmoid_mul(const SigmoidParams& p, uint32_t n_cols, cudaStream_t st);
 cudaError_t launch_angles(const AnglesParams& p, cudaStream_t st);
 bool rope_vec_applies(const RopeParams& p, uint32_t n_cols);
+cudaError_t launch_epoch_bump(unsigned int* ctr, cudaStream_t st);
 cudaError_t launch_head_norm(const HeadNormParams& p, uint32_t n_cols, uint32_t n_heads, cudaStream_t st);
 int prefill_supported(const pa_ctx* ctx);
 cudaError_t launch_prefill(const pa_layer* L, const PrefillParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_q,
@@ -769,6 +770,12 @@ static int decode_impl(pa_layer* L, const pa_item* items, uint32_t n_items, cons
   if (merge) {
     p.merge = ctx->tune.old_tail ? 1u : 2u; p.merge_ctr = ctx->merge_ctr;
     p.gate = gate; p.gate_col_stride = gcs; p.gate_head_stride = ghs; p.out = out; p.out_col_stride = ocs; p.act_f16 = ctx->cfg.act_dtype == PA_F16;
+  }
+  // an exchanging call numbers itself ahead of its combine kernel: in the decode kernel where that runs
+  const bool decode_runs = !verify_tc && max_rows > 0;
+  if (exchange && !ctx->core_only) {
+    if (decode_runs) p.xch_ctr = ctx->xc.ctr;
+    else { CU_TRY(ctx, launch_epoch_bump(ctx->xc.ctr, st)); ctx->stats.kernel_launches++; }
   }
   timing_mark(ctx, st, 0);
   if (verify_tc) CU_TRY(ctx, launch_verify(L, vp, tm_k, tm_v, ctx->cfg.n_kv_heads, st));

@@ -227,7 +227,7 @@ struct ItemList {
 struct ExchangeView {
   float* peer[8];
   uint32_t world, rank, max_rows, hd;
-  unsigned int* ctr;   // local: [0] call counter (epoch), [1] CTA ticket of the running launch
+  unsigned int* ctr;   // local: [0] call counter (epoch); every exchanging call advances it once, ahead of its combine kernel
 };
 
 }  // namespace pa

@@ -47,9 +47,12 @@ __device__ __forceinline__ void fma4(float4& acc, const float4& x, float w) {
 // rank's buffer, waits (bounded) for the other ranks' slices and merges them in rank order, so every rank ends with the
 // same bits.  Every value travels as one 8-byte store {value, tag} (tag = call counter + 1): an 8-byte store lands
 // whole, so the receiver spins on the words themselves and no flag, fence or second round trip is needed.  The buffers
-// alternate with the call counter's parity; the last of the call's slices to get through advances the counter.
-// A thread owns NV dims of the slice (dd[]: dims within the slice).  `epoch`: the call counter, read by the caller at
-// any time between the end of the previous kernel and its own slice's xch_done (it cannot move in between).
+// alternate with the call counter's parity.  The counter is advanced once per exchanging call, ahead of the combine
+// kernel that reads it: by the first thread of the call's decode kernel after its wait (every kernel of the call
+// before has finished then), or by a one-thread kernel where no decode kernel runs.  (Counting the slices through at
+// the end of the combine kernel instead put 512 atomics on one word at the tail of a 128-row call.)
+// A thread owns NV dims of the slice (dd[]: dims within the slice).  `epoch`: the call counter as the combine kernel
+// finds it after its wait.
 template <int HD>
 struct XchSlot {
   size_t blk, o_idx, ml_idx;
@@ -133,15 +136,10 @@ __device__ __forceinline__ void xch_get(const ExchangeView& x, const XchSlot<HD>
   for (int k = 0; k < NV; ++k) t[k] = og[k];
   Lsum = Lg;
 }
-// one thread per slice, after its own xch_get: the last slice of the call advances the call counter
-__device__ __forceinline__ void xch_done(const ExchangeView& x, uint32_t total_units) {
-  __threadfence();
-  if (atomicAdd(x.ctr + 1, 1u) == total_units - 1) { x.ctr[1] = 0; __threadfence(); atomicAdd(x.ctr, 1u); }
-}
 // the three steps for a slice held by threads 0..63 (one dim each) with m and l in thread 64
 template <int HD>
 __device__ __forceinline__ void exchange_slice(const ExchangeView& x, uint32_t prow, uint32_t slice, int tid, float& t, float M, float& Lsum, uint32_t sweeps,
-                                               uint32_t* err, uint32_t total_units, uint32_t epoch) {
+                                               uint32_t* err, uint32_t epoch) {
   const XchSlot<HD> a(x, epoch, prow, slice * 64);
   const uint32_t dd[1] = {(uint32_t)tid & 63u};
   float tv[1] = {t};
@@ -149,7 +147,6 @@ __device__ __forceinline__ void exchange_slice(const ExchangeView& x, uint32_t p
   if (tid < 64) {
     xch_get<HD, 1>(x, a, dd, tv, Lsum, sweeps, err);
     t = tv[0];
-    if (tid == 0) xch_done(x, total_units);
   }
 }
 
@@ -278,6 +275,10 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   constexpr int CH = HD / 64;        // 128-byte chunks per cache row of one kv head
 
   const uint32_t split = blockIdx.x, g = blockIdx.y, item = blockIdx.z;
+  if (p.xch_ctr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    pdl_wait();                    // the exchanging call before this one has read the counter
+    atomicAdd(p.xch_ctr, 1u);      // this call's number: its combine kernel starts after this kernel's end
+  }
   const uint32_t n_cols = p.items.n_cols[item];
   if (p.gather) pdl_wait();   // the lists may come from the kernel before this one
   // gather: the item is one column whose list (length, then rows ascending) lives on the device; the split plan is
@@ -1102,6 +1103,15 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   if (*s_err && tid == 0) atomicMax(p.err, *s_err);
 }
 
+// the exchange's call counter for a call whose decode kernel does not run (a shard that holds no row of the call) or
+// is the tensor-core verify kernel
+__global__ void pa_epoch_bump_kernel(unsigned int* ctr) {
+  pdl_wait();
+  pdl_trigger();
+  atomicAdd(ctr, 1u);
+}
+cudaError_t launch_epoch_bump(unsigned int* ctr, cudaStream_t st) { return launch_pdl(pa_epoch_bump_kernel, dim3(1), dim3(1), 0, st, ctr); }
+
 // ------------------------------------------------------------------------------ combine --
 
 
@@ -1201,7 +1211,7 @@ __global__ void __launch_bounds__(256) pa_combine_kernel(const CombineParams p) 
     for (int i = 1; i < 16; ++i) t = __fadd_rn(t, sa[i * 64 + tid]);
   }
   if constexpr (XCH) {
-    exchange_slice<HD>(p.xc, prow, slice, tid, t, M, Lsum, p.xch_sweeps, p.err, gridDim.x * gridDim.y, xepoch);
+    exchange_slice<HD>(p.xc, prow, slice, tid, t, M, Lsum, p.xch_sweeps, p.err, xepoch);
   }
   if (tid < 64) {
     if (p.partial_out) {

@@ -38,6 +38,7 @@ struct DecodeParams {
   // merge != 0: no combine kernel follows; the CTAs of each (item, kv head) merge their own records, gate and store
   // (2: CTAs without a merge unit leave as soon as their record is counted; 1: they wait like the others)
   uint32_t merge; unsigned int* merge_ctr;
+  unsigned int* xch_ctr;   // != nullptr: the call ends in a cross-GPU exchange; the kernel's first thread advances its call counter
   const void* gate; uint64_t gate_col_stride, gate_head_stride;
   void* out; uint64_t out_col_stride; int act_f16;
   uint32_t* err;
