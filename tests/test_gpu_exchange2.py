@@ -44,6 +44,30 @@ def _worker(rank, world, port, ret):
                 Vf = np.concatenate([Vf, Vc[pos][None]])
                 ref = po.attn_f64(po.rope_neox_f64(q[0], nH, hd, 64, pos, 1e7)[None], Kf, Vf, nH, nKV, hd, pos, 1, g)
                 errs.append(float(np.abs(out - ref).max()))
+        # a short context that rank 1 holds nothing of (its decode kernel does not run: the call still takes its number
+        # in the exchange), single tokens and a 5-token block (the tensor-core verify kernel on rank 0)
+        eng0 = AttnEngine(AttnConfig(n_heads=nH, n_kv_heads=nKV, head_dim=hd, n_rot=64, rope_theta=1e7, max_seq=chunk, act_dtype=torch.float16), device=rank)
+        eng0.exchange_setup(rank, world, dist, max_rows=128)
+        sd0 = ShardedDecoder(eng0, ShardPlan(world, chunk), rank, dist, exchange="peer")
+        short = 500
+        K0 = util.normal_f16(51, (short + 16, nKV * hd)); V0 = util.normal_f16(52, (short + 16, nKV * hd))
+        Kf, Vf = po.np_f16_rne(K0[:short]).copy(), po.np_f16_rne(V0[:short]).copy()
+        if rank == 0:
+            eng0.cache(0, "k")[0, :short] = torch.from_numpy(Kf.view(np.int16)).cuda()
+            eng0.cache(0, "v")[0, :short] = torch.from_numpy(Vf.view(np.int16)).cuda()
+        d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.float16).cuda()
+        pos = short
+        for n_new in (1, 1, 5, 1):
+            q = util.normal_f16(500 + pos, (n_new, nH * hd)); g = util.normal_f16(600 + pos, (n_new, nH * hd))
+            out = eng0.encode_layer_sharded(0, pos, d(q), d(K0[pos:pos + n_new]), d(V0[pos:pos + n_new]), d(g)).float().cpu().numpy()
+            eng0.sync()
+            for c in range(n_new):
+                Kf = np.concatenate([Kf, po.f16_rne(po.rope_neox_f64(K0[pos + c], nKV, hd, 64, pos + c, 1e7))[None]])
+                Vf = np.concatenate([Vf, po.np_f16_rne(V0[pos + c])[None]])
+            qr = np.stack([po.rope_neox_f64(q[c], nH, hd, 64, pos + c, 1e7) for c in range(n_new)])
+            ref = po.attn_f64(qr, Kf, Vf, nH, nKV, hd, pos, n_new, g)
+            errs.append(float(np.abs(out - ref).max()))
+            pos += n_new
         # a batch of three sequences, one token each per step: one whose rows all sit on rank 0's shard (rank 1 holds
         # nothing of it), two that have grown into rank 1's; the peer form is one library call per step
         totals, n_seqs = [300, chunk + 77, chunk + 1900], 3
